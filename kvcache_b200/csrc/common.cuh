@@ -1,0 +1,85 @@
+// Shared helpers of the kernels: storage types, conversions, reductions, error codes.
+//
+// Every kernel keeps its arithmetic in float32 and converts only at loads and
+// stores, as the reference's fp16 kernels do (src/qwen_kernels.cu:2-3, :10-11);
+// the storage type here is bfloat16 or float32, chosen by the launcher's
+// `dtype` argument (0 = float32, 1 = bfloat16).
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <float.h>
+#include <stdint.h>
+
+#define KVB_API extern "C" __attribute__((visibility("default")))
+
+// Return codes of the launchers (0 = launched; CUDA errors are returned as positive codes).
+#define KVB_OK 0
+#define KVB_ERR_DTYPE (-1)
+#define KVB_ERR_SHAPE (-2)
+#define KVB_ERR_ALIGN (-3)
+#define KVB_ERR_LIMIT (-4)
+
+// Bits of the device-side error word that kernels set instead of touching bad memory.
+#define KVB_DEV_BAD_TOKEN 1   // a token id outside the vocabulary
+#define KVB_DEV_BAD_PAGE 2    // a needed key or value lies in a page the block table does not hold
+#define KVB_DEV_BAD_POS 4     // a position beyond the rotation table
+
+enum { KVB_F32 = 0, KVB_BF16 = 1 };
+
+typedef __nv_bfloat16 bf16;
+
+template <typename T> __device__ __forceinline__ float to_f32(T v);
+template <> __device__ __forceinline__ float to_f32<float>(float v) { return v; }
+template <> __device__ __forceinline__ float to_f32<bf16>(bf16 v) { return __bfloat162float(v); }
+
+template <typename T> __device__ __forceinline__ T from_f32(float v);
+template <> __device__ __forceinline__ float from_f32<float>(float v) { return v; }
+template <> __device__ __forceinline__ bf16 from_f32<bf16>(float v) { return __float2bfloat16_rn(v); }
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+
+// Sum over the block in a fixed order (warp shuffles, then the warps' partials one by
+// one), so a row's result does not depend on what else the launch holds.
+// `scratch` holds at least 33 floats.  All threads receive the result.
+__device__ __forceinline__ float block_sum(float v, float* scratch) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = (blockDim.x + 31) >> 5;
+    v = warp_sum(v);
+    __syncthreads();
+    if (lane == 0) scratch[warp] = v;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        float t = 0.f;
+        for (int w = 0; w < nwarps; ++w) t += scratch[w];
+        scratch[32] = t;
+    }
+    __syncthreads();
+    return scratch[32];
+}
+__device__ __forceinline__ float block_max(float v, float* scratch) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = (blockDim.x + 31) >> 5;
+    v = warp_max(v);
+    __syncthreads();
+    if (lane == 0) scratch[warp] = v;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        float t = -FLT_MAX;
+        for (int w = 0; w < nwarps; ++w) t = fmaxf(t, scratch[w]);
+        scratch[32] = t;
+    }
+    __syncthreads();
+    return scratch[32];
+}
+
+static inline int kvb_launch_status() {
+    cudaError_t e = cudaGetLastError();
+    return e == cudaSuccess ? KVB_OK : (int)e;
+}

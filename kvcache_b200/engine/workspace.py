@@ -1,0 +1,35 @@
+"""Named scratch buffers that outlive a step: activations keep their addresses from step
+to step (which CUDA graphs need) and nothing is allocated once the sizes have been seen.
+The reference allocates its activation buffers once, sized for the longest prompt
+(apps/qwen_serve.cu:69-83)."""
+from __future__ import annotations
+
+from typing import Dict, Tuple
+
+import torch
+
+
+class Workspace:
+    def __init__(self, device: torch.device | str):
+        self.device = torch.device(device)
+        self._buffers: Dict[str, torch.Tensor] = {}
+        self.frozen = False   # set while a CUDA graph is captured or replayed: growing is an error
+
+    def buffer(self, name: str, shape: Tuple[int, ...], dtype: torch.dtype) -> torch.Tensor:
+        count = 1
+        for s in shape:
+            count *= int(s)
+        buf = self._buffers.get(name)
+        if buf is None or buf.dtype != dtype or buf.numel() < count:
+            if self.frozen:
+                raise RuntimeError(f"workspace buffer '{name}' would have to grow to {count} elements "
+                                   f"while its addresses are pinned by a CUDA graph")
+            capacity = max(count, 1)
+            if buf is not None and buf.dtype == dtype:
+                capacity = max(capacity, buf.numel())
+            buf = torch.empty(capacity, dtype=dtype, device=self.device)
+            self._buffers[name] = buf
+        return buf[:count].view(shape)
+
+    def bytes(self) -> int:
+        return sum(b.numel() * b.element_size() for b in self._buffers.values())

@@ -1,0 +1,224 @@
+"""The kernel set: the contract every operator of a step goes through, and its CUDA form.
+
+`KernelSet` states what each operator computes; `CudaKernels` launches the
+hand-written sm_100a kernels of `kvcache_b200/csrc` through ctypes on the
+current CUDA stream.  The parts of a model call nothing else for device work
+(matrix products included: `linear`).  There is no CPU implementation in the
+package; `CudaKernels` raises if the device or the compiler is missing.
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Optional
+
+import torch
+
+from ..parts.base import PagedKVView, StepBatch
+from . import build
+
+_c_int, _c_float, _c_void_p = ctypes.c_int, ctypes.c_float, ctypes.c_void_p
+
+DEVICE_ERRORS = {1: "a token id outside the vocabulary",
+                 2: "a key or value was needed from a page the block table does not hold",
+                 4: "a position beyond the rotation table (longer than the model's maximum length)"}
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+class KernelSet:
+    """Operators of a step.  Shapes: T rows, H width, all tensors contiguous.
+
+    embed(table[V,H], ids[T]) -> h[T,H] float32
+    add_rmsnorm(h, delta, weight, eps, out, rows):
+        rows is None: h[r] += delta[r] (if delta is given); out[r] = h[r] * rsqrt(mean(h[r]^2) + eps) * weight
+        rows given:   v = h[rows[i]] + delta[rows[i]];      out[i] = v * rsqrt(mean(v^2) + eps) * weight
+    linear(x[M,K], w[N,K], out[M,N], bias[N] float32 or None): out = x . w^T + bias
+    qkv_rope_append(qkv[T,(Hq+2Hkv)D], bias, cos, sin, batch, kv, q_out[T,Hq*D]):
+        adds the bias, rotates queries and keys by the row's position, writes the queries to
+        q_out and, if kv.writes, keys and values into their cache pages
+    paged_attention(q[T,Hq*D], batch, kv, out[T,Hq*D], scale): causal (windowed if kv.spec.window)
+        softmax(scale * q.k) v over the keys of the row's request, from the pages
+    silu_mul(gate_up[T,2I], out[T,I]): out = silu(gate_up[:, :I]) * gate_up[:, I:]
+    sample(logits[R,V], temperature[R], seeds[R], counters[R]) -> tokens[R] int32
+    """
+
+    def check_errors(self) -> None:
+        """Raises if a kernel has flagged bad input since the last check (synchronises)."""
+
+
+def _dtype_code(t: torch.dtype) -> int:
+    if t == torch.float32:
+        return 0
+    if t == torch.bfloat16:
+        return 1
+    raise KernelError(f"kernels take float32 or bfloat16 tensors, got {t}")
+
+
+def _ptr(t: Optional[torch.Tensor]) -> _c_void_p:
+    if t is None:
+        return _c_void_p(0)
+    if not t.is_contiguous():
+        raise KernelError("kernels take contiguous tensors")
+    return _c_void_p(t.data_ptr())
+
+
+_RETURN_CODES = {-1: "unsupported dtype", -2: "unsupported shape", -3: "misaligned operand", -4: "size beyond the kernel's limit"}
+
+
+def _check(code: int, what: str) -> None:
+    if code == 0:
+        return
+    if code < 0:
+        raise KernelError(f"{what}: refused ({_RETURN_CODES.get(code, code)})")
+    raise KernelError(f"{what}: CUDA error {code} at launch")
+
+
+_SIGNATURES = {
+    "elementwise": {
+        "kvb_embed": [_c_int, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_void_p, _c_void_p],
+        "kvb_add_rmsnorm": [_c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_float, _c_void_p],
+        "kvb_silu_mul": [_c_int, _c_void_p, _c_void_p, _c_int, _c_int, _c_void_p],
+    },
+    "rope_append": {
+        "kvb_qkv_rope_append": [_c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_void_p,
+                                _c_void_p, _c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int,
+                                _c_int, _c_int, _c_int, _c_int, _c_void_p, _c_void_p],
+    },
+    "attention_generic": {
+        "kvb_paged_attention_generic": [_c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p,
+                                        _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int,
+                                        _c_float, _c_void_p, _c_void_p],
+    },
+    "gemm_simt": {
+        "kvb_gemm_simt": [_c_int, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_void_p],
+    },
+    "sampling": {
+        "kvb_sample_parts": [_c_int],
+        "kvb_sample": [_c_void_p, _c_int, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p],
+    },
+}
+
+
+class _Library:
+    """A lazily built and loaded kernel module with typed entry points."""
+
+    def __init__(self, module: str):
+        self.module = module
+        self._lib = None
+
+    def __getattr__(self, name: str):
+        if self._lib is None:
+            lib = build.load_module(self.module)
+            for fname, argtypes in _SIGNATURES[self.module].items():
+                fn = getattr(lib, fname)
+                fn.argtypes = argtypes
+                fn.restype = _c_int
+            self._lib = lib
+        return getattr(self._lib, name)
+
+
+class CudaKernels(KernelSet):
+    def __init__(self, device: torch.device | str = "cuda:0", bf16_gemm: str = "cublas"):
+        self.device = torch.device(device)
+        if self.device.type != "cuda" or not torch.cuda.is_available():
+            raise KernelError("kvcache_b200 runs on a CUDA device (sm_100a) only; no device is available")
+        major, minor = torch.cuda.get_device_capability(self.device)
+        if major != 10:
+            raise KernelError(f"kernels are built for sm_100a; device {self.device} is sm_{major}{minor}")
+        if bf16_gemm not in ("cublas", "simt"):
+            raise KernelError(f"unknown bf16_gemm '{bf16_gemm}'")
+        self.bf16_gemm = bf16_gemm
+        self._elementwise = _Library("elementwise")
+        self._rope = _Library("rope_append")
+        self._attn_generic = _Library("attention_generic")
+        self._gemm_simt = _Library("gemm_simt")
+        self._sampling = _Library("sampling")
+        self.error_word = torch.zeros(1, dtype=torch.int32, device=self.device)
+        self.launches = 0
+
+    # ---- helpers -----------------------------------------------------------
+    def _stream(self) -> _c_void_p:
+        return _c_void_p(torch.cuda.current_stream(self.device).cuda_stream)
+
+    def check_errors(self) -> None:
+        word = int(self.error_word.item())
+        if word:
+            self.error_word.zero_()
+            reasons = [text for bit, text in DEVICE_ERRORS.items() if word & bit]
+            raise KernelError("a kernel flagged bad input: " + "; ".join(reasons))
+
+    # ---- operators ---------------------------------------------------------
+    def embed(self, table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor) -> None:
+        T, H = out.shape
+        self.launches += 1
+        _check(self._elementwise.kvb_embed(_dtype_code(table.dtype), _ptr(table), _ptr(ids), _ptr(out), T, H,
+                                           table.shape[0], _ptr(self.error_word), self._stream()), "embed")
+
+    def add_rmsnorm(self, h: torch.Tensor, delta: Optional[torch.Tensor], weight: torch.Tensor, eps: float,
+                    out: torch.Tensor, rows: Optional[torch.Tensor] = None) -> None:
+        n_out, H = out.shape
+        self.launches += 1
+        _check(self._elementwise.kvb_add_rmsnorm(_dtype_code(out.dtype), _ptr(h), _ptr(delta), _ptr(weight),
+                                                 _ptr(out), _ptr(rows), n_out, H, float(eps), self._stream()),
+               "add_rmsnorm")
+
+    def silu_mul(self, gate_up: torch.Tensor, out: torch.Tensor) -> None:
+        T, I = out.shape
+        self.launches += 1
+        _check(self._elementwise.kvb_silu_mul(_dtype_code(out.dtype), _ptr(gate_up), _ptr(out), T, I, self._stream()),
+               "silu_mul")
+
+    def linear(self, x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bias: Optional[torch.Tensor] = None) -> None:
+        M, K = x.shape
+        N = w.shape[0]
+        if w.shape[1] != K or tuple(out.shape) != (M, N):
+            raise KernelError(f"linear: shapes x{tuple(x.shape)} w{tuple(w.shape)} out{tuple(out.shape)} do not fit")
+        self.launches += 1
+        if x.dtype == torch.bfloat16 and self.bf16_gemm == "cublas":
+            # Library matrix product, as the reference's cublasGemmEx (apps/qwen_serve.cu:27-39).
+            if out.dtype == torch.bfloat16:
+                torch.matmul(x, w.t(), out=out)
+            else:
+                torch.mm(x, w.t(), out_dtype=torch.float32, out=out)
+            if bias is not None:
+                out.add_(bias)
+            return
+        _check(self._gemm_simt.kvb_gemm_simt(_dtype_code(x.dtype), _dtype_code(out.dtype), _ptr(x), _ptr(w),
+                                             _ptr(bias), _ptr(out), M, N, K, self._stream()), "linear")
+
+    def qkv_rope_append(self, qkv: torch.Tensor, bias: Optional[torch.Tensor], cos: Optional[torch.Tensor],
+                        sin: Optional[torch.Tensor], batch: StepBatch, kv: PagedKVView, q_out: torch.Tensor,
+                        num_heads: int) -> None:
+        T = qkv.shape[0]
+        spec = kv.spec
+        rot_half = 0 if cos is None else cos.shape[1]
+        table_len = 0 if cos is None else cos.shape[0]
+        self.launches += 1
+        _check(self._rope.kvb_qkv_rope_append(
+            _dtype_code(qkv.dtype), _ptr(qkv), _ptr(bias), _ptr(cos), _ptr(sin), rot_half, table_len,
+            _ptr(batch.positions), _ptr(batch.row_segment), _ptr(kv.block_table), kv.block_table.shape[1],
+            _ptr(kv.k_pages), _ptr(kv.v_pages), _ptr(q_out), T, num_heads, spec.num_kv_heads, spec.head_dim,
+            kv.page_size, 1 if kv.writes else 0, _ptr(self.error_word), self._stream()), "qkv_rope_append")
+
+    def paged_attention(self, q: torch.Tensor, batch: StepBatch, kv: PagedKVView, out: torch.Tensor,
+                        num_heads: int, scale: float) -> None:
+        T = q.shape[0]
+        spec = kv.spec
+        self.launches += 1
+        _check(self._attn_generic.kvb_paged_attention_generic(
+            _dtype_code(q.dtype), _ptr(q), _ptr(kv.k_pages), _ptr(kv.v_pages), _ptr(kv.block_table),
+            kv.block_table.shape[1], _ptr(batch.positions), _ptr(batch.row_segment), _ptr(out), T, num_heads,
+            spec.num_kv_heads, spec.head_dim, kv.page_size, spec.window or 0, float(scale),
+            _ptr(self.error_word), self._stream()), "paged_attention")
+
+    def sample(self, logits: torch.Tensor, temperature: torch.Tensor, seeds: torch.Tensor, counters: torch.Tensor,
+               out: torch.Tensor, scratch_val: torch.Tensor, scratch_idx: torch.Tensor) -> None:
+        R, V = logits.shape
+        self.launches += 1
+        _check(self._sampling.kvb_sample(_ptr(logits), R, V, _ptr(temperature), _ptr(seeds), _ptr(counters),
+                                         _ptr(scratch_val), _ptr(scratch_idx), _ptr(out), self._stream()), "sample")
+
+    def sample_parts(self, vocab: int) -> int:
+        return int(self._sampling.kvb_sample_parts(vocab))

@@ -1,0 +1,156 @@
+"""Interfaces of the parts a model is put together from, and the context a step hands them.
+
+A part knows its own sizes and constants and nothing about the model around it.
+It declares the checkpoint tensors it wants (`tensor_specs`), takes them
+(`bind`), and runs on the rows of one step (`forward`).  The kinds of part:
+
+* `Norm`            - `add_norm(h, delta, out, ctx)`: folds `delta` into the float32 residual
+                      stream `h` and writes the normalised rows in the compute type.
+* `PositionEncoding`- `on_embed(h, ctx)` for encodings added to the embedding and
+                      `rotation()` for encodings that rotate queries and keys.
+* `Mixer`           - `forward(x, ctx) -> delta`; declares the cache it needs with
+                      `cache_spec()` (pages of keys and values) and `state_spec()`
+                      (per-request state of fixed size).
+* `FeedForward`     - `forward(x, ctx) -> delta`.
+* `Block`           - the arrangement of the four in one layer.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Any, Dict, Mapping, Optional, Tuple
+
+import torch
+
+from ..weights.loader import TensorSpec
+
+TORCH_DTYPES = {"bfloat16": torch.bfloat16, "float32": torch.float32}
+
+
+@dataclass(frozen=True)
+class PagedKVSpec:
+    """Pages of keys and values: `[pages, num_kv_heads, page_size, head_dim]` for K and for V.
+
+    `window`: how many keys, its own included, a query sees (None: all of them).
+    Layers whose specs are equal share a group: one block table, one page id
+    for all of them, as the reference uses one table for its 24 layers
+    (apps/qwen_serve.cu:99-100).
+    """
+    num_kv_heads: int
+    head_dim: int
+    window: Optional[int] = None
+
+
+@dataclass(frozen=True)
+class StateSpec:
+    """Per-request state of fixed size: one `shape`-sized tensor per live request, zeroed at admission."""
+    shape: Tuple[int, ...]
+    dtype: str = "float32"
+
+
+@dataclass
+class PagedKVView:
+    """The cache one layer call reads and writes."""
+    spec: PagedKVSpec
+    k_pages: torch.Tensor            # [pages, num_kv_heads, page_size, head_dim]
+    v_pages: torch.Tensor
+    block_table: torch.Tensor        # int32 [segments capacity, pages per request]; -1 where no page is held
+    page_size: int
+    writes: bool = True              # False: the call reads what another call wrote
+
+
+@dataclass
+class StepBatch:
+    """The rows of one step, on the device.  Row r is one token; a segment is the run of
+    rows that one request brings (a portion of a prompt, or one decoded token)."""
+    num_tokens: int
+    num_segments: int
+    num_wanted: int
+    token_ids: torch.Tensor          # int32 [T]
+    positions: torch.Tensor          # int32 [T]   absolute position of the row in its request
+    row_segment: torch.Tensor        # int32 [T]   which segment the row belongs to
+    seg_q_start: torch.Tensor        # int32 [S]   first row of the segment
+    seg_q_len: torch.Tensor          # int32 [S]
+    seg_kv_len: torch.Tensor         # int32 [S]   tokens of the request cached after this step
+    seg_slot: torch.Tensor           # int32 [S]   the request's state slot
+    wanted_rows: torch.Tensor        # int32 [R]   rows whose logits are returned
+    max_q_len: int = 1               # host copies, for launch shapes
+    max_kv_len: int = 1
+    host: Dict[str, Any] = field(default_factory=dict)
+
+
+@dataclass
+class LayerContext:
+    """What a part may touch during one layer call."""
+    batch: StepBatch
+    kernels: Any                     # the kernel set (see kvcache_b200.kernels.api)
+    workspace: Any                   # named scratch buffers that outlive the step
+    kv: Optional[PagedKVView] = None
+    state: Optional[torch.Tensor] = None   # [slots, *StateSpec.shape]
+    call_index: int = 0
+
+
+class Part:
+    """Base of all parts: checkpoint tensors in, device buffers held."""
+
+    def tensor_specs(self) -> Dict[str, TensorSpec]:
+        return {}
+
+    def init_kinds(self) -> Dict[str, str]:
+        """Random-weights mode: `{name: "normal" | "ones_plus_normal" | "skip"}` for non-default tensors."""
+        return {}
+
+    def bind(self, tensors: Mapping[str, torch.Tensor], device: torch.device) -> None:
+        """Takes this part's tensors (CPU, as stored) and places what it needs on the device."""
+
+    def weight_bytes(self) -> int:
+        """Bytes of device weights one step has to read (for rooflines)."""
+        return 0
+
+
+class Norm(Part):
+    def add_norm(self, h: torch.Tensor, delta: Optional[torch.Tensor], out: torch.Tensor,
+                 ctx: LayerContext, rows: Optional[torch.Tensor] = None) -> None:
+        raise NotImplementedError
+
+
+@dataclass(frozen=True)
+class Rotation:
+    """Rotate-half rotation of the first `2 * cos.shape[1]` dimensions of each head:
+    dimension t pairs with t + rotary_dim/2, angle table[pos, t]."""
+    cos: torch.Tensor                # float32 [positions, rotary_dim / 2], on the device
+    sin: torch.Tensor
+
+
+class PositionEncoding(Part):
+    def on_embed(self, h: torch.Tensor, ctx: LayerContext) -> None:
+        """Encodings that are added to the embedded rows act here; default: nothing."""
+
+    def rotation(self) -> Optional[Rotation]:
+        """Encodings that rotate queries and keys return their table; default: none."""
+        return None
+
+
+class Mixer(Part):
+    def cache_spec(self) -> Optional[PagedKVSpec]:
+        return None
+
+    def state_spec(self) -> Optional[StateSpec]:
+        return None
+
+    def forward(self, x: torch.Tensor, ctx: LayerContext) -> torch.Tensor:
+        raise NotImplementedError
+
+
+class FeedForward(Part):
+    def forward(self, x: torch.Tensor, ctx: LayerContext) -> torch.Tensor:
+        raise NotImplementedError
+
+
+class Block(Part):
+    """One layer.  `forward` receives the residual stream `h` (float32, updated in place)
+    and the delta the previous layer has not yet added to it, and returns its own."""
+
+    mixer: Mixer
+
+    def forward(self, h: torch.Tensor, pending: Optional[torch.Tensor], ctx: LayerContext) -> Optional[torch.Tensor]:
+        raise NotImplementedError

@@ -1,0 +1,50 @@
+"""Dense gated feed-forward (reference: apps/qwen_serve.cu:112-116, src/qwen_kernels.cu:102-105)."""
+from __future__ import annotations
+
+from typing import Dict, Mapping, Optional
+
+import torch
+
+from ..weights.loader import TensorSpec
+from .base import TORCH_DTYPES, FeedForward, LayerContext
+
+
+class GatedMLP(FeedForward):
+    """delta = (act(x Wg^T) * (x Wu^T)) Wd^T with act = silu; no biases."""
+
+    def __init__(self, hidden: int, intermediate: int, *, activation: str, prefix: str, dtype: str):
+        if activation != "silu":
+            raise ValueError(f"activation '{activation}' is not supported by the gated feed-forward kernel")
+        self.hidden, self.intermediate = hidden, intermediate
+        self.prefix = prefix
+        self.dtype = TORCH_DTYPES[dtype]
+        self.w_gate_up: Optional[torch.Tensor] = None
+        self.w_down: Optional[torch.Tensor] = None
+
+    def tensor_specs(self) -> Dict[str, TensorSpec]:
+        p = self.prefix
+        return {
+            f"{p}gate_proj.weight": TensorSpec((self.intermediate, self.hidden)),
+            f"{p}up_proj.weight": TensorSpec((self.intermediate, self.hidden)),
+            f"{p}down_proj.weight": TensorSpec((self.hidden, self.intermediate)),
+        }
+
+    def bind(self, tensors: Mapping[str, torch.Tensor], device: torch.device) -> None:
+        p = self.prefix
+        self.w_gate_up = torch.cat([tensors[f"{p}gate_proj.weight"], tensors[f"{p}up_proj.weight"]], dim=0) \
+            .to(self.dtype).to(device).contiguous()
+        self.w_down = tensors[f"{p}down_proj.weight"].to(self.dtype).to(device).contiguous()
+
+    def weight_bytes(self) -> int:
+        return (self.w_gate_up.numel() + self.w_down.numel()) * self.w_down.element_size()
+
+    def forward(self, x: torch.Tensor, ctx: LayerContext) -> torch.Tensor:
+        T = x.shape[0]
+        k, ws = ctx.kernels, ctx.workspace
+        gate_up = ws.buffer("ffn.gate_up", (T, 2 * self.intermediate), self.dtype)
+        k.linear(x, self.w_gate_up, gate_up)
+        act = ws.buffer("ffn.act", (T, self.intermediate), self.dtype)
+        k.silu_mul(gate_up, act)
+        delta = ws.buffer("ffn.delta", (T, self.hidden), self.dtype)
+        k.linear(act, self.w_down, delta)
+        return delta
