@@ -35,6 +35,7 @@ MODULES: Dict[str, dict] = {
 
 _loaded: Dict[str, ctypes.CDLL] = {}
 _lock = threading.Lock()
+_dir_lock = threading.Lock()
 
 
 class BuildError(RuntimeError):
@@ -56,7 +57,7 @@ def find_nvcc() -> str:
 def _writable_dir(path: str) -> bool:
     try:
         os.makedirs(path, exist_ok=True)
-        probe = os.path.join(path, f".probe-{os.getpid()}")
+        probe = os.path.join(path, f".probe-{os.getpid()}-{threading.get_ident()}")
         with open(probe, "w"):
             pass
         os.remove(probe)
@@ -65,7 +66,18 @@ def _writable_dir(path: str) -> bool:
         return False
 
 
+_build_dir_cache: Optional[str] = None
+
+
 def build_dir() -> str:
+    global _build_dir_cache
+    with _dir_lock:
+        if _build_dir_cache is None:
+            _build_dir_cache = _choose_build_dir()
+        return _build_dir_cache
+
+
+def _choose_build_dir() -> str:
     override = os.environ.get("KVCACHE_B200_BUILD_DIR")
     if override and _writable_dir(override):
         return override

@@ -21,3 +21,66 @@ def make_runner(folder: str, kernels, *, dtype: str, device: str, page_size: int
 def random_tokens(vocab: int, n: int, seed: int) -> List[int]:
     rng = random.Random(seed)
     return [rng.randrange(vocab) for _ in range(n)]
+
+
+def paged_scenario(segments, *, num_kv_heads: int, head_dim: int, page_size: int, dtype, device,
+                   window=None, seed: int = 0, extra_pages: int = 3, fill_history: bool = True):
+    """A step's metadata and a paged cache with shuffled pages, made by hand for kernel tests.
+
+    `segments`: list of (tokens already cached, new tokens).  Returns (StepBatch, PagedKVView);
+    pages hold random keys and values for the cached part when `fill_history`.
+    """
+    import numpy as np
+    from kvcache_b200.parts.base import PagedKVSpec, PagedKVView, StepBatch
+    g = torch.Generator().manual_seed(seed)
+    S = len(segments)
+    T = sum(n for _, n in segments)
+    max_len = max(s + n for s, n in segments)
+    width = (max_len + page_size - 1) // page_size + 1
+    total_pages = sum((s + n + page_size - 1) // page_size for s, n in segments) + extra_pages
+    order = torch.randperm(total_pages, generator=g).tolist()      # shuffled physical pages
+    table = np.full((S, width), -1, dtype=np.int32)
+    at = 0
+    for i, (s, n) in enumerate(segments):
+        for j in range((s + n + page_size - 1) // page_size):
+            table[i, j] = order[at]
+            at += 1
+    shape = (total_pages, num_kv_heads, page_size, head_dim)
+    k_pages = torch.randn(shape, generator=g) if fill_history else torch.zeros(shape)
+    v_pages = torch.randn(shape, generator=g) if fill_history else torch.zeros(shape)
+    pos = np.concatenate([np.arange(s, s + n) for s, n in segments]).astype(np.int32)
+    row_seg = np.concatenate([np.full(n, i) for i, (s, n) in enumerate(segments)]).astype(np.int32)
+    q_start = np.cumsum([0] + [n for _, n in segments[:-1]]).astype(np.int32)
+    dev = lambda a: torch.as_tensor(a, dtype=torch.int32).to(device)
+    batch = StepBatch(
+        num_tokens=T, num_segments=S, num_wanted=0, token_ids=dev(np.zeros(T)), positions=dev(pos),
+        row_segment=dev(row_seg), seg_q_start=dev(q_start), seg_q_len=dev([n for _, n in segments]),
+        seg_kv_len=dev([s + n for s, n in segments]), seg_slot=dev(np.arange(S)), wanted_rows=dev([]),
+        max_q_len=max(n for _, n in segments), max_kv_len=max_len)
+    kv = PagedKVView(spec=PagedKVSpec(num_kv_heads, head_dim, window), k_pages=k_pages.to(dtype).to(device),
+                     v_pages=v_pages.to(dtype).to(device), block_table=dev(table), page_size=page_size, writes=True)
+    return batch, kv
+
+
+def clone_kv(kv, device=None):
+    from kvcache_b200.parts.base import PagedKVView
+    to = (lambda t: t.clone().to(device)) if device else (lambda t: t.clone())
+    return PagedKVView(spec=kv.spec, k_pages=to(kv.k_pages), v_pages=to(kv.v_pages), block_table=to(kv.block_table),
+                       page_size=kv.page_size, writes=kv.writes)
+
+
+def batch_to(batch, device):
+    import dataclasses
+    changes = {f.name: getattr(batch, f.name).to(device) for f in dataclasses.fields(batch)
+               if isinstance(getattr(batch, f.name), torch.Tensor)}
+    return dataclasses.replace(batch, **changes)
+
+
+def assert_close(got: torch.Tensor, want: torch.Tensor, rel: float, what: str = ""):
+    """max |got - want| <= rel * max(|want|) (the tolerance scales with the reference's size)."""
+    got, want = got.detach().double().cpu(), want.detach().double().cpu()
+    assert got.shape == want.shape, f"{what}: shape {tuple(got.shape)} vs {tuple(want.shape)}"
+    assert torch.isfinite(got).all(), f"{what}: non-finite values"
+    scale = max(want.abs().max().item(), 1e-30)
+    err = (got - want).abs().max().item()
+    assert err <= rel * scale, f"{what}: max abs error {err:.3e} > {rel:g} * {scale:.3e}"

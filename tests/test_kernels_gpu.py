@@ -1,0 +1,210 @@
+"""Each CUDA kernel alone against its plain PyTorch reference (float64 math on the same
+inputs), at sizes other than the engine tests use: head sizes in steps of 16, odd head
+counts and groups, widths and vocabularies that are no power of two, shuffled pages."""
+import pytest
+import torch
+
+from helpers import assert_close, batch_to, clone_kv, paged_scenario
+from torch_kernels import TorchKernels
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+REL = {torch.float32: 2e-5, torch.bfloat16: 1e-2}
+DTYPES = [torch.float32, torch.bfloat16]
+
+
+@pytest.fixture(scope="module")
+def kernels():
+    from kvcache_b200.kernels.api import CudaKernels
+    return CudaKernels(DEV)
+
+
+REF = TorchKernels(wide=True)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("T,H,V", [(1, 64, 100), (7, 896, 1531), (33, 120, 331)])
+def test_embed(kernels, dtype, T, H, V):
+    g = torch.Generator().manual_seed(0)
+    table = torch.randn(V, H, generator=g).to(dtype)
+    ids = torch.randint(0, V, (T,), generator=g, dtype=torch.int32)
+    out = torch.empty(T, H, dtype=torch.float32, device=DEV)
+    kernels.embed(table.to(DEV), ids.to(DEV), out)
+    assert torch.equal(out.cpu(), table[ids.long()].float())
+
+
+def test_embed_flags_bad_token(kernels):
+    from kvcache_b200.kernels.api import KernelError
+    table = torch.randn(10, 16, device=DEV)
+    out = torch.empty(2, 16, device=DEV)
+    kernels.embed(table, torch.tensor([3, 10], dtype=torch.int32, device=DEV), out)
+    with pytest.raises(KernelError, match="token id"):
+        kernels.check_errors()
+    kernels.check_errors()   # the word was cleared
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("T,H,eps", [(1, 64, 1e-6), (5, 896, 1e-6), (19, 120, 1e-5), (3, 3584, 1e-6), (4, 50, 1e-3)])
+def test_add_rmsnorm(kernels, dtype, T, H, eps):
+    g = torch.Generator().manual_seed(1)
+    h = torch.randn(T, H, generator=g) * 3
+    delta = torch.randn(T, H, generator=g).to(dtype)
+    w = 1 + 0.1 * torch.randn(H, generator=g)
+    for use_delta in (True, False):
+        h_ref, out_ref = h.clone(), torch.empty(T, H, dtype=dtype)
+        REF.add_rmsnorm(h_ref, delta if use_delta else None, w, eps, out_ref)
+        h_dev, out = h.clone().to(DEV), torch.empty(T, H, dtype=dtype, device=DEV)
+        kernels.add_rmsnorm(h_dev, delta.to(DEV) if use_delta else None, w.to(DEV), eps, out)
+        assert_close(h_dev, h_ref, 1e-6, "residual stream")
+        assert_close(out, out_ref, REL[dtype], "normalised rows")
+    rows = torch.tensor([T - 1, 0, T // 2], dtype=torch.int32)
+    out_ref = torch.empty(3, H, dtype=dtype)
+    REF.add_rmsnorm(h.clone(), delta, w, eps, out_ref, rows)
+    h_dev, out = h.clone().to(DEV), torch.empty(3, H, dtype=dtype, device=DEV)
+    kernels.add_rmsnorm(h_dev, delta.to(DEV), w.to(DEV), eps, out, rows.to(DEV))
+    assert torch.equal(h_dev.cpu(), h), "with rows the residual stream is left alone"
+    assert_close(out, out_ref, REL[dtype], "gathered rows")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("T,I", [(1, 128), (9, 4864), (31, 200), (2, 77)])
+def test_silu_mul(kernels, dtype, T, I):
+    gu = (torch.randn(T, 2 * I, generator=torch.Generator().manual_seed(2)) * 4).to(dtype)
+    ref = torch.empty(T, I, dtype=dtype)
+    REF.silu_mul(gu, ref)
+    out = torch.empty(T, I, dtype=dtype, device=DEV)
+    kernels.silu_mul(gu.to(DEV), out)
+    assert_close(out, ref, REL[dtype])
+
+
+@pytest.mark.parametrize("in_dtype,out_dtype", [(torch.float32, torch.float32), (torch.bfloat16, torch.bfloat16),
+                                                (torch.bfloat16, torch.float32)])
+@pytest.mark.parametrize("M,N,K", [(1, 256, 64), (5, 331, 120), (70, 130, 77), (64, 1152, 896), (129, 64, 333)])
+def test_gemm_simt(kernels, in_dtype, out_dtype, M, N, K):
+    g = torch.Generator().manual_seed(3)
+    x = torch.randn(M, K, generator=g).to(in_dtype)
+    w = torch.randn(N, K, generator=g).to(in_dtype)
+    bias = torch.randn(N, generator=g)
+    for b in (None, bias):
+        ref = torch.empty(M, N, dtype=out_dtype)
+        REF.linear(x, w, ref, b)
+        out = torch.empty(M, N, dtype=out_dtype, device=DEV)
+        saved = kernels.bf16_gemm
+        kernels.bf16_gemm = "simt"
+        try:
+            kernels.linear(x.to(DEV), w.to(DEV), out, b.to(DEV) if b is not None else None)
+        finally:
+            kernels.bf16_gemm = saved
+        assert_close(out, ref, REL[out_dtype])
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 256, 64), (8, 1152, 896), (70, 136, 80), (200, 331, 120)])
+def test_linear_bf16_library(kernels, M, N, K):
+    g = torch.Generator().manual_seed(4)
+    x = torch.randn(M, K, generator=g).to(torch.bfloat16)
+    w = torch.randn(N, K, generator=g).to(torch.bfloat16)
+    for out_dtype in (torch.bfloat16, torch.float32):
+        ref = torch.empty(M, N, dtype=out_dtype)
+        REF.linear(x, w, ref)
+        out = torch.empty(M, N, dtype=out_dtype, device=DEV)
+        kernels.linear(x.to(DEV), w.to(DEV), out)
+        assert_close(out, ref, REL[out_dtype])
+
+
+SCENARIOS = [
+    # (segments (cached, new), Hq, Hkv, D, page, window)
+    ([(0, 5)], 4, 2, 16, 16, None),
+    ([(0, 40), (17, 1), (63, 2)], 6, 2, 48, 8, None),
+    ([(130, 1), (0, 33), (31, 1), (200, 3)], 14, 2, 64, 16, None),
+    ([(300, 1)], 3, 1, 32, 8, None),
+    ([(0, 70), (90, 1), (41, 6)], 8, 8, 80, 16, 25),
+    ([(515, 2), (127, 1)], 5, 1, 128, 32, 128),
+    ([(0, 9)], 2, 2, 256, 4, None),
+]
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("scenario", SCENARIOS)
+def test_qkv_rope_append(kernels, dtype, scenario):
+    segments, Hq, Hkv, D, page, window = scenario
+    batch, kv = paged_scenario(segments, num_kv_heads=Hkv, head_dim=D, page_size=page, dtype=dtype, device="cpu",
+                               window=window, seed=5)
+    T = batch.num_tokens
+    g = torch.Generator().manual_seed(6)
+    qkv = torch.randn(T, (Hq + 2 * Hkv) * D, generator=g).to(dtype)
+    bias = torch.randn((Hq + 2 * Hkv) * D, generator=g)
+    from kvcache_b200.parts.position import RotaryHalf
+    rope = RotaryHalf(D, 10000.0, 1024)
+    rope.bind({}, torch.device("cpu"))
+    rot = rope.rotation()
+    for b in (bias, None):
+        kv_ref, q_ref = clone_kv(kv), torch.empty(T, Hq * D, dtype=dtype)
+        REF.qkv_rope_append(qkv, b, rot.cos, rot.sin, batch, kv_ref, q_ref, Hq)
+        kv_dev, q_out = clone_kv(kv, DEV), torch.empty(T, Hq * D, dtype=dtype, device=DEV)
+        kernels.qkv_rope_append(qkv.to(DEV), b.to(DEV) if b is not None else None, rot.cos.to(DEV), rot.sin.to(DEV),
+                                batch_to(batch, DEV), kv_dev, q_out, Hq)
+        assert_close(q_out, q_ref, REL[dtype], "queries")
+        assert_close(kv_dev.k_pages, kv_ref.k_pages, REL[dtype], "key pages")
+        assert_close(kv_dev.v_pages, kv_ref.v_pages, REL[dtype], "value pages")
+    kernels.check_errors()
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("scenario", SCENARIOS)
+def test_paged_attention_generic(kernels, dtype, scenario):
+    segments, Hq, Hkv, D, page, window = scenario
+    batch, kv = paged_scenario(segments, num_kv_heads=Hkv, head_dim=D, page_size=page, dtype=dtype, device="cpu",
+                               window=window, seed=7)
+    T = batch.num_tokens
+    q = torch.randn(T, Hq * D, generator=torch.Generator().manual_seed(8)).to(dtype)
+    ref = torch.empty(T, Hq * D, dtype=dtype)
+    REF.paged_attention(q, batch, kv, ref, Hq, D ** -0.5)
+    out = torch.empty(T, Hq * D, dtype=dtype, device=DEV)
+    kernels.paged_attention(q.to(DEV), batch_to(batch, DEV), clone_kv(kv, DEV), out, Hq, D ** -0.5)
+    assert_close(out, ref, REL[dtype])
+    kernels.check_errors()
+
+
+def test_attention_sees_one_far_key(kernels):
+    """One key among hundreds, on another page, scaled so that it takes all the weight: the
+    output must be that key's value."""
+    Hq, Hkv, D, page = 4, 2, 32, 16
+    batch, kv = paged_scenario([(700, 1)], num_kv_heads=Hkv, head_dim=D, page_size=page, dtype=torch.float32,
+                               device="cpu", seed=9)
+    q = torch.randn(1, Hq * D, generator=torch.Generator().manual_seed(10))
+    far = 37
+    p = int(kv.block_table[0, far // page])
+    for hk in range(Hkv):
+        kv.k_pages[p, hk, far % page] = 40.0 * q.view(Hq, D)[hk * 2] / q.view(Hq, D)[hk * 2].norm()
+    out = torch.empty(1, Hq * D, device=DEV)
+    kernels.paged_attention(q.to(DEV), batch_to(batch, DEV), clone_kv(kv, DEV), out, Hq, 1.0)
+    ref = torch.empty(1, Hq * D)
+    REF.paged_attention(q, batch, kv, ref, Hq, 1.0)
+    assert_close(out, ref, 2e-5)
+    got = out.view(Hq, D)[0].cpu()
+    assert (got - kv.v_pages[p, 0, far % page]).abs().max() < 1e-3
+
+
+@pytest.mark.parametrize("R,V", [(1, 256), (3, 331), (5, 151936), (64, 4099)])
+def test_sample(kernels, R, V):
+    from plain_qwen2 import gumbel_scores
+    g = torch.Generator().manual_seed(11)
+    logits = torch.randn(R, V, generator=g)
+    logits[0, V // 2] = logits[0].max() + 1
+    if V > 40:
+        logits[0, 7] = logits[0, V // 2]           # a tie: the lowest index wins
+    temperature = torch.tensor([0.0 if r % 2 == 0 else 0.7 for r in range(R)])
+    seeds = torch.tensor([1234567890123 + r for r in range(R)], dtype=torch.int64)
+    counters = torch.tensor([r * 3 for r in range(R)], dtype=torch.int32)
+    parts = kernels.sample_parts(V)
+    out = torch.empty(R, dtype=torch.int32, device=DEV)
+    kernels.sample(logits.to(DEV), temperature.to(DEV), seeds.to(DEV), counters.to(DEV), out,
+                   torch.empty(R * parts, device=DEV), torch.empty(R * parts, dtype=torch.int32, device=DEV))
+    out = out.cpu()
+    for r in range(min(R, 6)):
+        if temperature[r] == 0:
+            assert int(out[r]) == int(torch.argmax(logits[r])) or logits[r, out[r]] == logits[r].max()
+            assert int(out[r]) == int((logits[r] == logits[r].max()).nonzero()[0])
+        elif V <= 5000:
+            scores = gumbel_scores(logits[r], 0.7, int(seeds[r]), int(counters[r]))
+            assert scores[int(out[r])] >= scores.max() - 1e-4
