@@ -1,0 +1,70 @@
+"""The Python entry point: token ids in, generated token ids out, through the scheduler, the
+step function and the sampler.  It does in one process what the reference's driver does
+around its binary (tools/run_serve.py:28-38: ids to the engine, generated ids back)."""
+from __future__ import annotations
+
+import time
+from typing import Dict, List, Optional, Sequence, Union
+
+from ..config.options import EngineOptions
+from ..sampling.params import SamplingParams
+from ..sampling.sampler import Sampler
+from .core import EngineCore
+from .runner import StepEntry
+from .scheduler import Request, Scheduler
+
+
+class LLM:
+    """`LLM(folder, dtype="bfloat16", ...).generate(prompts, params)` -> one id list per prompt."""
+
+    def __init__(self, model: str, options: Optional[EngineOptions] = None, kernels=None, **option_fields):
+        if options is None:
+            options = EngineOptions(**option_fields)
+        elif option_fields:
+            raise ValueError("give either options or option fields, not both")
+        if options.num_pages is None and options.max_cached_tokens is None:
+            options.max_cached_tokens = 8192   # the reference's pool: 512 pages of 16 (apps/qwen_serve.cu:21)
+        self.options = options
+        self.core = EngineCore(model, options, kernels=kernels)
+        self.config = self.core.config
+        self.sampler = Sampler(self.core.kernels, self.core.device, self.core.model.vocab_size, options.max_running)
+        self.scheduler = self._new_scheduler()
+        self.last_stats = None
+        self.last_seconds = 0.0
+
+    def _new_scheduler(self) -> Scheduler:
+        o = self.options
+        return Scheduler(self.core.cache, max_running=o.max_running, max_tokens_per_step=o.max_tokens_per_step,
+                         chunk_size=o.chunk_size, max_model_len=self.core.max_model_len, admission=o.admission,
+                         default_eos=getattr(self.config, "eos_token_ids", ()))
+
+    def step(self) -> List[Request]:
+        """One scheduler iteration: plan, run, sample, record.  Returns finished requests."""
+        pieces = self.scheduler.schedule()
+        if not pieces:
+            return []
+        entries = [StepEntry(p.request.slot, p.tokens, [p.count - 1] if p.samples else []) for p in pieces]
+        logits = self.core.runner.step(entries)
+        sampling = [p.request for p in pieces if p.samples]
+        tokens = self.sampler.sample(logits, [r.params for r in sampling], [len(r.output) for r in sampling])
+        return self.scheduler.update(pieces, tokens)
+
+    def generate(self, prompts: Sequence[Sequence[int]],
+                 params: Union[SamplingParams, Sequence[SamplingParams], None] = None) -> List[List[int]]:
+        if params is None:
+            params = SamplingParams()
+        per_prompt = [params] * len(prompts) if isinstance(params, SamplingParams) else list(params)
+        if len(per_prompt) != len(prompts):
+            raise ValueError("one SamplingParams per prompt, or one for all")
+        self.scheduler = self._new_scheduler()
+        requests = [self.scheduler.add_request(p, sp) for p, sp in zip(prompts, per_prompt)]
+        start = time.perf_counter()
+        while self.scheduler.has_work():
+            before = self.scheduler.stats.steps
+            self.step()
+            if self.scheduler.stats.steps == before and self.scheduler.has_work() and not self.scheduler.running:
+                raise RuntimeError("the scheduler made no progress (a waiting request fits neither slots nor pages)")
+        self.core.kernels.check_errors()
+        self.last_seconds = time.perf_counter() - start
+        self.last_stats = self.scheduler.stats
+        return [r.output for r in requests]

@@ -1,0 +1,270 @@
+"""The scheduler: admits requests, cuts prompts into portions under a token budget, decodes,
+finishes and frees.  Host logic only; it talks to the cache manager's bookkeeping and never
+to the device.
+
+Grown from the reference's loop (apps/qwen_serve.cu:177-204) and toy engine
+(src/include/engine.h:100-140): retire, then admit in arrival order while the batch has room
+and the worst case of every admitted request still fits the pool
+(`reserved + ceil((prompt + max_new) / page) <= pages`, engine.h:114-124), then one decode
+token for every running request.  What is new here: a step mixes decode tokens with portions
+of prompts (the reference prefills each prompt whole and alone, qwen_serve.cu:90-124); a
+request is checked for its end right after sampling, so `max_new = 1` yields one token (the
+reference yields two, qwen_serve.cu:192-203); and a request that can never fit is refused
+when it is submitted (the reference's loop would spin forever, qwen_serve.cu:195,201).
+
+When pages run out.  `admission="reserve"` (default): they cannot, because every admitted
+request's worst case is held back.  `admission="optimistic"`: a request is admitted when its
+next portion fits; if a later step lacks pages, the newest running request is preempted - its
+pages and slot are given back, it returns to the head of the waiting queue and its tokens are
+run again later - until the step fits.  A lone request that cannot grow any further ends with
+reason "out_of_pages".
+"""
+from __future__ import annotations
+
+from collections import deque
+from dataclasses import dataclass, field
+from typing import Deque, Dict, List, Optional, Sequence, Tuple
+
+from ..cache.manager import CacheManager
+from ..sampling.params import SamplingParams
+
+WAITING, RUNNING, FINISHED = "waiting", "running", "finished"
+
+
+class RequestRejected(ValueError):
+    pass
+
+
+@dataclass
+class Request:
+    id: int
+    prompt: List[int]
+    params: SamplingParams
+    eos: Tuple[int, ...] = ()
+    state: str = WAITING
+    slot: int = -1
+    output: List[int] = field(default_factory=list)
+    num_computed: int = 0          # tokens of prompt + output already run through the model
+    finish_reason: Optional[str] = None
+    preemptions: int = 0
+    reserved: Optional[List[int]] = None   # pages held back for it in each group (reserve policy)
+
+    @property
+    def tokens(self) -> List[int]:
+        return self.prompt + self.output
+
+    @property
+    def num_tokens(self) -> int:
+        return len(self.prompt) + len(self.output)
+
+
+@dataclass
+class Piece:
+    """One request's share of a step."""
+    request: Request
+    start: int                     # first position run in this step
+    count: int
+    samples: bool                  # the piece ends at the request's last token: a token is sampled
+
+    @property
+    def tokens(self) -> List[int]:
+        return self.request.tokens[self.start:self.start + self.count]
+
+
+@dataclass
+class SchedulerStats:
+    """The reference's EngineStats (src/include/engine.h:33-45) plus portion counts."""
+    steps: int = 0
+    decode_tokens: int = 0
+    prefill_tokens: int = 0
+    generated: int = 0
+    finished: int = 0
+    preemptions: int = 0
+    peak_running: int = 0
+    peak_pages: int = 0
+
+
+class Scheduler:
+    def __init__(self, cache: CacheManager, *, max_running: int, max_tokens_per_step: int, chunk_size: int,
+                 max_model_len: int, admission: str = "reserve", default_eos: Sequence[int] = ()):
+        if admission not in ("reserve", "optimistic"):
+            raise ValueError(f"unknown admission policy '{admission}'")
+        self.cache = cache
+        self.max_running = min(max_running, cache.max_slots)
+        self.max_tokens_per_step = max_tokens_per_step
+        self.chunk_size = chunk_size
+        self.max_model_len = max_model_len
+        self.admission = admission
+        self.default_eos = tuple(default_eos)
+        self.waiting: Deque[Request] = deque()
+        self.running: List[Request] = []
+        self.finished: List[Request] = []
+        self.reserved = [0] * len(cache.groups)
+        self.stats = SchedulerStats()
+        self._next_id = 0
+
+    # ---- submission --------------------------------------------------------
+    def _worst_case(self, total_tokens: int) -> List[int]:
+        return [g.pages.worst_case_pages(total_tokens, self.chunk_size) for g in self.cache.groups]
+
+    def add_request(self, prompt: Sequence[int], params: SamplingParams) -> Request:
+        prompt = [int(t) for t in prompt]
+        if not prompt:
+            raise RequestRejected("a request needs at least one prompt token")
+        total = len(prompt) + params.max_new_tokens
+        if total > self.max_model_len:
+            raise RequestRejected(f"prompt ({len(prompt)}) + max_new_tokens ({params.max_new_tokens}) exceeds the "
+                                  f"model length {self.max_model_len}")
+        worst = self._worst_case(total)
+        if any(w > self.cache.num_pages for w in worst):
+            raise RequestRejected(f"the request can need {max(worst)} pages; the pool has {self.cache.num_pages}")
+        eos = () if params.ignore_eos else (params.eos_token_ids if params.eos_token_ids is not None else self.default_eos)
+        request = Request(self._next_id, prompt, params, eos=tuple(eos))
+        self._next_id += 1
+        self.waiting.append(request)
+        return request
+
+    def has_work(self) -> bool:
+        return bool(self.waiting or self.running)
+
+    # ---- one step's plan ---------------------------------------------------
+    def _admit(self, request: Request) -> None:
+        request.slot = self.cache.admit()
+        request.state = RUNNING
+        if self.admission == "reserve":
+            request.reserved = self._worst_case(len(request.prompt) + request.params.max_new_tokens)
+            for g, pages in enumerate(request.reserved):
+                self.reserved[g] += pages
+        self.running.append(request)
+
+    def _can_reserve(self, request: Request) -> bool:
+        worst = self._worst_case(len(request.prompt) + request.params.max_new_tokens)
+        return all(self.reserved[g] + w <= self.cache.num_pages for g, w in enumerate(worst))
+
+    def _retire(self, request: Request, reason: str) -> None:
+        request.state, request.finish_reason = FINISHED, reason
+        self._give_back(request)
+        self.running.remove(request)
+        self.finished.append(request)
+        self.stats.finished += 1
+
+    def _give_back(self, request: Request) -> None:
+        self.cache.release(request.slot)
+        request.slot = -1
+        if request.reserved is not None:
+            for g, pages in enumerate(request.reserved):
+                self.reserved[g] -= pages
+            request.reserved = None
+
+    def _preempt_newest(self, keep: Optional[Request] = None) -> Optional[Request]:
+        """Gives back the newest running request's pages; it waits again, first in line."""
+        for victim in reversed(self.running):
+            if victim is keep:
+                continue
+            self._give_back(victim)
+            self.running.remove(victim)
+            victim.state, victim.num_computed = WAITING, 0
+            victim.preemptions += 1
+            self.stats.preemptions += 1
+            self.waiting.appendleft(victim)
+            return victim
+        return None
+
+    def schedule(self) -> List[Piece]:
+        """Chooses this step's pieces: one token for every running request that is decoding,
+        then portions of unfinished prompts (oldest first), then newly admitted requests, all
+        under the token budget and the pages that are free.  May preempt (optimistic policy)."""
+        budget = self.max_tokens_per_step
+        pieces: List[Piece] = []
+        additions: List[Tuple[int, int]] = []
+
+        def fits(request: Request, count: int) -> bool:
+            return self.cache.pages_short(additions + [(request.slot, count)]) == 0
+
+        def place(request: Request, count: int) -> None:
+            nonlocal budget
+            start = request.num_computed
+            pieces.append(Piece(request, start, count, start + count == request.num_tokens))
+            additions.append((request.slot, count))
+            budget -= count
+
+        # Running requests, oldest first: decodes take one token, prompts a portion.
+        index = 0
+        while index < len(self.running):
+            request = self.running[index]
+            remaining = request.num_tokens - request.num_computed
+            count = min(remaining, self.chunk_size, budget)
+            if count <= 0:
+                index += 1
+                continue
+            while not fits(request, count):
+                victim = self._preempt_newest(keep=request)
+                if victim is None:
+                    break
+                # Drop what the victim had been given in this step.
+                pieces[:] = [p for p in pieces if p.request is not victim]
+                additions[:] = [(p.request.slot, p.count) for p in pieces]
+                budget = self.max_tokens_per_step - sum(p.count for p in pieces)
+            if not fits(request, count):
+                smaller = count
+                while smaller > 1 and not fits(request, smaller):
+                    smaller -= 1
+                if fits(request, smaller) and smaller < remaining:
+                    count = smaller           # a shorter portion of a prompt still makes progress
+                else:
+                    self._retire(request, "out_of_pages")
+                    continue
+            place(request, count)
+            index += 1
+
+        # Waiting requests, in arrival order; the first that does not fit blocks the rest.
+        while self.waiting and len(self.running) < self.max_running and budget > 0:
+            request = self.waiting[0]
+            if self.admission == "reserve" and not self._can_reserve(request):
+                break
+            count = min(request.num_tokens - request.num_computed, self.chunk_size, budget)
+            self.waiting.popleft()
+            self._admit(request)
+            if not fits(request, count):
+                # Not even its first portion fits now: back to the head of the queue.
+                self._give_back(request)
+                self.running.remove(request)
+                request.state = WAITING
+                self.waiting.appendleft(request)
+                break
+            place(request, count)
+
+        self.stats.peak_running = max(self.stats.peak_running, len(self.running))
+        return pieces
+
+    # ---- after the step ----------------------------------------------------
+    def update(self, pieces: Sequence[Piece], sampled: Sequence[int]) -> List[Request]:
+        """Records the step: `sampled` holds one token for every piece with `samples`, in
+        order.  Returns the requests that finished."""
+        done: List[Request] = []
+        it = iter(sampled)
+        self.stats.steps += 1
+        for piece in pieces:
+            request = piece.request
+            request.num_computed += piece.count
+            if piece.count == 1 and piece.start >= len(request.prompt):
+                self.stats.decode_tokens += 1
+            else:
+                self.stats.prefill_tokens += piece.count
+            if not piece.samples:
+                continue
+            token = int(next(it))
+            request.output.append(token)
+            self.stats.generated += 1
+            if token in request.eos:
+                reason = "eos"
+            elif len(request.output) >= request.params.max_new_tokens:
+                reason = "length"
+            elif request.num_tokens >= self.max_model_len:
+                reason = "model_length"
+            else:
+                continue
+            self._retire(request, reason)
+            done.append(request)
+        self.stats.peak_pages = max(self.stats.peak_pages, self.cache.used_pages())
+        return done
