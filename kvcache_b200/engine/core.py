@@ -43,4 +43,4 @@ class EngineCore:
                                   dtype=options.dtype, device=self.device)
         self.runner = ModelRunner(self.model, self.cache, self.kernels,
                                   max_tokens_per_step=options.max_tokens_per_step,
-                                  max_segments=options.max_running)
+                                  max_segments=options.max_running, use_graphs=options.use_graphs)

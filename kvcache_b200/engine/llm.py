@@ -8,7 +8,7 @@ from typing import Dict, List, Optional, Sequence, Union
 
 from ..config.options import EngineOptions
 from ..sampling.params import SamplingParams
-from ..sampling.sampler import Sampler
+from ..sampling.sampler import TokenReader
 from .core import EngineCore
 from .runner import StepEntry
 from .scheduler import Request, Scheduler
@@ -27,7 +27,7 @@ class LLM:
         self.options = options
         self.core = EngineCore(model, options, kernels=kernels)
         self.config = self.core.config
-        self.sampler = Sampler(self.core.kernels, self.core.device, self.core.model.vocab_size, options.max_running)
+        self.reader = TokenReader(self.core.device, options.max_running)
         self.scheduler = self._new_scheduler()
         self.last_stats = None
         self.last_seconds = 0.0
@@ -43,11 +43,12 @@ class LLM:
         pieces = self.scheduler.schedule()
         if not pieces:
             return []
-        entries = [StepEntry(p.request.slot, p.tokens, [p.count - 1] if p.samples else []) for p in pieces]
-        logits = self.core.runner.step(entries)
-        sampling = [p.request for p in pieces if p.samples]
-        tokens = self.sampler.sample(logits, [r.params for r in sampling], [len(r.output) for r in sampling])
-        return self.scheduler.update(pieces, tokens)
+        entries = [StepEntry(p.request.slot, p.tokens, [p.count - 1] if p.samples else [],
+                             (p.request.params.temperature, p.request.params.seed, len(p.request.output)))
+                   for p in pieces]
+        _, tokens = self.core.runner.step(entries, sample=True)
+        sampled = self.reader.read(tokens) if tokens is not None else []
+        return self.scheduler.update(pieces, sampled)
 
     def generate(self, prompts: Sequence[Sequence[int]],
                  params: Union[SamplingParams, Sequence[SamplingParams], None] = None) -> List[List[int]]:

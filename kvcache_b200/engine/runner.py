@@ -5,12 +5,19 @@ The reference has two forwards - a whole prompt of one sequence
 and rebuilds and copies five metadata arrays per step (:129-147).  Here one
 `step` takes any mix of prompt portions and single decoded tokens, cut anywhere,
 packs the step's metadata into one host buffer, copies it once, runs only the rows
-it was given and returns float32 logits at the wanted places.
+it was given and returns float32 logits at the wanted places (and, if asked, the
+tokens sampled from them on the device).
+
+A step in which every request brings exactly one token and wants its logits is
+replayed from a CUDA graph captured for that batch size, as the reference's
+qwen_infer captures its one-token forward (apps/qwen_infer.cu:135-208); what
+changes between replays - ids, positions, block tables, sampling parameters -
+lies in the metadata buffer at fixed addresses.
 """
 from __future__ import annotations
 
 from dataclasses import dataclass
-from typing import List, Optional, Sequence, Tuple
+from typing import Dict, List, Optional, Sequence, Tuple
 
 import numpy as np
 import torch
@@ -23,11 +30,13 @@ from .workspace import Workspace
 
 @dataclass
 class StepEntry:
-    """One request's share of a step: its slot, its next tokens, and the places among
-    these tokens whose logits are wanted."""
+    """One request's share of a step: its slot, its next tokens, the places among these
+    tokens whose logits are wanted, and how tokens are sampled at those places
+    (temperature, seed, tokens sampled so far); None samples greedily."""
     slot: int
     tokens: Sequence[int]
     want: Sequence[int] = ()
+    sampling: Optional[Tuple[float, int, int]] = None
 
 
 def _align4(n: int) -> int:
@@ -37,13 +46,18 @@ def _align4(n: int) -> int:
 class StepLayout:
     """Where each array of a step's metadata lies in the packed int32 buffer."""
 
+    SECTIONS = (("token_ids", "T", 1), ("positions", "T", 1), ("row_segment", "T", 1), ("seg_q_start", "S", 1),
+                ("seg_q_len", "S", 1), ("seg_kv_len", "S", 1), ("seg_slot", "S", 1), ("wanted_rows", "R", 1),
+                ("sample_temperature", "R", 1), ("sample_counter", "R", 1), ("sample_seed", "R", 2))
+
     def __init__(self, T: int, S: int, R: int, table_width: int, num_groups: int):
         self.T, self.S, self.R = T, S, R
         self.table_width, self.num_groups = table_width, num_groups
+        sizes = {"T": T, "S": S, "R": R}
         offset = 0
         self.offsets = {}
-        for name, count in (("token_ids", T), ("positions", T), ("row_segment", T), ("seg_q_start", S),
-                            ("seg_q_len", S), ("seg_kv_len", S), ("seg_slot", S), ("wanted_rows", R)):
+        for name, dim, words in self.SECTIONS:
+            count = sizes[dim] * words
             self.offsets[name] = (offset, count)
             offset += _align4(count)
         self.table_offsets = []
@@ -58,28 +72,40 @@ class StepLayout:
 
     def table(self, buf, group: int):
         begin = self.table_offsets[group]
-        return buf[begin:begin + self.S * self.table_width].view(self.S, self.table_width) \
-            if isinstance(buf, torch.Tensor) else buf[begin:begin + self.S * self.table_width].reshape(self.S, self.table_width)
+        flat = buf[begin:begin + self.S * self.table_width]
+        return flat.view(self.S, self.table_width) if isinstance(flat, torch.Tensor) else flat.reshape(self.S, self.table_width)
+
+
+class _DecodeGraph:
+    def __init__(self, graph, logits, tokens, launches):
+        self.graph, self.logits, self.tokens, self.launches = graph, logits, tokens, launches
 
 
 class ModelRunner:
     def __init__(self, model: DecoderModel, cache: CacheManager, kernels, *, max_tokens_per_step: int,
-                 max_segments: Optional[int] = None):
+                 max_segments: Optional[int] = None, use_graphs: bool = False):
         self.model, self.cache, self.kernels = model, cache, kernels
         self.device = model.device
         self.max_tokens = max_tokens_per_step
         self.max_segments = max_segments or cache.max_slots
         self.workspace = Workspace(self.device)
+        self.graph_workspace = Workspace(self.device, row_capacity=self.max_segments)
         width = cache.max_pages_per_request
         groups = len(cache.groups)
         capacity = StepLayout(self.max_tokens, self.max_segments, self.max_tokens, width, groups).total
         self._meta_device = torch.zeros(capacity, dtype=torch.int32, device=self.device)
         self._on_cuda = self.device.type == "cuda"
+        self.use_graphs = use_graphs and self._on_cuda
         ring = 4 if self._on_cuda else 1
         self._staging = [torch.zeros(capacity, dtype=torch.int32, pin_memory=self._on_cuda) for _ in range(ring)]
         self._staging_events = [None] * ring
         self._ring = 0
+        self._graphs: Dict[int, _DecodeGraph] = {}
+        parts = kernels.sample_parts(model.vocab_size)
+        self._sample_parts = parts
         self.steps_run = 0
+        self.last_h2d_bytes = 0
+        self.graph_replays = 0
 
     # ---- metadata ----------------------------------------------------------
     def _next_staging(self):
@@ -90,7 +116,7 @@ class ModelRunner:
             event.synchronize()
         return i, self._staging[i]
 
-    def prepare(self, entries: Sequence[StepEntry]) -> Tuple[StepBatch, "object"]:
+    def prepare(self, entries: Sequence[StepEntry]):
         """Extends the cache for the entries, packs and uploads the step's metadata."""
         if not entries:
             raise ValueError("a step needs at least one entry")
@@ -115,23 +141,39 @@ class ModelRunner:
         starts_np = np.asarray(starts, dtype=np.int32)
         q_start = np.zeros(S, dtype=np.int32)
         np.cumsum(counts_np[:-1], out=q_start[1:])
-        layout.view(host, "token_ids")[:] = np.concatenate([np.asarray(e.tokens, dtype=np.int32) for e in entries])
-        row_segment = np.repeat(np.arange(S, dtype=np.int32), counts_np)
+        if T == S:                                   # one token per request: no concatenation needed
+            layout.view(host, "token_ids")[:] = [e.tokens[0] for e in entries]
+            row_segment = np.arange(S, dtype=np.int32)
+            layout.view(host, "positions")[:] = starts_np
+        else:
+            layout.view(host, "token_ids")[:] = np.concatenate([np.asarray(e.tokens, dtype=np.int32) for e in entries])
+            row_segment = np.repeat(np.arange(S, dtype=np.int32), counts_np)
+            layout.view(host, "positions")[:] = np.arange(T, dtype=np.int32) - q_start[row_segment] + starts_np[row_segment]
         layout.view(host, "row_segment")[:] = row_segment
-        layout.view(host, "positions")[:] = np.arange(T, dtype=np.int32) - q_start[row_segment] + starts_np[row_segment]
         layout.view(host, "seg_q_start")[:] = q_start
         layout.view(host, "seg_q_len")[:] = counts_np
         layout.view(host, "seg_kv_len")[:] = starts_np + counts_np
         slots = [e.slot for e in entries]
-        layout.view(host, "seg_slot")[:] = np.asarray(slots, dtype=np.int32)
+        layout.view(host, "seg_slot")[:] = slots
         if R:
-            layout.view(host, "wanted_rows")[:] = np.concatenate(
-                [q_start[i] + np.asarray(e.want, dtype=np.int32) for i, e in enumerate(entries) if len(e.want)])
+            wanted, temps, counters, seeds = [], [], [], []
+            for i, e in enumerate(entries):
+                for w in e.want:
+                    wanted.append(q_start[i] + w)
+                    t, seed, counter = e.sampling if e.sampling is not None else (0.0, 0, 0)
+                    temps.append(t)
+                    counters.append(counter)
+                    seeds.append(seed & 0x7FFFFFFFFFFFFFFF)
+            layout.view(host, "wanted_rows")[:] = wanted
+            layout.view(host, "sample_temperature").view(np.float32)[:] = temps
+            layout.view(host, "sample_counter")[:] = counters
+            layout.view(host, "sample_seed").view(np.int64)[:] = seeds
         for g in range(len(self.cache.groups)):
             layout.table(host, g)[:] = self.cache.table_rows(g, slots)
 
         dev = self._meta_device
         dev[:layout.total].copy_(staging[:layout.total], non_blocking=True)
+        self.last_h2d_bytes = layout.total * 4
         if self._on_cuda:
             event = torch.cuda.Event()
             event.record()
@@ -145,14 +187,62 @@ class ModelRunner:
             max_q_len=int(counts_np.max()), max_kv_len=int((starts_np + counts_np).max()),
             host={"counts": counts_np, "starts": starts_np, "q_start": q_start, "slots": slots})
         view = self.cache.step_view([layout.table(dev, g) for g in range(len(self.cache.groups))])
-        return batch, view
+        return batch, view, layout
 
     # ---- the step ----------------------------------------------------------
-    def step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
-        """Runs the entries as one batch; returns float32 logits [wanted places, vocab] in the
-        order of the entries and of their `want` lists.  The tensor is a view of a buffer
-        the next step overwrites."""
-        batch, view = self.prepare(entries)
-        logits = self.model.forward(batch, self.kernels, self.workspace, view)
+    def _sample(self, logits: torch.Tensor, layout: StepLayout, workspace: Workspace) -> torch.Tensor:
+        R = logits.shape[0]
+        dev = self._meta_device
+        tokens = workspace.buffer("sample.tokens", (R,), torch.int32)
+        self.kernels.sample(logits, layout.view(dev, "sample_temperature").view(torch.float32),
+                            layout.view(dev, "sample_seed").view(torch.int64), layout.view(dev, "sample_counter"), tokens,
+                            workspace.buffer("sample.part_val", (R * self._sample_parts,), torch.float32),
+                            workspace.buffer("sample.part_idx", (R * self._sample_parts,), torch.int32))
+        return tokens
+
+    def _forward(self, batch, view, layout, workspace, sample: bool):
+        logits = self.model.forward(batch, self.kernels, workspace, view)
+        tokens = self._sample(logits, layout, workspace) if sample and batch.num_wanted else None
+        return logits, tokens
+
+    def _decode_graph(self, batch, view, layout) -> _DecodeGraph:
+        B = batch.num_tokens
+        found = self._graphs.get(B)
+        if found is not None:
+            return found
+        ws = self.graph_workspace
+        self._forward(batch, view, layout, ws, True)          # sizes the buffers; writes what the replay rewrites
+        torch.cuda.synchronize(self.device)
+        graph = torch.cuda.CUDAGraph()
+        before = self.kernels.launches
+        ws.frozen = True
+        try:
+            with torch.cuda.graph(graph):
+                logits, tokens = self._forward(batch, view, layout, ws, True)
+        finally:
+            ws.frozen = False
+        found = _DecodeGraph(graph, logits, tokens, self.kernels.launches - before)
+        self._graphs[B] = found
+        return found
+
+    def step(self, entries: Sequence[StepEntry], sample: bool = False, token_source: Optional[torch.Tensor] = None):
+        """Runs the entries as one batch.  Returns float32 logits [wanted places, vocab] in the
+        order of the entries and of their `want` lists - or, with `sample`, the pair
+        (logits, int32 tokens sampled at those places, on the device).  The tensors are
+        views of buffers the next step overwrites.  `token_source`: a device tensor of this
+        step's token ids that replaces the ids of the entries (tokens the previous step
+        sampled, which the host has not read yet)."""
+        batch, view, layout = self.prepare(entries)
+        if token_source is not None:
+            batch.token_ids.copy_(token_source[:batch.num_tokens], non_blocking=True)
+        decode_only = sample and self.use_graphs and batch.num_tokens == batch.num_segments == batch.num_wanted
+        if decode_only:
+            found = self._decode_graph(batch, view, layout)
+            found.graph.replay()
+            self.kernels.launches += found.launches
+            self.graph_replays += 1
+            logits, tokens = found.logits, found.tokens
+        else:
+            logits, tokens = self._forward(batch, view, layout, self.workspace, sample)
         self.steps_run += 1
-        return logits
+        return (logits, tokens) if sample else logits

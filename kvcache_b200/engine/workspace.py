@@ -10,8 +10,11 @@ import torch
 
 
 class Workspace:
-    def __init__(self, device: torch.device | str):
+    def __init__(self, device: torch.device | str, row_capacity: int = 0):
+        """`row_capacity`: buffers whose first dimension is at most this many rows are made
+        for that many rows at once, so they never move afterwards."""
         self.device = torch.device(device)
+        self.row_capacity = row_capacity
         self._buffers: Dict[str, torch.Tensor] = {}
         self.frozen = False   # set while a CUDA graph is captured or replayed: growing is an error
 
@@ -25,6 +28,8 @@ class Workspace:
                 raise RuntimeError(f"workspace buffer '{name}' would have to grow to {count} elements "
                                    f"while its addresses are pinned by a CUDA graph")
             capacity = max(count, 1)
+            if shape and 0 < int(shape[0]) <= self.row_capacity:
+                capacity = max(capacity, count // int(shape[0]) * self.row_capacity)
             if buf is not None and buf.dtype == dtype:
                 capacity = max(capacity, buf.numel())
             buf = torch.empty(capacity, dtype=dtype, device=self.device)
