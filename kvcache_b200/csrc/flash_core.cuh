@@ -1,0 +1,218 @@
+// Warp-level core of the bfloat16 attention kernels over cache pages: a warp owns 16 query
+// rows, keys and values arrive in shared memory 64 keys at a time (cp.async, rows padded by
+// 16 bytes so that ldmatrix is free of bank conflicts for every head size), scores and the
+// weighted sum run on the tensor cores (mma.sync m16n8k16, float32 accumulators), and the
+// softmax is the running (max, sum, acc) form of the reference
+// (src/qwen_kernels.cu:159-176; split merge src/flash_decode.cu:82-101), in base 2.
+//
+// Compiled once per head size: KVB_HEAD_DIM is given on the command line (a multiple of 16,
+// at most 128; larger heads use the generic kernel).
+#pragma once
+#include "common.cuh"
+
+#ifndef KVB_HEAD_DIM
+#error "compile with -DKVB_HEAD_DIM=<head size>"
+#endif
+
+namespace flash {
+
+constexpr int D = KVB_HEAD_DIM;
+static_assert(D % 16 == 0 && D >= 16 && D <= 128, "head sizes 16..128 in steps of 16");
+constexpr int CHUNKS = D / 8;        // 16-byte chunks in a row
+constexpr int STRIDE = D + 8;        // elements between rows in shared memory (one chunk of padding)
+constexpr int KT = 64;               // keys in a tile
+constexpr int KS = D / 16;           // k-steps of Q.K^T
+constexpr int NT_O = D / 8;          // 8-wide column tiles of the output
+constexpr int TILE_ELEMS = KT * STRIDE;
+constexpr float NEG_INF = -INFINITY;
+
+__device__ __forceinline__ uint32_t smem_addr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void cp_async16(void* smem, const void* gmem, bool valid) {
+    const int bytes = valid ? 16 : 0;   // 0 source bytes: the 16 destination bytes are zero-filled
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(smem_addr(smem)), "l"(gmem), "r"(bytes));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
+
+__device__ __forceinline__ void ldmatrix_x4(uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3, const void* p) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(smem_addr(p)));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3, const void* p) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(smem_addr(p)));
+}
+__device__ __forceinline__ void mma_bf16(float* c, const uint32_t* a, uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+
+// Where the keys of one (request, kv head) lie.
+struct KVSource {
+    const bf16* k_pages;
+    const bf16* v_pages;
+    const int* table;      // the request's row of the block table
+    int hk, Hkv, page_size, page_shift;
+};
+
+// Copies keys/values [key0, key0 + KT) into a stage; keys >= key_end (or before key_lo) are zero-filled.
+// Called by `nthreads` threads (a warp or a block), thread index `tid`.
+__device__ __forceinline__ void load_tile(bf16* ks, bf16* vs, const KVSource& src, int key0, int key_lo, int key_end,
+                                          int tid, int nthreads) {
+    for (int idx = tid; idx < KT * CHUNKS; idx += nthreads) {
+        const int row = idx / CHUNKS, c = idx - row * CHUNKS;
+        const int j = key0 + row;
+        const bool valid = j >= key_lo && j < key_end;
+        size_t off = 0;
+        if (valid) {
+            const int page = __ldg(src.table + (j >> src.page_shift));
+            off = (((size_t)page * src.Hkv + src.hk) * src.page_size + (j & (src.page_size - 1))) * D + c * 8;
+        }
+        cp_async16(ks + row * STRIDE + c * 8, src.k_pages + off, valid);
+        cp_async16(vs + row * STRIDE + c * 8, src.v_pages + off, valid);
+    }
+}
+
+// The 16 query rows of a warp.
+struct WarpRows {
+    uint32_t q[KS][4];     // A fragments of Q
+    float o[NT_O][4];      // output accumulators: [.][0..1] row g, [.][2..3] row g + 8
+    float m[2], l[2];      // running maximum (base-2 units) and this thread's share of the running sum
+    int pos[2];            // absolute position of rows g and g + 8 (-1: the row does not exist)
+};
+
+__device__ __forceinline__ void rows_init(WarpRows& w) {
+#pragma unroll
+    for (int i = 0; i < NT_O; ++i) w.o[i][0] = w.o[i][1] = w.o[i][2] = w.o[i][3] = 0.f;
+    w.m[0] = w.m[1] = NEG_INF;
+    w.l[0] = w.l[1] = 0.f;
+}
+
+// Loads the Q fragments: `row_ptr(r)` gives the global address of row r's D elements, or nullptr.
+template <typename RowPtr>
+__device__ __forceinline__ void rows_load_q(WarpRows& w, RowPtr row_ptr) {
+    const int lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+    const bf16* r0 = row_ptr(g);
+    const bf16* r1 = row_ptr(g + 8);
+#pragma unroll
+    for (int ks = 0; ks < KS; ++ks) {
+        const int d = ks * 16 + 2 * t;
+        w.q[ks][0] = r0 ? *reinterpret_cast<const uint32_t*>(r0 + d) : 0u;
+        w.q[ks][1] = r1 ? *reinterpret_cast<const uint32_t*>(r1 + d) : 0u;
+        w.q[ks][2] = r0 ? *reinterpret_cast<const uint32_t*>(r0 + d + 8) : 0u;
+        w.q[ks][3] = r1 ? *reinterpret_cast<const uint32_t*>(r1 + d + 8) : 0u;
+    }
+}
+
+// One tile of keys [key0, key0 + KT) from a stage: scores, masking, running softmax, weighted sum.
+// A key j is seen by a row at position p iff key_lo(p) <= j <= p, key_lo(p) = max(0, p - window + 1).
+__device__ __forceinline__ void rows_tile(WarpRows& w, const bf16* ks, const bf16* vs, int key0, int window,
+                                          float scale_log2) {
+    const int lane = threadIdx.x & 31, t = lane & 3;
+    float s[KT / 8][4];
+#pragma unroll
+    for (int i = 0; i < KT / 8; ++i) s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f;
+    {
+        const int mi = lane >> 3, key_off = (mi >> 1) * 8 + (lane & 7), d_off = (mi & 1) * 8;
+#pragma unroll
+        for (int k = 0; k < KS; ++k) {
+#pragma unroll
+            for (int n2 = 0; n2 < KT / 16; ++n2) {
+                uint32_t b0, b1, b2, b3;
+                ldmatrix_x4(b0, b1, b2, b3, ks + (n2 * 16 + key_off) * STRIDE + k * 16 + d_off);
+                mma_bf16(s[2 * n2], w.q[k], b0, b1);
+                mma_bf16(s[2 * n2 + 1], w.q[k], b2, b3);
+            }
+        }
+    }
+    // Scale, mask, row maxima.
+    float mx[2] = {NEG_INF, NEG_INF};
+#pragma unroll
+    for (int n = 0; n < KT / 8; ++n) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const int r = e >> 1;
+            const int j = key0 + n * 8 + 2 * t + (e & 1);
+            const int p = w.pos[r];
+            const bool seen = j <= p && (window <= 0 || j > p - window);
+            const float v = seen ? s[n][e] * scale_log2 : NEG_INF;
+            s[n][e] = v;
+            mx[r] = fmaxf(mx[r], v);
+        }
+    }
+    float corr[2], base[2];
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
+        mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
+        const float m_new = fmaxf(w.m[r], mx[r]);
+        base[r] = m_new == NEG_INF ? 0.f : m_new;
+        corr[r] = exp2f(w.m[r] - base[r]);
+        w.m[r] = m_new;
+        w.l[r] *= corr[r];
+    }
+#pragma unroll
+    for (int n = 0; n < KT / 8; ++n) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const float p = exp2f(s[n][e] - base[e >> 1]);
+            s[n][e] = p;
+            w.l[e >> 1] += p;
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < NT_O; ++i) {
+        w.o[i][0] *= corr[0]; w.o[i][1] *= corr[0];
+        w.o[i][2] *= corr[1]; w.o[i][3] *= corr[1];
+    }
+    {
+        const int mi = lane >> 3, key_off = (mi & 1) * 8 + (lane & 7), d_off = (mi >> 1) * 8;
+#pragma unroll
+        for (int kk = 0; kk < KT / 16; ++kk) {
+            uint32_t pa[4];
+            pa[0] = pack_bf16(s[2 * kk][0], s[2 * kk][1]);
+            pa[1] = pack_bf16(s[2 * kk][2], s[2 * kk][3]);
+            pa[2] = pack_bf16(s[2 * kk + 1][0], s[2 * kk + 1][1]);
+            pa[3] = pack_bf16(s[2 * kk + 1][2], s[2 * kk + 1][3]);
+#pragma unroll
+            for (int n2 = 0; n2 < NT_O / 2; ++n2) {
+                uint32_t b0, b1, b2, b3;
+                ldmatrix_x4_trans(b0, b1, b2, b3, vs + (kk * 16 + key_off) * STRIDE + n2 * 16 + d_off);
+                mma_bf16(w.o[2 * n2], pa, b0, b1);
+                mma_bf16(w.o[2 * n2 + 1], pa, b2, b3);
+            }
+        }
+    }
+}
+
+// Sums each row's l over the four threads that share it.
+__device__ __forceinline__ void rows_finish_sum(WarpRows& w) {
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        w.l[r] += __shfl_xor_sync(0xffffffffu, w.l[r], 1);
+        w.l[r] += __shfl_xor_sync(0xffffffffu, w.l[r], 2);
+    }
+}
+
+// Writes normalised rows: `row_ptr(r)` gives the output address of row r or nullptr.
+template <typename RowPtr>
+__device__ __forceinline__ void rows_store(const WarpRows& w, RowPtr row_ptr) {
+    const int lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        bf16* out = row_ptr(g + 8 * r);
+        if (!out) continue;
+        const float inv = w.l[r] > 0.f ? 1.f / w.l[r] : 0.f;
+#pragma unroll
+        for (int i = 0; i < NT_O; ++i)
+            *reinterpret_cast<uint32_t*>(out + i * 8 + 2 * t) = pack_bf16(w.o[i][2 * r] * inv, w.o[i][2 * r + 1] * inv);
+    }
+}
+
+}  // namespace flash

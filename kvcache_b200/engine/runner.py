@@ -48,12 +48,14 @@ class StepLayout:
 
     SECTIONS = (("token_ids", "T", 1), ("positions", "T", 1), ("row_segment", "T", 1), ("seg_q_start", "S", 1),
                 ("seg_q_len", "S", 1), ("seg_kv_len", "S", 1), ("seg_slot", "S", 1), ("wanted_rows", "R", 1),
-                ("sample_temperature", "R", 1), ("sample_counter", "R", 1), ("sample_seed", "R", 2))
+                ("sample_temperature", "R", 1), ("sample_counter", "R", 1), ("sample_seed", "R", 2),
+                ("decode_items", "S", 1), ("prefill_tiles", "TILES", 2))
+    TILE_ROWS = 64
 
     def __init__(self, T: int, S: int, R: int, table_width: int, num_groups: int):
         self.T, self.S, self.R = T, S, R
         self.table_width, self.num_groups = table_width, num_groups
-        sizes = {"T": T, "S": S, "R": R}
+        sizes = {"T": T, "S": S, "R": R, "TILES": T // self.TILE_ROWS + S}
         offset = 0
         self.offsets = {}
         for name, dim, words in self.SECTIONS:
@@ -170,6 +172,18 @@ class ModelRunner:
             layout.view(host, "sample_seed").view(np.int64)[:] = seeds
         for g in range(len(self.cache.groups)):
             layout.table(host, g)[:] = self.cache.table_rows(g, slots)
+        if T == S:
+            n_items, n_tiles = S, 0
+            layout.view(host, "decode_items")[:] = row_segment
+        else:
+            single = counts_np == 1
+            items = np.nonzero(single)[0].astype(np.int32)
+            n_items = len(items)
+            layout.view(host, "decode_items")[:n_items] = items
+            tiles = [(i, r) for i in np.nonzero(~single)[0] for r in range(0, counts[i], StepLayout.TILE_ROWS)]
+            n_tiles = len(tiles)
+            if n_tiles:
+                layout.view(host, "prefill_tiles")[:2 * n_tiles] = np.asarray(tiles, dtype=np.int32).reshape(-1)
 
         dev = self._meta_device
         dev[:layout.total].copy_(staging[:layout.total], non_blocking=True)
@@ -184,6 +198,8 @@ class ModelRunner:
             row_segment=layout.view(dev, "row_segment"), seg_q_start=layout.view(dev, "seg_q_start"),
             seg_q_len=layout.view(dev, "seg_q_len"), seg_kv_len=layout.view(dev, "seg_kv_len"),
             seg_slot=layout.view(dev, "seg_slot"), wanted_rows=layout.view(dev, "wanted_rows"),
+            decode_items=layout.view(dev, "decode_items")[:n_items], num_decode_items=n_items,
+            prefill_tiles=layout.view(dev, "prefill_tiles")[:2 * n_tiles].view(-1, 2), num_prefill_tiles=n_tiles,
             max_q_len=int(counts_np.max()), max_kv_len=int((starts_np + counts_np).max()),
             host={"counts": counts_np, "starts": starts_np, "q_start": q_start, "slots": slots})
         view = self.cache.step_view([layout.table(dev, g) for g in range(len(self.cache.groups))])
@@ -211,7 +227,10 @@ class ModelRunner:
         if found is not None:
             return found
         ws = self.graph_workspace
+        moved = ws.moved
         self._forward(batch, view, layout, ws, True)          # sizes the buffers; writes what the replay rewrites
+        if ws.moved != moved:
+            self._graphs.clear()                              # a buffer moved: graphs that hold its old address go
         torch.cuda.synchronize(self.device)
         graph = torch.cuda.CUDAGraph()
         before = self.kernels.launches

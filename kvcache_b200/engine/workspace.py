@@ -16,6 +16,7 @@ class Workspace:
         self.device = torch.device(device)
         self.row_capacity = row_capacity
         self._buffers: Dict[str, torch.Tensor] = {}
+        self.moved = 0        # how many times an existing buffer was replaced by a larger one
         self.frozen = False   # set while a CUDA graph is captured or replayed: growing is an error
 
     def buffer(self, name: str, shape: Tuple[int, ...], dtype: torch.dtype) -> torch.Tensor:
@@ -32,9 +33,22 @@ class Workspace:
                 capacity = max(capacity, count // int(shape[0]) * self.row_capacity)
             if buf is not None and buf.dtype == dtype:
                 capacity = max(capacity, buf.numel())
+            if buf is not None:
+                self.moved += 1
             buf = torch.empty(capacity, dtype=dtype, device=self.device)
             self._buffers[name] = buf
         return buf[:count].view(shape)
+
+    def zeros(self, name: str, shape: Tuple[int, ...], dtype: torch.dtype) -> torch.Tensor:
+        """Like `buffer`, but zero when first made (or remade); its users leave it zero."""
+        count = 1
+        for s in shape:
+            count *= int(s)
+        before = self._buffers.get(name)
+        view = self.buffer(name, shape, dtype)
+        if self._buffers[name] is not before:
+            self._buffers[name].zero_()
+        return view
 
     def bytes(self) -> int:
         return sum(b.numel() * b.element_size() for b in self._buffers.values())

@@ -9,7 +9,7 @@ package; `CudaKernels` raises if the device or the compiler is missing.
 from __future__ import annotations
 
 import ctypes
-from typing import Optional
+from typing import Dict, Optional, Sequence
 
 import torch
 
@@ -94,6 +94,14 @@ _SIGNATURES = {
     "gemm_simt": {
         "kvb_gemm_simt": [_c_int, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_void_p],
     },
+    "attention_flash": {
+        "kvb_flash_head_dim": [],
+        "kvb_flash_decode": [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_int, _c_void_p,
+                             _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float,
+                             _c_void_p],
+        "kvb_flash_prefill": [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_int, _c_void_p,
+                              _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_float, _c_void_p],
+    },
     "sampling": {
         "kvb_sample_parts": [_c_int],
         "kvb_sample": [_c_void_p, _c_int, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p],
@@ -104,13 +112,13 @@ _SIGNATURES = {
 class _Library:
     """A lazily built and loaded kernel module with typed entry points."""
 
-    def __init__(self, module: str):
-        self.module = module
+    def __init__(self, module: str, variant: str = "", flags: Sequence[str] = ()):
+        self.module, self.variant, self.flags = module, variant, tuple(flags)
         self._lib = None
 
     def __getattr__(self, name: str):
         if self._lib is None:
-            lib = build.load_module(self.module)
+            lib = build.load_module(self.module, self.variant, self.flags)
             for fname, argtypes in _SIGNATURES[self.module].items():
                 fn = getattr(lib, fname)
                 fn.argtypes = argtypes
@@ -135,6 +143,9 @@ class CudaKernels(KernelSet):
         self._attn_generic = _Library("attention_generic")
         self._gemm_simt = _Library("gemm_simt")
         self._sampling = _Library("sampling")
+        self._flash: Dict[int, _Library] = {}
+        self.flash_attention = True          # bfloat16, head sizes 16..128: tensor-core kernels
+        self.decode_ctas_wanted = 148 * 4    # the split over the keys aims at this many warps in flight
         self.error_word = torch.zeros(1, dtype=torch.int32, device=self.device)
         self.launches = 0
 
@@ -202,10 +213,40 @@ class CudaKernels(KernelSet):
             _ptr(kv.k_pages), _ptr(kv.v_pages), _ptr(q_out), T, num_heads, spec.num_kv_heads, spec.head_dim,
             kv.page_size, 1 if kv.writes else 0, _ptr(self.error_word), self._stream()), "qkv_rope_append")
 
+    def _flash_library(self, head_dim: int) -> _Library:
+        lib = self._flash.get(head_dim)
+        if lib is None:
+            lib = _Library("attention_flash", f"d{head_dim}", [f"-DKVB_HEAD_DIM={head_dim}"])
+            self._flash[head_dim] = lib
+        return lib
+
     def paged_attention(self, q: torch.Tensor, batch: StepBatch, kv: PagedKVView, out: torch.Tensor,
-                        num_heads: int, scale: float) -> None:
+                        num_heads: int, scale: float, workspace=None) -> None:
         T = q.shape[0]
         spec = kv.spec
+        D, Hkv = spec.head_dim, spec.num_kv_heads
+        if (self.flash_attention and q.dtype == torch.bfloat16 and D % 16 == 0 and D <= 128 and num_heads // Hkv <= 16
+                and workspace is not None and batch.decode_items is not None):
+            lib = self._flash_library(D)
+            if batch.num_prefill_tiles:
+                self.launches += 1
+                _check(lib.kvb_flash_prefill(
+                    _ptr(q), _ptr(out), _ptr(kv.k_pages), _ptr(kv.v_pages), _ptr(kv.block_table), kv.block_table.shape[1],
+                    _ptr(batch.prefill_tiles), batch.num_prefill_tiles, _ptr(batch.seg_q_start), _ptr(batch.seg_q_len),
+                    _ptr(batch.seg_kv_len), num_heads, Hkv, kv.page_size, spec.window or 0, float(scale), self._stream()),
+                    "flash_prefill")
+            n = batch.num_decode_items
+            if n:
+                nsplit = max(1, min(32, -(-self.decode_ctas_wanted // (n * Hkv))))
+                scratch = workspace.buffer("attn.decode_scratch", (n * Hkv * nsplit * 16 * (D + 2),), torch.float32)
+                tickets = workspace.zeros("attn.decode_tickets", (n * Hkv,), torch.int32)
+                self.launches += 1
+                _check(lib.kvb_flash_decode(
+                    _ptr(q), _ptr(out), _ptr(kv.k_pages), _ptr(kv.v_pages), _ptr(kv.block_table), kv.block_table.shape[1],
+                    _ptr(batch.decode_items), n, _ptr(batch.seg_q_start), _ptr(batch.seg_q_len), _ptr(batch.seg_kv_len),
+                    _ptr(scratch), _ptr(tickets), num_heads, Hkv, kv.page_size, spec.window or 0, nsplit, float(scale),
+                    self._stream()), "flash_decode")
+            return
         self.launches += 1
         _check(self._attn_generic.kvb_paged_attention_generic(
             _dtype_code(q.dtype), _ptr(q), _ptr(kv.k_pages), _ptr(kv.v_pages), _ptr(kv.block_table),

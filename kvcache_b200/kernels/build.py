@@ -31,7 +31,11 @@ MODULES: Dict[str, dict] = {
     "attention_generic": {"src": "attention_generic.cu", "deps": ["common.cuh"]},
     "gemm_simt": {"src": "gemm_simt.cu", "deps": ["common.cuh"]},
     "sampling": {"src": "sampling.cu", "deps": ["common.cuh"]},
+    # Compiled per head size: variant "d<head_dim>" with -DKVB_HEAD_DIM=<head_dim>.
+    "attention_flash": {"src": "attention_flash.cu", "deps": ["common.cuh", "flash_core.cuh"]},
 }
+# Variants that `build_all` makes for modules compiled per size.
+DEFAULT_VARIANTS = {"attention_flash": [("d64", ["-DKVB_HEAD_DIM=64"]), ("d128", ["-DKVB_HEAD_DIM=128"])]}
 
 _loaded: Dict[str, ctypes.CDLL] = {}
 _lock = threading.Lock()
@@ -166,6 +170,10 @@ def build_all(modules: Optional[Iterable[str]] = None, jobs: int = 0) -> List[st
     """Compiles every module (in parallel) without loading any; returns the libraries' paths."""
     from concurrent.futures import ThreadPoolExecutor
     names = list(modules) if modules is not None else list(MODULES)
-    jobs = jobs or min(len(names), os.cpu_count() or 1)
+    work = []
+    for name in names:
+        for variant, flags in DEFAULT_VARIANTS.get(name, [("", [])]):
+            work.append((name, variant, tuple(flags)))
+    jobs = jobs or min(len(work), os.cpu_count() or 1)
     with ThreadPoolExecutor(max_workers=max(1, jobs)) as pool:
-        return list(pool.map(compile_module, names))
+        return list(pool.map(lambda w: compile_module(*w), work))

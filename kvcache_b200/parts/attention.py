@@ -75,7 +75,7 @@ class GQAAttention(Mixer):
         k.qkv_rope_append(qkv, self.b_qkv, rotation.cos if rotation else None, rotation.sin if rotation else None,
                           ctx.batch, ctx.kv, q, self.num_heads)
         attn = ws.buffer("attn.out", (T, self.q_size), self.dtype)
-        k.paged_attention(q, ctx.batch, ctx.kv, attn, self.num_heads, self.scale)
+        k.paged_attention(q, ctx.batch, ctx.kv, attn, self.num_heads, self.scale, ws)
         delta = ws.buffer("attn.delta", (T, self.hidden), self.dtype)
         k.linear(attn, self.w_o, delta)
         return delta

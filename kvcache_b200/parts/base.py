@@ -73,6 +73,12 @@ class StepBatch:
     seg_kv_len: torch.Tensor         # int32 [S]   tokens of the request cached after this step
     seg_slot: torch.Tensor           # int32 [S]   the request's state slot
     wanted_rows: torch.Tensor        # int32 [R]   rows whose logits are returned
+    # Attention work lists: segments that bring one token, and 64-row tiles (segment, first row)
+    # of the segments that bring more.
+    decode_items: Optional[torch.Tensor] = None    # int32 [num_decode_items]
+    prefill_tiles: Optional[torch.Tensor] = None   # int32 [num_prefill_tiles, 2]
+    num_decode_items: int = 0
+    num_prefill_tiles: int = 0
     max_q_len: int = 1               # host copies, for launch shapes
     max_kv_len: int = 1
     host: Dict[str, Any] = field(default_factory=dict)

@@ -165,6 +165,62 @@ def test_paged_attention_generic(kernels, dtype, scenario):
     kernels.check_errors()
 
 
+FLASH_SCENARIOS = SCENARIOS[:6] + [
+    ([(4000, 1), (64, 1), (63, 1), (0, 1), (129, 1)], 14, 2, 64, 16, None),     # decode only, split over the keys
+    ([(0, 200), (300, 130), (1000, 1)], 14, 2, 64, 16, None),                   # several tiles per segment
+    ([(0, 150), (700, 1), (90, 70)], 4, 4, 96, 8, 33),                          # window shorter than a key tile
+    ([(2500, 1), (100, 1)], 16, 1, 128, 64, 1000),                              # group of 16, large pages
+    ([(50, 3), (64, 2)], 2, 1, 112, 16, None),
+]
+
+
+@pytest.mark.parametrize("scenario", FLASH_SCENARIOS)
+def test_paged_attention_flash(kernels, scenario):
+    from kvcache_b200.engine.workspace import Workspace
+    segments, Hq, Hkv, D, page, window = scenario
+    dtype = torch.bfloat16
+    batch, kv = paged_scenario(segments, num_kv_heads=Hkv, head_dim=D, page_size=page, dtype=dtype, device="cpu",
+                               window=window, seed=12)
+    T = batch.num_tokens
+    q = torch.randn(T, Hq * D, generator=torch.Generator().manual_seed(13)).to(dtype)
+    ref = torch.empty(T, Hq * D, dtype=dtype)
+    REF.paged_attention(q, batch, kv, ref, Hq, D ** -0.5)
+    ws = Workspace(DEV)
+    for wanted in (148 * 4, 3, 100000):          # many splits, one split, as many as allowed
+        kernels.decode_ctas_wanted = wanted
+        out = torch.full((T, Hq * D), float("nan"), dtype=dtype, device=DEV)
+        kernels.paged_attention(q.to(DEV), batch_to(batch, DEV), clone_kv(kv, DEV), out, Hq, D ** -0.5, ws)
+        assert_close(out, ref, REL[dtype], f"decode_ctas_wanted={wanted}")
+    kernels.decode_ctas_wanted = 148 * 4
+    assert int(ws.buffer("attn.decode_tickets", (1,), torch.int32).sum()) == 0
+    kernels.check_errors()
+
+
+def test_flash_attention_sees_one_far_key_and_the_window_edge(kernels):
+    """bfloat16 tensor-core path: a single key that takes all the weight is found among
+    thousands (another page, another split); with a window it is seen at distance
+    window - 1 and not at distance window."""
+    from kvcache_b200.engine.workspace import Workspace
+    Hq, Hkv, D, page = 4, 2, 64, 16
+    ws = Workspace(DEV)
+    for cached, far, window, seen in [(3000, 1234, None, True), (3000, 3000 - 99, 100, True), (3000, 3000 - 100, 100, False)]:
+        batch, kv = paged_scenario([(cached, 1)], num_kv_heads=Hkv, head_dim=D, page_size=page, dtype=torch.bfloat16,
+                                   device="cpu", window=window, seed=14)
+        q = torch.randn(1, Hq * D, generator=torch.Generator().manual_seed(15)).to(torch.bfloat16)
+        p = int(kv.block_table[0, far // page])
+        for hk in range(Hkv):
+            qh = q.view(Hq, D)[hk * 2].float()
+            kv.k_pages[p, hk, far % page] = (60.0 * qh / qh.norm() ** 2).to(torch.bfloat16)
+            kv.v_pages[p, hk, far % page] = 7.0
+        out = torch.empty(1, Hq * D, dtype=torch.bfloat16, device=DEV)
+        kernels.paged_attention(q.to(DEV), batch_to(batch, DEV), clone_kv(kv, DEV), out, Hq, 1.0, ws)
+        ref = torch.empty(1, Hq * D, dtype=torch.bfloat16)
+        REF.paged_attention(q, batch, kv, ref, Hq, 1.0)
+        assert_close(out, ref, 1e-2)
+        got = out.view(Hq, D)[0].float().cpu()
+        assert ((got - 7.0).abs().max() < 0.1) == seen
+
+
 def test_attention_sees_one_far_key(kernels):
     """One key among hundreds, on another page, scaled so that it takes all the weight: the
     output must be that key's value."""

@@ -70,7 +70,7 @@ class TorchKernels:
             kv.k_pages[page, :, slot, :] = x[:, Hq:Hq + Hkv, :].to(kv.k_pages.dtype)
             kv.v_pages[page, :, slot, :] = x[:, Hq + Hkv:, :].to(kv.v_pages.dtype)
 
-    def paged_attention(self, q, batch, kv, out, num_heads, scale):
+    def paged_attention(self, q, batch, kv, out, num_heads, scale, workspace=None):
         f = self.f
         T = q.shape[0]
         Hq, Hkv, D = num_heads, kv.spec.num_kv_heads, kv.spec.head_dim
