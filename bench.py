@@ -225,6 +225,8 @@ def main() -> int:
     parser.add_argument("--batch", type=int, default=8)
     parser.add_argument("--skip-e2e", action="store_true")
     parser.add_argument("--skip-points", action="store_true")
+    parser.add_argument("--skip-prefill", action="store_true")
+    parser.add_argument("--no-graphs", action="store_true", help="launch the decode step's kernels one by one (for profilers)")
     args = parser.parse_args()
 
     if args.impl == "reference":
@@ -242,13 +244,14 @@ def main() -> int:
         folder = make_folder(tmp, args.layers)
         sampler = ClockSampler()
         sampler.start()
-        main_run = time_decode(folder, args.batch, CONTEXT, args.steps, args.warmup)
+        main_run = time_decode(folder, args.batch, CONTEXT, args.steps, args.warmup, use_graphs=not args.no_graphs)
         clocks = sampler.stop()
         points = {}
         if not args.skip_points:
             for b in (1, 64):
                 points[f"decode_b{b}"] = round(time_decode(folder, b, CONTEXT, args.steps, args.warmup)["tok_s"], 1)
-        prefill = time_prefill(folder, PREFILL_TOKENS, args.layers)
+        prefill = {"ms": float("nan"), "tok_s": float("nan"), "flops": float("nan")} if args.skip_prefill else \
+            time_prefill(folder, PREFILL_TOKENS, args.layers)
         e2e = None if args.skip_e2e else time_e2e(folder, args.batch, CONTEXT, args.steps, args.warmup)
 
     achieved = main_run["bytes_per_step"] / (main_run["ms_per_step"] / 1e3) / 1e9

@@ -14,11 +14,13 @@ using namespace flash;
 #define PREFILL_STAGES 2
 
 // ---------------------------------------------------------------------------------------------
-// Decode: one warp per (item, kv head, split).  An item is a segment whose rows * group <= 16:
-// row r of the warp is query (r / G) of the segment, head hk * G + r % G, so keys and values
-// are read once for all heads that share them.  Each split scans a range of key tiles and
-// leaves (m, l, acc) in scratch; the last split to finish (a ticket counter per (item, kv head))
-// merges them in split order and resets the counter.
+// Decode: one block of four warps per (item, kv head, split).  An item is a segment whose
+// rows * group <= 16: row r is query (r / G) of the segment, head hk * G + r % G, so keys and
+// values are read once for all heads that share them.  The block scans a range of key tiles;
+// of every 64-key tile each warp takes 16 keys and keeps its own running (m, l, acc), the four
+// are merged through shared memory at the end.  With several splits the block leaves
+// (m, l, acc) in scratch and the last block to finish (a ticket counter per (item, kv head))
+// merges the splits in order and resets the counter.
 // ---------------------------------------------------------------------------------------------
 struct DecodeParams {
     const bf16* q;             // [T, Hq * D]
@@ -37,12 +39,15 @@ struct DecodeParams {
     float scale_log2;
 };
 
-__global__ void __launch_bounds__(32) flash_decode_kernel(const DecodeParams p) {
+constexpr int MAX_SPLITS = 32;
+
+__global__ void __launch_bounds__(128) flash_decode_kernel(const DecodeParams p) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     bf16* smem = reinterpret_cast<bf16*>(smem_raw);
+    __shared__ int ticket_s;
     const int split = blockIdx.x, hk = blockIdx.y, item = blockIdx.z;
     const int seg = p.items ? p.items[item] : item;
-    const int lane = threadIdx.x, g = lane >> 2, t = lane & 3;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
     const int G = p.Hq / p.Hkv;
     const int q_start = p.seg_q_start[seg], q_len = p.seg_q_len[seg], kv_len = p.seg_kv_len[seg];
     const int rows = q_len * G;
@@ -70,74 +75,123 @@ __global__ void __launch_bounds__(32) flash_decode_kernel(const DecodeParams p) 
     constexpr int STAGES = DECODE_STAGES;
 #pragma unroll
     for (int s = 0; s < STAGES - 1; ++s) {
-        if (s < n) load_tile(smem + (2 * s) * TILE_ELEMS, smem + (2 * s + 1) * TILE_ELEMS, src, (my_begin + s) * KT, key_lo, kv_len, lane, 32);
+        if (s < n) load_tile(smem + (2 * s) * TILE_ELEMS, smem + (2 * s + 1) * TILE_ELEMS, src, (my_begin + s) * KT, key_lo, kv_len);
         cp_async_commit();
     }
     for (int i = 0; i < n; ++i) {
         const int ahead = i + STAGES - 1;
         if (ahead < n) {
             const int s = ahead % STAGES;
-            load_tile(smem + (2 * s) * TILE_ELEMS, smem + (2 * s + 1) * TILE_ELEMS, src, (my_begin + ahead) * KT, key_lo, kv_len, lane, 32);
+            load_tile(smem + (2 * s) * TILE_ELEMS, smem + (2 * s + 1) * TILE_ELEMS, src, (my_begin + ahead) * KT, key_lo, kv_len);
         }
         cp_async_commit();
         cp_async_wait<STAGES - 1>();
-        __syncwarp();
+        __syncthreads();
         const int s = i % STAGES;
-        rows_tile(w, smem + (2 * s) * TILE_ELEMS, smem + (2 * s + 1) * TILE_ELEMS, (my_begin + i) * KT, p.window, p.scale_log2);
-        __syncwarp();
+        // Of every tile each warp takes 16 keys and keeps its own running (m, l, acc).  Rows that do not
+        // exist (beyond rows) have zero queries and are never stored, so only the positions of existing rows
+        // decide whether the keys need their mask.
+        {
+            const int key0 = (my_begin + i) * KT + warp * 16;
+            if (key0 < kv_len)
+                rows_tile_auto<16>(w, smem + (2 * s) * TILE_ELEMS + warp * 16 * STRIDE,
+                                   smem + (2 * s + 1) * TILE_ELEMS + warp * 16 * STRIDE, key0, p.window, p.scale_log2,
+                                   first_pos, kv_len - 1, true);
+        }
+        __syncthreads();
     }
     rows_finish_sum(w);
 
-    auto out_row = [&](int r) -> bf16* {
-        return r < rows ? p.out + ((size_t)(q_start + r / G) * p.Hq + hk * G + r % G) * D : nullptr;
-    };
-    if (n_valid == 1) {
-        rows_store(w, out_row);
-        return;
-    }
-    // Leave this split's partial result, then take a ticket.
-    const size_t slot = ((size_t)item * p.Hkv + hk) * p.nsplit;
-    float* po = p.part_o + (slot + split) * 16 * D;
-    float* pml = p.part_ml + (slot + split) * 16 * 2;
+    // The four warps' results meet in shared memory (the stages are free now).
+    float* wo = reinterpret_cast<float*>(smem_raw);            // [4][16][D]
+    float* wml = wo + 4 * 16 * D;                              // [4][16][2]
+    float* wgt = wml + 4 * 16 * 2;                             // [16][MAX_SPLITS] weights of the split merge
 #pragma unroll
     for (int r = 0; r < 2; ++r) {
         const int row = g + 8 * r;
 #pragma unroll
         for (int i = 0; i < NT_O; ++i)
-            *reinterpret_cast<float2*>(po + row * D + i * 8 + 2 * t) = make_float2(w.o[i][2 * r], w.o[i][2 * r + 1]);
-        if (t == 0) { pml[row * 2] = w.m[r]; pml[row * 2 + 1] = w.l[r]; }
+            *reinterpret_cast<float2*>(wo + (warp * 16 + row) * D + i * 8 + 2 * t) = make_float2(w.o[i][2 * r], w.o[i][2 * r + 1]);
+        if (t == 0) { wml[(warp * 16 + row) * 2] = w.m[r]; wml[(warp * 16 + row) * 2 + 1] = w.l[r]; }
     }
-    __threadfence();
-    __syncwarp();
-    int ticket = 0;
-    if (lane == 0) ticket = atomicAdd(p.tickets + item * p.Hkv + hk, 1);
-    ticket = __shfl_sync(0xffffffffu, ticket, 0);
-    if (ticket != n_valid - 1) return;
-    __threadfence();
-    if (lane == 0) p.tickets[item * p.Hkv + hk] = 0;
-    // Merge: lane s holds split s (nsplit <= 32).  M = max m_s; weight_s = 2^(m_s - M) / sum_s 2^(m_s - M) l_s;
-    // out = sum_s weight_s acc_s, added in split order.
-    for (int row = 0; row < rows; ++row) {
-        float ms = NEG_INF, ls = 0.f;
-        if (lane < n_valid) {
-            const float* ml = p.part_ml + ((slot + lane) * 16 + row) * 2;
-            ms = __ldcg(ml);
-            ls = __ldcg(ml + 1);
+    __syncthreads();
+    const size_t slot = ((size_t)item * p.Hkv + hk) * p.nsplit;
+    for (int idx = tid; idx < rows * D; idx += 128) {
+        const int row = idx / D, d = idx - row * D;
+        float M = NEG_INF;
+#pragma unroll
+        for (int x = 0; x < 4; ++x) M = fmaxf(M, wml[(x * 16 + row) * 2]);
+        const float base = M == NEG_INF ? 0.f : M;
+        float L = 0.f, acc = 0.f;
+#pragma unroll
+        for (int x = 0; x < 4; ++x) {
+            const float e = exp2f(wml[(x * 16 + row) * 2] - base);
+            L += e * wml[(x * 16 + row) * 2 + 1];
+            acc += e * wo[(x * 16 + row) * D + d];
         }
-        const float M = warp_max(ms);
-        const float e = exp2f(ms - (M == NEG_INF ? 0.f : M));
-        const float L = warp_sum(e * ls);
-        const float weight = L > 0.f ? e / L : 0.f;
-        bf16* o = out_row(row);
-        for (int d0 = 0; d0 < D; d0 += 32) {
-            const int d = d0 + lane;
-            float acc = 0.f;
-            for (int s = 0; s < n_valid; ++s) {
-                const float ws = __shfl_sync(0xffffffffu, weight, s);
-                if (d < D) acc += ws * __ldcg(p.part_o + ((slot + s) * 16 + row) * D + d);
+        if (n_valid == 1) {
+            p.out[((size_t)(q_start + row / G) * p.Hq + hk * G + row % G) * D + d] = __float2bfloat16_rn(L > 0.f ? acc / L : 0.f);
+        } else {
+            p.part_o[((slot + split) * 16 + row) * D + d] = acc;
+            if (d == 0) {
+                p.part_ml[((slot + split) * 16 + row) * 2] = M;
+                p.part_ml[((slot + split) * 16 + row) * 2 + 1] = L;
             }
-            if (d < D) o[d] = __float2bfloat16_rn(acc);
         }
+    }
+    if (n_valid == 1) return;
+
+    // Take a ticket; the last block of this (item, kv head) merges the splits.
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) ticket_s = atomicAdd(p.tickets + item * p.Hkv + hk, 1);
+    __syncthreads();
+    if (ticket_s != n_valid - 1) return;
+    __threadfence();
+    if (tid == 0) p.tickets[item * p.Hkv + hk] = 0;
+    // weight[row][s] = 2^(m_s - M) / sum_s 2^(m_s - M) l_s; out[row][d] = sum_s weight[row][s] acc_s[row][d],
+    // added in split order.  Loads are issued many at a time: this block is alone with their latency.
+    float* mls = wgt + 16 * MAX_SPLITS;                        // [16][MAX_SPLITS][2]
+    for (int idx = tid; idx < rows * n_valid; idx += 128) {
+        const int row = idx / n_valid, s = idx - row * n_valid;
+        const float2 ml = __ldcg(reinterpret_cast<const float2*>(p.part_ml + ((slot + s) * 16 + row) * 2));
+        mls[(row * MAX_SPLITS + s) * 2] = ml.x;
+        mls[(row * MAX_SPLITS + s) * 2 + 1] = ml.y;
+    }
+    __syncthreads();
+    if (tid < rows) {
+        const int row = tid;
+        float M = NEG_INF;
+        for (int s = 0; s < n_valid; ++s) M = fmaxf(M, mls[(row * MAX_SPLITS + s) * 2]);
+        const float base = M == NEG_INF ? 0.f : M;
+        float L = 0.f;
+        for (int s = 0; s < n_valid; ++s) {
+            const float e = exp2f(mls[(row * MAX_SPLITS + s) * 2] - base);
+            L += e * mls[(row * MAX_SPLITS + s) * 2 + 1];
+            wgt[row * MAX_SPLITS + s] = e;
+        }
+        const float inv = L > 0.f ? 1.f / L : 0.f;
+        for (int s = 0; s < n_valid; ++s) wgt[row * MAX_SPLITS + s] *= inv;
+    }
+    __syncthreads();
+    for (int idx = tid; idx < rows * (D / 4); idx += 128) {
+        const int row = idx / (D / 4), d = (idx - row * (D / 4)) * 4;
+        const float* po = p.part_o + (slot * 16 + row) * D + d;
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int s0 = 0; s0 < n_valid; s0 += 8) {
+            float4 v[8];
+#pragma unroll
+            for (int x = 0; x < 8; ++x)
+                v[x] = s0 + x < n_valid ? __ldcg(reinterpret_cast<const float4*>(po + (size_t)(s0 + x) * 16 * D))
+                                        : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+            for (int x = 0; x < 8; ++x) {
+                const float ws = s0 + x < n_valid ? wgt[row * MAX_SPLITS + s0 + x] : 0.f;
+                acc.x += ws * v[x].x; acc.y += ws * v[x].y; acc.z += ws * v[x].z; acc.w += ws * v[x].w;
+            }
+        }
+        bf16* o = p.out + ((size_t)(q_start + row / G) * p.Hq + hk * G + row % G) * D + d;
+        *reinterpret_cast<uint2*>(o) = make_uint2(pack_bf16(acc.x, acc.y), pack_bf16(acc.z, acc.w));
     }
 }
 
@@ -158,7 +212,7 @@ KVB_API int kvb_flash_decode(const void* q, void* out, const void* k_pages, cons
     if (n_items <= 0) return KVB_OK;
     if (Hkv < 1 || Hq % Hkv != 0 || Hq / Hkv > 16) return KVB_ERR_SHAPE;
     if (page_size < 1 || (page_size & (page_size - 1)) != 0) return KVB_ERR_SHAPE;
-    if (nsplit < 1 || nsplit > 32 || n_items > 65535 || Hkv > 65535) return KVB_ERR_LIMIT;
+    if (nsplit < 1 || nsplit > MAX_SPLITS || n_items > 65535 || Hkv > 65535) return KVB_ERR_LIMIT;
     DecodeParams p;
     p.q = (const bf16*)q; p.out = (bf16*)out; p.k_pages = (const bf16*)k_pages; p.v_pages = (const bf16*)v_pages;
     p.block_table = block_table; p.items = items; p.seg_q_start = seg_q_start; p.seg_q_len = seg_q_len;
@@ -171,15 +225,19 @@ KVB_API int kvb_flash_decode(const void* q, void* out, const void* k_pages, cons
     while ((1 << p.page_shift) < page_size) ++p.page_shift;
     p.window = window; p.nsplit = nsplit;
     p.scale_log2 = scale * 1.4426950408889634f;
-    const size_t smem = (size_t)DECODE_STAGES * 2 * TILE_ELEMS * sizeof(bf16);
+    size_t smem = (size_t)DECODE_STAGES * 2 * TILE_ELEMS * sizeof(bf16);
+    const size_t merge = (size_t)(4 * 16 * D + 4 * 16 * 2 + 3 * 16 * MAX_SPLITS) * sizeof(float);
+    if (merge > smem) smem = merge;
     static bool configured = false;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(flash_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return (int)e;
+        e = cudaFuncSetAttribute(flash_decode_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+        if (e != cudaSuccess) return (int)e;
         configured = true;
     }
     dim3 grid(nsplit, Hkv, n_items);
-    flash_decode_kernel<<<grid, 32, smem, stream>>>(p);
+    flash_decode_kernel<<<grid, 128, smem, stream>>>(p);
     return kvb_launch_status();
 }
 
@@ -234,14 +292,14 @@ __global__ void __launch_bounds__(128) flash_prefill_kernel(const PrefillParams 
     constexpr int STAGES = PREFILL_STAGES;
 #pragma unroll
     for (int s = 0; s < STAGES - 1; ++s) {
-        if (s < n) load_tile(smem + (2 * s) * TILE_ELEMS, smem + (2 * s + 1) * TILE_ELEMS, src, (kt_begin + s) * KT, key_lo, pos_last + 1, threadIdx.x, 128);
+        if (s < n) load_tile(smem + (2 * s) * TILE_ELEMS, smem + (2 * s + 1) * TILE_ELEMS, src, (kt_begin + s) * KT, key_lo, pos_last + 1);
         cp_async_commit();
     }
     for (int i = 0; i < n; ++i) {
         const int ahead = i + STAGES - 1;
         if (ahead < n) {
             const int s = ahead % STAGES;
-            load_tile(smem + (2 * s) * TILE_ELEMS, smem + (2 * s + 1) * TILE_ELEMS, src, (kt_begin + ahead) * KT, key_lo, pos_last + 1, threadIdx.x, 128);
+            load_tile(smem + (2 * s) * TILE_ELEMS, smem + (2 * s + 1) * TILE_ELEMS, src, (kt_begin + ahead) * KT, key_lo, pos_last + 1);
         }
         cp_async_commit();
         cp_async_wait<STAGES - 1>();
@@ -249,7 +307,8 @@ __global__ void __launch_bounds__(128) flash_prefill_kernel(const PrefillParams 
         const int s = i % STAGES;
         const int key0 = (kt_begin + i) * KT;
         if (warp_rows > 0 && key0 <= warp_pos_last && key0 + KT > warp_key_lo)
-            rows_tile(w, smem + (2 * s) * TILE_ELEMS, smem + (2 * s + 1) * TILE_ELEMS, key0, p.window, p.scale_log2);
+            rows_tile_auto<KT>(w, smem + (2 * s) * TILE_ELEMS, smem + (2 * s + 1) * TILE_ELEMS, key0, p.window, p.scale_log2,
+                           warp_pos_first, warp_pos_last, warp_rows == 16);
         __syncthreads();
     }
     rows_finish_sum(w);
@@ -279,6 +338,8 @@ KVB_API int kvb_flash_prefill(const void* q, void* out, const void* k_pages, con
     static bool configured = false;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(flash_prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+        e = cudaFuncSetAttribute(flash_prefill_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }

@@ -62,21 +62,33 @@ struct KVSource {
 };
 
 // Copies keys/values [key0, key0 + KT) into a stage; keys >= key_end (or before key_lo) are zero-filled.
-// Called by `nthreads` threads (a warp or a block), thread index `tid`.
-__device__ __forceinline__ void load_tile(bf16* ks, bf16* vs, const KVSource& src, int key0, int key_lo, int key_end,
-                                          int tid, int nthreads) {
-    for (int idx = tid; idx < KT * CHUNKS; idx += nthreads) {
-        const int row = idx / CHUNKS, c = idx - row * CHUNKS;
-        const int j = key0 + row;
-        const bool valid = j >= key_lo && j < key_end;
-        size_t off = 0;
-        if (valid) {
-            const int page = __ldg(src.table + (j >> src.page_shift));
-            off = (((size_t)page * src.Hkv + src.hk) * src.page_size + (j & (src.page_size - 1))) * D + c * 8;
-        }
-        cp_async16(ks + row * STRIDE + c * 8, src.k_pages + off, valid);
-        cp_async16(vs + row * STRIDE + c * 8, src.v_pages + off, valid);
+// Called by a block of 128 threads: two threads share a row and take alternate 16-byte chunks, so
+// neighbours fetch one 32-byte sector together and each thread looks its page up once.
+__device__ __forceinline__ void load_tile(bf16* ks, bf16* vs, const KVSource& src, int key0, int key_lo, int key_end) {
+    const int row = threadIdx.x >> 1, half = threadIdx.x & 1;
+    const int j = key0 + row;
+    const bool valid = j >= key_lo && j < key_end;
+    size_t off = 0;
+    if (valid) {
+        const int page = __ldg(src.table + (j >> src.page_shift));
+        off = (((size_t)page * src.Hkv + src.hk) * src.page_size + (j & (src.page_size - 1))) * D;
     }
+    const bf16* kg = src.k_pages + off;
+    const bf16* vg = src.v_pages + off;
+    bf16* kd = ks + row * STRIDE;
+    bf16* vd = vs + row * STRIDE;
+#pragma unroll
+    for (int c = 0; c < CHUNKS / 2; ++c) {
+        const int e = (2 * c + half) * 8;
+        cp_async16(kd + e, kg + e, valid);
+        cp_async16(vd + e, vg + e, valid);
+    }
+}
+
+__device__ __forceinline__ float ex2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
 }
 
 // The 16 query rows of a warp.
@@ -110,20 +122,23 @@ __device__ __forceinline__ void rows_load_q(WarpRows& w, RowPtr row_ptr) {
     }
 }
 
-// One tile of keys [key0, key0 + KT) from a stage: scores, masking, running softmax, weighted sum.
+// NK keys [key0, key0 + NK) whose rows start at `ks` / `vs` in a stage: scores, masking, running
+// softmax, weighted sum.  NK is a multiple of 16 (a whole tile, or a part of one).
 // A key j is seen by a row at position p iff key_lo(p) <= j <= p, key_lo(p) = max(0, p - window + 1).
+// MASKED = false: the caller knows that every row sees every key of the range.
+template <int NK, bool MASKED>
 __device__ __forceinline__ void rows_tile(WarpRows& w, const bf16* ks, const bf16* vs, int key0, int window,
                                           float scale_log2) {
     const int lane = threadIdx.x & 31, t = lane & 3;
-    float s[KT / 8][4];
+    float s[NK / 8][4];
 #pragma unroll
-    for (int i = 0; i < KT / 8; ++i) s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f;
+    for (int i = 0; i < NK / 8; ++i) s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f;
     {
         const int mi = lane >> 3, key_off = (mi >> 1) * 8 + (lane & 7), d_off = (mi & 1) * 8;
 #pragma unroll
         for (int k = 0; k < KS; ++k) {
 #pragma unroll
-            for (int n2 = 0; n2 < KT / 16; ++n2) {
+            for (int n2 = 0; n2 < NK / 16; ++n2) {
                 uint32_t b0, b1, b2, b3;
                 ldmatrix_x4(b0, b1, b2, b3, ks + (n2 * 16 + key_off) * STRIDE + k * 16 + d_off);
                 mma_bf16(s[2 * n2], w.q[k], b0, b1);
@@ -131,19 +146,19 @@ __device__ __forceinline__ void rows_tile(WarpRows& w, const bf16* ks, const bf1
             }
         }
     }
-    // Scale, mask, row maxima.
+    // Row maxima of the raw scores (masked ones count as -inf); scores stay unscaled until the exponent.
     float mx[2] = {NEG_INF, NEG_INF};
 #pragma unroll
-    for (int n = 0; n < KT / 8; ++n) {
+    for (int n = 0; n < NK / 8; ++n) {
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
-            const int r = e >> 1;
-            const int j = key0 + n * 8 + 2 * t + (e & 1);
-            const int p = w.pos[r];
-            const bool seen = j <= p && (window <= 0 || j > p - window);
-            const float v = seen ? s[n][e] * scale_log2 : NEG_INF;
-            s[n][e] = v;
-            mx[r] = fmaxf(mx[r], v);
+            if (MASKED) {
+                const int j = key0 + n * 8 + 2 * t + (e & 1);
+                const int p = w.pos[e >> 1];
+                const bool seen = j <= p && (window <= 0 || j > p - window);
+                if (!seen) s[n][e] = NEG_INF;
+            }
+            mx[e >> 1] = fmaxf(mx[e >> 1], s[n][e]);
         }
     }
     float corr[2], base[2];
@@ -151,30 +166,32 @@ __device__ __forceinline__ void rows_tile(WarpRows& w, const bf16* ks, const bf1
     for (int r = 0; r < 2; ++r) {
         mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
         mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
-        const float m_new = fmaxf(w.m[r], mx[r]);
+        const float m_new = fmaxf(w.m[r], mx[r] * scale_log2);      // scale_log2 > 0: the maximum commutes with it
         base[r] = m_new == NEG_INF ? 0.f : m_new;
-        corr[r] = exp2f(w.m[r] - base[r]);
+        corr[r] = ex2(w.m[r] - base[r]);
         w.m[r] = m_new;
         w.l[r] *= corr[r];
     }
 #pragma unroll
-    for (int n = 0; n < KT / 8; ++n) {
+    for (int n = 0; n < NK / 8; ++n) {
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
-            const float p = exp2f(s[n][e] - base[e >> 1]);
+            const float p = ex2(fmaf(s[n][e], scale_log2, -base[e >> 1]));
             s[n][e] = p;
             w.l[e >> 1] += p;
         }
     }
+    if (__any_sync(0xffffffffu, corr[0] != 1.f || corr[1] != 1.f)) {   // the maxima seldom move once a few tiles are in
 #pragma unroll
-    for (int i = 0; i < NT_O; ++i) {
-        w.o[i][0] *= corr[0]; w.o[i][1] *= corr[0];
-        w.o[i][2] *= corr[1]; w.o[i][3] *= corr[1];
+        for (int i = 0; i < NT_O; ++i) {
+            w.o[i][0] *= corr[0]; w.o[i][1] *= corr[0];
+            w.o[i][2] *= corr[1]; w.o[i][3] *= corr[1];
+        }
     }
     {
         const int mi = lane >> 3, key_off = (mi & 1) * 8 + (lane & 7), d_off = (mi >> 1) * 8;
 #pragma unroll
-        for (int kk = 0; kk < KT / 16; ++kk) {
+        for (int kk = 0; kk < NK / 16; ++kk) {
             uint32_t pa[4];
             pa[0] = pack_bf16(s[2 * kk][0], s[2 * kk][1]);
             pa[1] = pack_bf16(s[2 * kk][2], s[2 * kk][3]);
@@ -189,6 +206,16 @@ __device__ __forceinline__ void rows_tile(WarpRows& w, const bf16* ks, const bf1
             }
         }
     }
+}
+
+// NK keys from key0 on: masked only if a row may miss one of them.  `pos_min` / `pos_max`: smallest and
+// largest position among the warp's existing rows.
+template <int NK>
+__device__ __forceinline__ void rows_tile_auto(WarpRows& w, const bf16* ks, const bf16* vs, int key0, int window,
+                                               float scale_log2, int pos_min, int pos_max, bool all_rows_exist) {
+    const bool open = all_rows_exist && key0 + NK - 1 <= pos_min && (window <= 0 || key0 > pos_max - window);
+    if (open) rows_tile<NK, false>(w, ks, vs, key0, window, scale_log2);
+    else rows_tile<NK, true>(w, ks, vs, key0, window, scale_log2);
 }
 
 // Sums each row's l over the four threads that share it.

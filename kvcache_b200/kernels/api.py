@@ -145,7 +145,8 @@ class CudaKernels(KernelSet):
         self._sampling = _Library("sampling")
         self._flash: Dict[int, _Library] = {}
         self.flash_attention = True          # bfloat16, head sizes 16..128: tensor-core kernels
-        self.decode_ctas_wanted = 148 * 4    # the split over the keys aims at this many warps in flight
+        self.decode_ctas_wanted = 148 * 4    # the split over the keys aims at this many blocks in flight
+        self.decode_min_tiles = 4            # ... but gives a split at least this many 64-key tiles
         self.error_word = torch.zeros(1, dtype=torch.int32, device=self.device)
         self.launches = 0
 
@@ -237,7 +238,8 @@ class CudaKernels(KernelSet):
                     "flash_prefill")
             n = batch.num_decode_items
             if n:
-                nsplit = max(1, min(32, -(-self.decode_ctas_wanted // (n * Hkv))))
+                tiles = -(-max(batch.max_kv_len, 1) // 64)
+                nsplit = max(1, min(32, self.decode_ctas_wanted // (n * Hkv), tiles // self.decode_min_tiles))
                 scratch = workspace.buffer("attn.decode_scratch", (n * Hkv * nsplit * 16 * (D + 2),), torch.float32)
                 tickets = workspace.zeros("attn.decode_tickets", (n * Hkv,), torch.int32)
                 self.launches += 1

@@ -186,12 +186,12 @@ def test_paged_attention_flash(kernels, scenario):
     ref = torch.empty(T, Hq * D, dtype=dtype)
     REF.paged_attention(q, batch, kv, ref, Hq, D ** -0.5)
     ws = Workspace(DEV)
-    for wanted in (148 * 4, 3, 100000):          # many splits, one split, as many as allowed
-        kernels.decode_ctas_wanted = wanted
+    for wanted, min_tiles in ((148 * 4, 4), (3, 4), (100000, 1)):   # default; one split; as many as allowed
+        kernels.decode_ctas_wanted, kernels.decode_min_tiles = wanted, min_tiles
         out = torch.full((T, Hq * D), float("nan"), dtype=dtype, device=DEV)
         kernels.paged_attention(q.to(DEV), batch_to(batch, DEV), clone_kv(kv, DEV), out, Hq, D ** -0.5, ws)
         assert_close(out, ref, REL[dtype], f"decode_ctas_wanted={wanted}")
-    kernels.decode_ctas_wanted = 148 * 4
+    kernels.decode_ctas_wanted, kernels.decode_min_tiles = 148 * 4, 4
     assert int(ws.buffer("attn.decode_tickets", (1,), torch.int32).sum()) == 0
     kernels.check_errors()
 
