@@ -78,29 +78,33 @@ KVB_API int kvb_add_rmsnorm(int dtype, float* h, const void* delta, const float*
     return kvb_launch_status();
 }
 
-// out[r, i] = silu(gu[r, i]) * gu[r, I + i],  silu(g) = g / (1 + exp(-g))   (src/qwen_kernels.cu:102-105)
+// out[r, i] = silu(gate[r, i]) * up[r, i],  silu(g) = g / (1 + exp(-g))   (src/qwen_kernels.cu:102-105).
+// gu[r, :] holds the gate and up projections of row r: [gate(I) | up(I)], or, interleaved in eights,
+// gate i at column 16 (i / 8) + i % 8 and up i eight columns further.
 template <typename T>
-__global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, int I, size_t total) {
+__global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, int I, size_t total, int interleaved) {
     for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
          idx += (size_t)gridDim.x * blockDim.x) {
         const size_t r = idx / I;
         const int i = (int)(idx - r * I);
-        const float g = to_f32<T>(gu[r * 2 * I + i]);
-        const float u = to_f32<T>(gu[r * 2 * I + I + i]);
+        const int gcol = interleaved ? 16 * (i >> 3) + (i & 7) : i;
+        const float g = to_f32<T>(gu[r * 2 * I + gcol]);
+        const float u = to_f32<T>(gu[r * 2 * I + gcol + (interleaved ? 8 : I)]);
         out[idx] = from_f32<T>(g / (1.f + expf(-g)) * u);
     }
 }
 
-KVB_API int kvb_silu_mul(int dtype, const void* gate_up, void* out, int T, int I, cudaStream_t stream) {
+KVB_API int kvb_silu_mul(int dtype, const void* gate_up, void* out, int T, int I, int interleaved, cudaStream_t stream) {
+    if (interleaved && I % 8 != 0) return KVB_ERR_SHAPE;
     const size_t total = (size_t)T * I;
     if (total == 0) return KVB_OK;
     const int threads = 256;
     size_t blocks = (total + threads - 1) / threads;
     if (blocks > 148 * 16) blocks = 148 * 16;
     if (dtype == KVB_F32)
-        silu_mul_kernel<float><<<(int)blocks, threads, 0, stream>>>((const float*)gate_up, (float*)out, I, total);
+        silu_mul_kernel<float><<<(int)blocks, threads, 0, stream>>>((const float*)gate_up, (float*)out, I, total, interleaved);
     else if (dtype == KVB_BF16)
-        silu_mul_kernel<bf16><<<(int)blocks, threads, 0, stream>>>((const bf16*)gate_up, (bf16*)out, I, total);
+        silu_mul_kernel<bf16><<<(int)blocks, threads, 0, stream>>>((const bf16*)gate_up, (bf16*)out, I, total, interleaved);
     else
         return KVB_ERR_DTYPE;
     return kvb_launch_status();

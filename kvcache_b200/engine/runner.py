@@ -256,8 +256,6 @@ class ModelRunner:
             batch.token_ids.copy_(token_source[:batch.num_tokens], non_blocking=True)
         decode_only = sample and self.use_graphs and batch.num_tokens == batch.num_segments == batch.num_wanted
         if decode_only:
-            # Launch shapes in a graph are fixed: size them for the longest request the cache allows.
-            batch.max_kv_len = self.cache.max_pages_per_request * self.cache.page_size
             found = self._decode_graph(batch, view, layout)
             found.graph.replay()
             self.kernels.launches += found.launches

@@ -79,7 +79,7 @@ _SIGNATURES = {
     "elementwise": {
         "kvb_embed": [_c_int, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_void_p, _c_void_p],
         "kvb_add_rmsnorm": [_c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_float, _c_void_p],
-        "kvb_silu_mul": [_c_int, _c_void_p, _c_void_p, _c_int, _c_int, _c_void_p],
+        "kvb_silu_mul": [_c_int, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_void_p],
     },
     "rope_append": {
         "kvb_qkv_rope_append": [_c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_void_p,
@@ -93,6 +93,9 @@ _SIGNATURES = {
     },
     "gemm_simt": {
         "kvb_gemm_simt": [_c_int, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_void_p],
+    },
+    "gemm_skinny": {
+        "kvb_gemm_skinny": [_c_int, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_void_p],
     },
     "attention_flash": {
         "kvb_flash_head_dim": [],
@@ -143,6 +146,8 @@ class CudaKernels(KernelSet):
         self._attn_generic = _Library("attention_generic")
         self._gemm_simt = _Library("gemm_simt")
         self._sampling = _Library("sampling")
+        self._gemm_skinny = _Library("gemm_skinny")
+        self.skinny_gemm = True              # bfloat16, M <= 64, K % 32 == 0: weight-streaming kernel
         self._flash: Dict[int, _Library] = {}
         self.flash_attention = True          # bfloat16, head sizes 16..128: tensor-core kernels
         self.decode_ctas_wanted = 148 * 4    # the split over the keys aims at this many blocks in flight
@@ -176,18 +181,42 @@ class CudaKernels(KernelSet):
                                                  _ptr(out), _ptr(rows), n_out, H, float(eps), self._stream()),
                "add_rmsnorm")
 
-    def silu_mul(self, gate_up: torch.Tensor, out: torch.Tensor) -> None:
+    def silu_mul(self, gate_up: torch.Tensor, out: torch.Tensor, interleaved: bool = False) -> None:
         T, I = out.shape
         self.launches += 1
-        _check(self._elementwise.kvb_silu_mul(_dtype_code(out.dtype), _ptr(gate_up), _ptr(out), T, I, self._stream()),
-               "silu_mul")
+        _check(self._elementwise.kvb_silu_mul(_dtype_code(out.dtype), _ptr(gate_up), _ptr(out), T, I,
+                                              1 if interleaved else 0, self._stream()), "silu_mul")
+
+    def gate_up_act(self, x: torch.Tensor, w_gate_up: torch.Tensor, out: torch.Tensor, workspace, interleaved: bool) -> None:
+        """out[M, I] = silu(x Wg^T) * (x Wu^T); `w_gate_up` [2 I, K] holds gate and up rows one after the
+        other, or interleaved in eights (see csrc/gemm_skinny.cu)."""
+        M, K = x.shape
+        I = out.shape[1]
+        if interleaved and self._skinny(x.dtype, M, K):
+            self.launches += 1
+            _check(self._gemm_skinny.kvb_gemm_skinny(_dtype_code(out.dtype), 1, _ptr(x), _ptr(w_gate_up), _ptr(None),
+                                                     _ptr(out), M, 2 * I, K, self._stream()), "gate_up_act (skinny)")
+            return
+        gate_up = workspace.buffer("ffn.gate_up", (M, 2 * I), out.dtype)
+        self.linear(x, w_gate_up, gate_up)
+        self.silu_mul(gate_up, out, interleaved)
+
+    SKINNY_MAX_ROWS = 16     # above this the library product is faster (measured at M = 64)
+
+    def _skinny(self, dtype: torch.dtype, M: int, K: int) -> bool:
+        return self.skinny_gemm and dtype == torch.bfloat16 and M <= self.SKINNY_MAX_ROWS and K % 32 == 0
 
     def linear(self, x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bias: Optional[torch.Tensor] = None) -> None:
-        M, K = x.shape
-        N = w.shape[0]
-        if w.shape[1] != K or tuple(out.shape) != (M, N):
+        """out = x . w^T + bias."""
+        M = x.shape[0]
+        N, K = w.shape
+        if x.shape[1] != K or tuple(out.shape) != (M, N):
             raise KernelError(f"linear: shapes x{tuple(x.shape)} w{tuple(w.shape)} out{tuple(out.shape)} do not fit")
         self.launches += 1
+        if self._skinny(x.dtype, M, K):
+            _check(self._gemm_skinny.kvb_gemm_skinny(_dtype_code(out.dtype), 0, _ptr(x), _ptr(w), _ptr(bias),
+                                                     _ptr(out), M, N, K, self._stream()), "linear (skinny)")
+            return
         if x.dtype == torch.bfloat16 and self.bf16_gemm == "cublas":
             # Library matrix product, as the reference's cublasGemmEx (apps/qwen_serve.cu:27-39).
             if out.dtype == torch.bfloat16:
@@ -238,7 +267,9 @@ class CudaKernels(KernelSet):
                     "flash_prefill")
             n = batch.num_decode_items
             if n:
-                tiles = -(-max(batch.max_kv_len, 1) // 64)
+                # Sized by the longest request the block table allows, not by this step's lengths, so that the
+                # split (and with it the rounding) is the same in every step and under a CUDA graph.
+                tiles = -(-(kv.block_table.shape[1] * kv.page_size) // 64)
                 nsplit = max(1, min(32, self.decode_ctas_wanted // (n * Hkv), tiles // self.decode_min_tiles))
                 scratch = workspace.buffer("attn.decode_scratch", (n * Hkv * nsplit * 16 * (D + 2),), torch.float32)
                 tickets = workspace.zeros("attn.decode_tickets", (n * Hkv,), torch.int32)

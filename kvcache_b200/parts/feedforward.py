@@ -20,6 +20,7 @@ class GatedMLP(FeedForward):
         self.dtype = TORCH_DTYPES[dtype]
         self.w_gate_up: Optional[torch.Tensor] = None
         self.w_down: Optional[torch.Tensor] = None
+        self.interleaved = False
 
     def tensor_specs(self) -> Dict[str, TensorSpec]:
         p = self.prefix
@@ -31,8 +32,16 @@ class GatedMLP(FeedForward):
 
     def bind(self, tensors: Mapping[str, torch.Tensor], device: torch.device) -> None:
         p = self.prefix
-        self.w_gate_up = torch.cat([tensors[f"{p}gate_proj.weight"], tensors[f"{p}up_proj.weight"]], dim=0) \
-            .to(self.dtype).to(device).contiguous()
+        gate, up = tensors[f"{p}gate_proj.weight"], tensors[f"{p}up_proj.weight"]
+        # One projection for gate and up.  When the width allows, rows are interleaved in eights (gate rows
+        # 8 b .. 8 b + 7, then the up rows of the same indices) so that a kernel's thread holds both values
+        # of an index and can write the activation without a second pass.
+        self.interleaved = self.intermediate % 8 == 0
+        if self.interleaved:
+            both = torch.stack([gate.view(-1, 8, self.hidden), up.view(-1, 8, self.hidden)], dim=1).reshape(-1, self.hidden)
+        else:
+            both = torch.cat([gate, up], dim=0)
+        self.w_gate_up = both.to(self.dtype).to(device).contiguous()
         self.w_down = tensors[f"{p}down_proj.weight"].to(self.dtype).to(device).contiguous()
 
     def weight_bytes(self) -> int:
@@ -41,10 +50,8 @@ class GatedMLP(FeedForward):
     def forward(self, x: torch.Tensor, ctx: LayerContext) -> torch.Tensor:
         T = x.shape[0]
         k, ws = ctx.kernels, ctx.workspace
-        gate_up = ws.buffer("ffn.gate_up", (T, 2 * self.intermediate), self.dtype)
-        k.linear(x, self.w_gate_up, gate_up)
         act = ws.buffer("ffn.act", (T, self.intermediate), self.dtype)
-        k.silu_mul(gate_up, act)
+        k.gate_up_act(x, self.w_gate_up, act, ws, self.interleaved)
         delta = ws.buffer("ffn.delta", (T, self.hidden), self.dtype)
         k.linear(act, self.w_down, delta)
         return delta

@@ -70,11 +70,12 @@ def test_add_rmsnorm(kernels, dtype, T, H, eps):
 @pytest.mark.parametrize("T,I", [(1, 128), (9, 4864), (31, 200), (2, 77)])
 def test_silu_mul(kernels, dtype, T, I):
     gu = (torch.randn(T, 2 * I, generator=torch.Generator().manual_seed(2)) * 4).to(dtype)
-    ref = torch.empty(T, I, dtype=dtype)
-    REF.silu_mul(gu, ref)
-    out = torch.empty(T, I, dtype=dtype, device=DEV)
-    kernels.silu_mul(gu.to(DEV), out)
-    assert_close(out, ref, REL[dtype])
+    for interleaved in ([False, True] if I % 8 == 0 else [False]):
+        ref = torch.empty(T, I, dtype=dtype)
+        REF.silu_mul(gu, ref, interleaved)
+        out = torch.empty(T, I, dtype=dtype, device=DEV)
+        kernels.silu_mul(gu.to(DEV), out, interleaved)
+        assert_close(out, ref, REL[dtype])
 
 
 @pytest.mark.parametrize("in_dtype,out_dtype", [(torch.float32, torch.float32), (torch.bfloat16, torch.bfloat16),
@@ -98,6 +99,66 @@ def test_gemm_simt(kernels, in_dtype, out_dtype, M, N, K):
         assert_close(out, ref, REL[out_dtype])
 
 
+@pytest.mark.parametrize("M,N,K", [(1, 256, 64), (3, 331, 96), (8, 1152, 896), (8, 896, 4864), (9, 40, 32), (16, 9728, 896),
+                                   (17, 1000, 320), (33, 151936, 64), (64, 1152, 896), (64, 200, 4864), (5, 20000, 128)])
+def test_gemm_skinny(kernels, request, M, N, K):
+    g = torch.Generator().manual_seed(16)
+    x = torch.randn(M, K, generator=g).to(torch.bfloat16)
+    w = torch.randn(N, K, generator=g).to(torch.bfloat16)
+    bias = torch.randn(N, generator=g)
+    saved_rows = kernels.SKINNY_MAX_ROWS
+    kernels.SKINNY_MAX_ROWS = 64
+    request.addfinalizer(lambda: setattr(kernels, 'SKINNY_MAX_ROWS', saved_rows))
+    assert kernels._skinny(torch.bfloat16, M, K)
+    for out_dtype in (torch.bfloat16, torch.float32):
+        for b in (None, bias):
+            ref = torch.empty(M, N, dtype=out_dtype)
+            REF.linear(x, w, ref, b)
+            out = torch.full((M, N), float("nan"), dtype=out_dtype, device=DEV)
+            kernels.linear(x.to(DEV), w.to(DEV), out, b.to(DEV) if b is not None else None)
+            assert_close(out, ref, REL[out_dtype])
+
+
+@pytest.mark.parametrize("M,I,K", [(1, 128, 64), (8, 4864, 896), (13, 200, 96), (64, 320, 128), (70, 200, 120), (5, 77, 64)])
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_gate_up_act(kernels, request, dtype, M, I, K):
+    saved_rows = kernels.SKINNY_MAX_ROWS
+    kernels.SKINNY_MAX_ROWS = 64
+    request.addfinalizer(lambda: setattr(kernels, 'SKINNY_MAX_ROWS', saved_rows))
+    """Gate/up projection with the activation: fused into the skinny kernel's output, or as
+    library product + activation kernel; interleaved rows where the width allows."""
+    from kvcache_b200.engine.workspace import Workspace
+    from kvcache_b200.parts.feedforward import GatedMLP
+    g = torch.Generator().manual_seed(18)
+    x = torch.randn(M, K, generator=g).to(dtype)
+    wg, wu = torch.randn(I, K, generator=g).to(dtype), torch.randn(I, K, generator=g).to(dtype)
+    gate, up = x.double() @ wg.double().t(), x.double() @ wu.double().t()
+    want = gate / (1 + torch.exp(-gate)) * up
+    name = {torch.float32: "float32", torch.bfloat16: "bfloat16"}[dtype]
+    ffn = GatedMLP(K, I, activation="silu", prefix="m.", dtype=name)
+    ffn.bind({"m.gate_proj.weight": wg, "m.up_proj.weight": wu, "m.down_proj.weight": torch.zeros(K, I)}, torch.device(DEV))
+    assert ffn.interleaved == (I % 8 == 0)
+    out = torch.full((M, I), float("nan"), dtype=dtype, device=DEV)
+    kernels.gate_up_act(x.to(DEV), ffn.w_gate_up, out, Workspace(DEV), ffn.interleaved)
+    # bfloat16: gate and up are rounded before the activation on the unfused path.
+    assert_close(out, want, 2e-5 if dtype == torch.float32 else 2e-2)
+
+
+def test_gemm_skinny_rows_do_not_depend_on_the_batch(kernels, request):
+    saved_rows = kernels.SKINNY_MAX_ROWS
+    kernels.SKINNY_MAX_ROWS = 64
+    request.addfinalizer(lambda: setattr(kernels, 'SKINNY_MAX_ROWS', saved_rows))
+    g = torch.Generator().manual_seed(17)
+    x = torch.randn(64, 896, generator=g).to(torch.bfloat16).to(DEV)
+    w = torch.randn(1152, 896, generator=g).to(torch.bfloat16).to(DEV)
+    full = torch.empty(64, 1152, dtype=torch.bfloat16, device=DEV)
+    kernels.linear(x, w, full)
+    for M in (1, 7, 8, 20, 33):
+        part = torch.empty(M, 1152, dtype=torch.bfloat16, device=DEV)
+        kernels.linear(x[:M].contiguous(), w, part)
+        assert torch.equal(part, full[:M]), M
+
+
 @pytest.mark.parametrize("M,N,K", [(1, 256, 64), (8, 1152, 896), (70, 136, 80), (200, 331, 120)])
 def test_linear_bf16_library(kernels, M, N, K):
     g = torch.Generator().manual_seed(4)
@@ -107,7 +168,12 @@ def test_linear_bf16_library(kernels, M, N, K):
         ref = torch.empty(M, N, dtype=out_dtype)
         REF.linear(x, w, ref)
         out = torch.empty(M, N, dtype=out_dtype, device=DEV)
-        kernels.linear(x.to(DEV), w.to(DEV), out)
+        saved = kernels.skinny_gemm
+        kernels.skinny_gemm = False
+        try:
+            kernels.linear(x.to(DEV), w.to(DEV), out)
+        finally:
+            kernels.skinny_gemm = saved
         assert_close(out, ref, REL[out_dtype])
 
 

@@ -92,10 +92,19 @@ class TorchKernels:
                 result[r, h] = torch.softmax(s, dim=0) @ vals[:, h // group, :]
         out.copy_(result.view(T, Hq * D).to(out.dtype))
 
-    def silu_mul(self, gate_up, out):
+    def silu_mul(self, gate_up, out, interleaved=False):
         I = out.shape[1]
-        g, u = gate_up[:, :I].to(self.f), gate_up[:, I:].to(self.f)
+        if interleaved:
+            pairs = gate_up.view(gate_up.shape[0], I // 8, 2, 8)
+            g, u = pairs[:, :, 0, :].reshape(-1, I).to(self.f), pairs[:, :, 1, :].reshape(-1, I).to(self.f)
+        else:
+            g, u = gate_up[:, :I].to(self.f), gate_up[:, I:].to(self.f)
         out.copy_((g / (1.0 + torch.exp(-g)) * u).to(out.dtype))
+
+    def gate_up_act(self, x, w_gate_up, out, workspace, interleaved):
+        gate_up = torch.empty(x.shape[0], w_gate_up.shape[0], dtype=out.dtype, device=out.device)
+        self.linear(x, w_gate_up, gate_up)
+        self.silu_mul(gate_up, out, interleaved)
 
     def sample_parts(self, vocab):
         return 1
