@@ -65,10 +65,74 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ h, const T* __restrict__ 
     }
 }
 
+// The same with 4 elements per thread and step (H a multiple of 4, rows 16-byte aligned).
+template <typename T> struct Vec4;
+template <> struct Vec4<float> {
+    static __device__ __forceinline__ float4 load(const float* p) { return *reinterpret_cast<const float4*>(p); }
+    static __device__ __forceinline__ void store(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
+};
+template <> struct Vec4<bf16> {
+    static __device__ __forceinline__ float4 load(const bf16* p) {
+        const uint2 raw = *reinterpret_cast<const uint2*>(p);
+        const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
+        const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
+        return make_float4(a.x, a.y, b.x, b.y);
+    }
+    static __device__ __forceinline__ void store(bf16* p, float4 v) {
+        __nv_bfloat162 a = __floats2bfloat162_rn(v.x, v.y), b = __floats2bfloat162_rn(v.z, v.w);
+        uint2 raw;
+        raw.x = *reinterpret_cast<uint32_t*>(&a);
+        raw.y = *reinterpret_cast<uint32_t*>(&b);
+        *reinterpret_cast<uint2*>(p) = raw;
+    }
+};
+
+template <typename T>
+__global__ void add_rmsnorm_vec_kernel(float* __restrict__ h, const T* __restrict__ delta, const float* __restrict__ w,
+                                       T* __restrict__ out, const int* __restrict__ rows, int H, float eps) {
+    __shared__ float scratch[33];
+    const int o = blockIdx.x;
+    const int r = rows ? rows[o] : o;
+    float* hr = h + (size_t)r * H;
+    const T* dr = delta ? delta + (size_t)r * H : nullptr;
+    float ss = 0.f;
+    for (int i = threadIdx.x * 4; i < H; i += blockDim.x * 4) {
+        float4 v = *reinterpret_cast<const float4*>(hr + i);
+        if (dr) {
+            const float4 d = Vec4<T>::load(dr + i);
+            v.x += d.x; v.y += d.y; v.z += d.z; v.w += d.w;
+            if (!rows) *reinterpret_cast<float4*>(hr + i) = v;
+        }
+        // Summed in the order of the scalar kernel's thread: element by element.
+        ss += v.x * v.x; ss += v.y * v.y; ss += v.z * v.z; ss += v.w * v.w;
+    }
+    const float total = block_sum(ss, scratch);
+    const float inv = 1.f / sqrtf(total / (float)H + eps);
+    T* orow = out + (size_t)o * H;
+    for (int i = threadIdx.x * 4; i < H; i += blockDim.x * 4) {
+        float4 v = *reinterpret_cast<const float4*>(hr + i);
+        if (rows && dr) {
+            const float4 d = Vec4<T>::load(dr + i);
+            v.x += d.x; v.y += d.y; v.z += d.z; v.w += d.w;
+        }
+        const float4 ww = *reinterpret_cast<const float4*>(w + i);
+        Vec4<T>::store(orow + i, make_float4(v.x * inv * ww.x, v.y * inv * ww.y, v.z * inv * ww.z, v.w * inv * ww.w));
+    }
+}
+
 KVB_API int kvb_add_rmsnorm(int dtype, float* h, const void* delta, const float* w, void* out, const int* rows,
                             int n_out, int H, float eps, cudaStream_t stream) {
     if (n_out <= 0) return KVB_OK;
     const int threads = H >= 2048 ? 512 : (H >= 512 ? 256 : 128);
+    const bool vec = H % 4 == 0 && ((((uintptr_t)h | (uintptr_t)w | (uintptr_t)out | (uintptr_t)delta) & 15) == 0);
+    if (vec && dtype == KVB_F32) {
+        add_rmsnorm_vec_kernel<float><<<n_out, threads / 2, 0, stream>>>(h, (const float*)delta, w, (float*)out, rows, H, eps);
+        return kvb_launch_status();
+    }
+    if (vec && dtype == KVB_BF16) {
+        add_rmsnorm_vec_kernel<bf16><<<n_out, threads / 2, 0, stream>>>(h, (const bf16*)delta, w, (bf16*)out, rows, H, eps);
+        return kvb_launch_status();
+    }
     if (dtype == KVB_F32)
         add_rmsnorm_kernel<float><<<n_out, threads, 0, stream>>>(h, (const float*)delta, w, (float*)out, rows, H, eps);
     else if (dtype == KVB_BF16)
@@ -94,6 +158,28 @@ __global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, i
     }
 }
 
+// Eight outputs per thread and step: 16-byte loads of gate and up, one 16-byte (bfloat16) store.
+__global__ void silu_mul_vec8_kernel(const bf16* __restrict__ gu, bf16* __restrict__ out, int I, size_t groups, int interleaved) {
+    const int per_row = I >> 3;
+    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < groups; idx += (size_t)gridDim.x * blockDim.x) {
+        const size_t r = idx / per_row;
+        const int b = (int)(idx - r * per_row);
+        const bf16* gp = gu + r * 2 * I + (interleaved ? 16 * b : 8 * b);
+        const uint4 graw = *reinterpret_cast<const uint4*>(gp);
+        const uint4 uraw = *reinterpret_cast<const uint4*>(gp + (interleaved ? 8 : I));
+        const uint32_t gw[4] = {graw.x, graw.y, graw.z, graw.w}, uw[4] = {uraw.x, uraw.y, uraw.z, uraw.w};
+        uint32_t ow[4];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const float2 g = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&gw[k]));
+            const float2 u = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&uw[k]));
+            __nv_bfloat162 o = __floats2bfloat162_rn(g.x / (1.f + expf(-g.x)) * u.x, g.y / (1.f + expf(-g.y)) * u.y);
+            ow[k] = *reinterpret_cast<uint32_t*>(&o);
+        }
+        *reinterpret_cast<uint4*>(out + r * I + 8 * b) = make_uint4(ow[0], ow[1], ow[2], ow[3]);
+    }
+}
+
 KVB_API int kvb_silu_mul(int dtype, const void* gate_up, void* out, int T, int I, int interleaved, cudaStream_t stream) {
     if (interleaved && I % 8 != 0) return KVB_ERR_SHAPE;
     const size_t total = (size_t)T * I;
@@ -101,6 +187,13 @@ KVB_API int kvb_silu_mul(int dtype, const void* gate_up, void* out, int T, int I
     const int threads = 256;
     size_t blocks = (total + threads - 1) / threads;
     if (blocks > 148 * 16) blocks = 148 * 16;
+    if (dtype == KVB_BF16 && I % 8 == 0 && ((((uintptr_t)gate_up | (uintptr_t)out) & 15) == 0)) {
+        const size_t groups = total / 8;
+        size_t vblocks = (groups + threads - 1) / threads;
+        if (vblocks > 148 * 16) vblocks = 148 * 16;
+        silu_mul_vec8_kernel<<<(int)vblocks, threads, 0, stream>>>((const bf16*)gate_up, (bf16*)out, I, groups, interleaved);
+        return kvb_launch_status();
+    }
     if (dtype == KVB_F32)
         silu_mul_kernel<float><<<(int)blocks, threads, 0, stream>>>((const float*)gate_up, (float*)out, I, total, interleaved);
     else if (dtype == KVB_BF16)

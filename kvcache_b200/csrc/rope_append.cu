@@ -66,6 +66,86 @@ __global__ void qkv_rope_append_kernel(const T* __restrict__ qkv, const float* _
     }
 }
 
+// bfloat16, head sizes and rotation halves that are multiples of 8: one thread moves 8 elements
+// (16 bytes) of a head; for a rotated chunk it also reads the partner chunk rot/2 further (or back).
+__global__ void qkv_rope_append_vec8_kernel(const bf16* __restrict__ qkv, const float* __restrict__ bias,
+                                            const float* __restrict__ cos_t, const float* __restrict__ sin_t,
+                                            int rot_half, int table_len, const int* __restrict__ positions,
+                                            const int* __restrict__ row_segment, const int* __restrict__ block_table,
+                                            int table_stride, bf16* __restrict__ k_pages, bf16* __restrict__ v_pages,
+                                            bf16* __restrict__ q_out, int Hq, int Hkv, int D, int page_size, int write_kv,
+                                            int* __restrict__ err) {
+    const int r = blockIdx.x;
+    const int width = (Hq + 2 * Hkv) * D;
+    const int pos = positions[r];
+    const bf16* src = qkv + (size_t)r * width;
+    const int rot = 2 * rot_half;
+    size_t page_base = 0;
+    bool page_ok = true;
+    if (write_kv) {
+        const int seg = row_segment[r];
+        const int page = block_table[(size_t)seg * table_stride + pos / page_size];
+        if (page < 0) {
+            page_ok = false;
+            if (threadIdx.x == 0) atomicOr(err, KVB_DEV_BAD_PAGE);
+        }
+        page_base = (size_t)(page < 0 ? 0 : page) * Hkv * page_size * D + (size_t)(pos % page_size) * D;
+    }
+    const bool pos_ok = rot_half == 0 || (pos >= 0 && pos < table_len);
+    if (!pos_ok && threadIdx.x == 0) atomicOr(err, KVB_DEV_BAD_POS);
+    const float* cr = cos_t + (size_t)(pos_ok ? pos : 0) * rot_half;
+    const float* sr = sin_t + (size_t)(pos_ok ? pos : 0) * rot_half;
+    const int chunks_per_head = D >> 3;
+    for (int c = threadIdx.x; c < (width >> 3); c += blockDim.x) {
+        const int head = c / chunks_per_head, d = (c - head * chunks_per_head) * 8;
+        const int idx = head * D + d;
+        float x[8];
+        {
+            const uint4 raw = *reinterpret_cast<const uint4*>(src + idx);
+            const uint32_t wv[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                const float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&wv[k]));
+                x[2 * k] = f.x; x[2 * k + 1] = f.y;
+            }
+            if (bias) {
+#pragma unroll
+                for (int k = 0; k < 8; ++k) x[k] += bias[idx + k];
+            }
+        }
+        const bool is_v = head >= Hq + Hkv;
+        if (!is_v && d < rot) {
+            const bool low = d < rot_half;
+            const int t0 = low ? d : d - rot_half;
+            const int pidx = low ? idx + rot_half : idx - rot_half;
+            const uint4 raw = *reinterpret_cast<const uint4*>(src + pidx);
+            const uint32_t wv[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                const float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&wv[k]));
+                float xp0 = f.x, xp1 = f.y;
+                if (bias) { xp0 += bias[pidx + 2 * k]; xp1 += bias[pidx + 2 * k + 1]; }
+                const float c0 = cr[t0 + 2 * k], s0 = sr[t0 + 2 * k], c1 = cr[t0 + 2 * k + 1], s1 = sr[t0 + 2 * k + 1];
+                x[2 * k] = low ? (x[2 * k] * c0 - xp0 * s0) : (x[2 * k] * c0 + xp0 * s0);
+                x[2 * k + 1] = low ? (x[2 * k + 1] * c1 - xp1 * s1) : (x[2 * k + 1] * c1 + xp1 * s1);
+            }
+        }
+        uint32_t ow[4];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            __nv_bfloat162 o = __floats2bfloat162_rn(x[2 * k], x[2 * k + 1]);
+            ow[k] = *reinterpret_cast<uint32_t*>(&o);
+        }
+        const uint4 packed = make_uint4(ow[0], ow[1], ow[2], ow[3]);
+        if (head < Hq) {
+            *reinterpret_cast<uint4*>(q_out + (size_t)r * Hq * D + idx) = packed;
+        } else if (write_kv && page_ok) {
+            const int hk = is_v ? head - Hq - Hkv : head - Hq;
+            *reinterpret_cast<uint4*>((is_v ? v_pages : k_pages) + page_base + (size_t)hk * page_size * D + d) = packed;
+        }
+    }
+}
+
 KVB_API int kvb_qkv_rope_append(int dtype, const void* qkv, const float* bias, const float* cos_t,
                                 const float* sin_t, int rot_half, int table_len, const int* positions,
                                 const int* row_segment, const int* block_table, int table_stride, void* k_pages,
@@ -75,6 +155,13 @@ KVB_API int kvb_qkv_rope_append(int dtype, const void* qkv, const float* bias, c
     if (2 * rot_half > D || rot_half < 0) return KVB_ERR_SHAPE;
     const int width = (Hq + 2 * Hkv) * D;
     const int threads = width >= 1024 ? 256 : 128;
+    const uintptr_t addresses = (uintptr_t)qkv | (uintptr_t)k_pages | (uintptr_t)v_pages | (uintptr_t)q_out;
+    if (dtype == KVB_BF16 && D % 8 == 0 && rot_half % 8 == 0 && (addresses & 15) == 0) {
+        qkv_rope_append_vec8_kernel<<<T, width >= 2048 ? 256 : 128, 0, stream>>>(
+            (const bf16*)qkv, bias, cos_t, sin_t, rot_half, table_len, positions, row_segment, block_table, table_stride,
+            (bf16*)k_pages, (bf16*)v_pages, (bf16*)q_out, Hq, Hkv, D, page_size, write_kv, err);
+        return kvb_launch_status();
+    }
     if (dtype == KVB_F32)
         qkv_rope_append_kernel<float><<<T, threads, 0, stream>>>(
             (const float*)qkv, bias, cos_t, sin_t, rot_half, table_len, positions, row_segment, block_table,

@@ -18,7 +18,8 @@ from . import build
 
 _c_int, _c_float, _c_void_p = ctypes.c_int, ctypes.c_float, ctypes.c_void_p
 
-DEVICE_ERRORS = {1: "a token id outside the vocabulary",
+DEVICE_ERRORS = {8: "a wait inside a kernel ran out (a pipeline stalled); the step's results are not valid",
+                 1: "a token id outside the vocabulary",
                  2: "a key or value was needed from a page the block table does not hold",
                  4: "a position beyond the rotation table (longer than the model's maximum length)"}
 
@@ -97,6 +98,9 @@ _SIGNATURES = {
     "gemm_skinny": {
         "kvb_gemm_skinny": [_c_int, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_void_p],
     },
+    "gemm_tcgen05": {
+        "kvb_gemm_tcgen05": [_c_int, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_void_p, _c_void_p],
+    },
     "attention_flash": {
         "kvb_flash_head_dim": [],
         "kvb_flash_decode": [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_int, _c_void_p,
@@ -131,14 +135,19 @@ class _Library:
 
 
 class CudaKernels(KernelSet):
-    def __init__(self, device: torch.device | str = "cuda:0", bf16_gemm: str = "cublas"):
+    def __init__(self, device: torch.device | str = "cuda:0", bf16_gemm: str = "auto"):
+        """`bf16_gemm`: which kernel multiplies bfloat16 matrices of more than SKINNY_MAX_ROWS rows:
+        "tcgen05" (the tensor-memory kernel of csrc/gemm_tcgen05.cu), "cublas" (the library, as the
+        reference uses it), "simt" (CUDA cores), or "auto": tcgen05 where its 128 x 256 tiles fill the
+        machine - there it is measured at 0.8 to 0.85 of the library and fuses the gated activation -
+        and the library for the smaller products, which the tile shapes of this kernel serve badly."""
         self.device = torch.device(device)
         if self.device.type != "cuda" or not torch.cuda.is_available():
             raise KernelError("kvcache_b200 runs on a CUDA device (sm_100a) only; no device is available")
         major, minor = torch.cuda.get_device_capability(self.device)
         if major != 10:
             raise KernelError(f"kernels are built for sm_100a; device {self.device} is sm_{major}{minor}")
-        if bf16_gemm not in ("cublas", "simt"):
+        if bf16_gemm not in ("auto", "tcgen05", "cublas", "simt"):
             raise KernelError(f"unknown bf16_gemm '{bf16_gemm}'")
         self.bf16_gemm = bf16_gemm
         self._elementwise = _Library("elementwise")
@@ -147,11 +156,13 @@ class CudaKernels(KernelSet):
         self._gemm_simt = _Library("gemm_simt")
         self._sampling = _Library("sampling")
         self._gemm_skinny = _Library("gemm_skinny")
+        self._gemm_tc = _Library("gemm_tcgen05")
         self.skinny_gemm = True              # bfloat16, M <= 64, K % 32 == 0: weight-streaming kernel
         self._flash: Dict[int, _Library] = {}
         self.flash_attention = True          # bfloat16, head sizes 16..128: tensor-core kernels
         self.decode_ctas_wanted = 148 * 4    # the split over the keys aims at this many blocks in flight
         self.decode_min_tiles = 4            # ... but gives a split at least this many 64-key tiles
+        self.sm_count = torch.cuda.get_device_properties(self.device).multi_processor_count
         self.error_word = torch.zeros(1, dtype=torch.int32, device=self.device)
         self.launches = 0
 
@@ -197,6 +208,11 @@ class CudaKernels(KernelSet):
             _check(self._gemm_skinny.kvb_gemm_skinny(_dtype_code(out.dtype), 1, _ptr(x), _ptr(w_gate_up), _ptr(None),
                                                      _ptr(out), M, 2 * I, K, self._stream()), "gate_up_act (skinny)")
             return
+        if interleaved and self._tcgen05(x, w_gate_up, out):
+            self.launches += 1
+            _check(self._gemm_tc.kvb_gemm_tcgen05(_dtype_code(out.dtype), 1, _ptr(x), _ptr(w_gate_up), _ptr(None), _ptr(out), M,
+                                                  2 * I, K, _ptr(self.error_word), self._stream()), "gate_up_act (tcgen05)")
+            return
         gate_up = workspace.buffer("ffn.gate_up", (M, 2 * I), out.dtype)
         self.linear(x, w_gate_up, gate_up)
         self.silu_mul(gate_up, out, interleaved)
@@ -205,6 +221,14 @@ class CudaKernels(KernelSet):
 
     def _skinny(self, dtype: torch.dtype, M: int, K: int) -> bool:
         return self.skinny_gemm and dtype == torch.bfloat16 and M <= self.SKINNY_MAX_ROWS and K % 32 == 0
+
+    def _tcgen05(self, x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> bool:
+        """The tensor-memory kernel takes bfloat16 operands whose rows are multiples of 16 bytes."""
+        if x.dtype != torch.bfloat16 or w.shape[1] % 8 != 0 or (x.data_ptr() | w.data_ptr() | out.data_ptr()) % 16 != 0:
+            return False
+        if self.bf16_gemm == "auto":
+            return -(-x.shape[0] // 128) * -(-w.shape[0] // 256) >= self.sm_count
+        return self.bf16_gemm == "tcgen05"
 
     def linear(self, x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bias: Optional[torch.Tensor] = None) -> None:
         """out = x . w^T + bias."""
@@ -217,7 +241,11 @@ class CudaKernels(KernelSet):
             _check(self._gemm_skinny.kvb_gemm_skinny(_dtype_code(out.dtype), 0, _ptr(x), _ptr(w), _ptr(bias),
                                                      _ptr(out), M, N, K, self._stream()), "linear (skinny)")
             return
-        if x.dtype == torch.bfloat16 and self.bf16_gemm == "cublas":
+        if self._tcgen05(x, w, out):
+            _check(self._gemm_tc.kvb_gemm_tcgen05(_dtype_code(out.dtype), 0, _ptr(x), _ptr(w), _ptr(bias), _ptr(out), M, N, K,
+                                                  _ptr(self.error_word), self._stream()), "linear (tcgen05)")
+            return
+        if x.dtype == torch.bfloat16 and self.bf16_gemm != "simt":
             # Library matrix product, as the reference's cublasGemmEx (apps/qwen_serve.cu:27-39).
             if out.dtype == torch.bfloat16:
                 torch.matmul(x, w.t(), out=out)

@@ -32,6 +32,7 @@ MODULES: Dict[str, dict] = {
     "gemm_simt": {"src": "gemm_simt.cu", "deps": ["common.cuh"]},
     "sampling": {"src": "sampling.cu", "deps": ["common.cuh"]},
     "gemm_skinny": {"src": "gemm_skinny.cu", "deps": ["common.cuh"]},
+    "gemm_tcgen05": {"src": "gemm_tcgen05.cu", "deps": ["common.cuh"]},
     # Compiled per head size: variant "d<head_dim>" with -DKVB_HEAD_DIM=<head_dim>.
     "attention_flash": {"src": "attention_flash.cu", "deps": ["common.cuh", "flash_core.cuh"]},
 }

@@ -159,6 +159,54 @@ def test_gemm_skinny_rows_do_not_depend_on_the_batch(kernels, request):
         assert torch.equal(part, full[:M]), M
 
 
+TC_SHAPES = [(128, 128, 64), (128, 128, 128), (2048, 1152, 896), (300, 896, 4864), (17, 331, 120), (129, 130, 72),
+             (1, 64, 8), (250, 9728, 896), (64, 151936, 896), (1000, 200, 200)]
+
+
+@pytest.mark.parametrize("M,N,K", TC_SHAPES)
+def test_gemm_tcgen05(M, N, K):
+    """The tensor-memory kernel against float64 on the same bfloat16 inputs: whole tiles, ragged edges in M, N
+    and K, one row, many K blocks (more than the ring has stages)."""
+    from kvcache_b200.kernels.api import CudaKernels
+    k = CudaKernels(DEV, bf16_gemm="tcgen05")
+    k.skinny_gemm = False
+    g = torch.Generator().manual_seed(19)
+    x = torch.randn(M, K, generator=g).to(torch.bfloat16)
+    w = torch.randn(N, K, generator=g).to(torch.bfloat16)
+    bias = torch.randn(N, generator=g)
+    xd, wd = x.to(DEV), w.to(DEV)
+    for out_dtype in (torch.bfloat16, torch.float32):
+        for b in (None, bias):
+            if N > 100000 and b is not None:
+                continue
+            out = torch.full((M, N), float("nan"), dtype=out_dtype, device=DEV)
+            assert k._tcgen05(xd, wd, out)
+            k.linear(xd, wd, out, b.to(DEV) if b is not None else None)
+            k.check_errors()
+            want = x.double() @ w.double().t() + (b.double() if b is not None else 0)
+            assert_close(out, want, REL[out_dtype])
+
+
+@pytest.mark.parametrize("M,I,K", [(128, 64, 64), (300, 4864, 896), (77, 200, 120), (2048, 320, 96)])
+def test_gemm_tcgen05_gated(M, I, K):
+    from kvcache_b200.engine.workspace import Workspace
+    from kvcache_b200.kernels.api import CudaKernels
+    from kvcache_b200.parts.feedforward import GatedMLP
+    k = CudaKernels(DEV, bf16_gemm="tcgen05")
+    k.skinny_gemm = False
+    g = torch.Generator().manual_seed(20)
+    x = torch.randn(M, K, generator=g).to(torch.bfloat16)
+    wg, wu = (torch.randn(I, K, generator=g) * 0.2).to(torch.bfloat16), (torch.randn(I, K, generator=g) * 0.2).to(torch.bfloat16)
+    gate, up = x.double() @ wg.double().t(), x.double() @ wu.double().t()
+    want = gate / (1 + torch.exp(-gate)) * up
+    ffn = GatedMLP(K, I, activation="silu", prefix="m.", dtype="bfloat16")
+    ffn.bind({"m.gate_proj.weight": wg, "m.up_proj.weight": wu, "m.down_proj.weight": torch.zeros(K, I)}, torch.device(DEV))
+    out = torch.full((M, I), float("nan"), dtype=torch.bfloat16, device=DEV)
+    k.gate_up_act(x.to(DEV), ffn.w_gate_up, out, Workspace(DEV), ffn.interleaved)
+    k.check_errors()
+    assert_close(out, want, 1e-2)
+
+
 @pytest.mark.parametrize("M,N,K", [(1, 256, 64), (8, 1152, 896), (70, 136, 80), (200, 331, 120)])
 def test_linear_bf16_library(kernels, M, N, K):
     g = torch.Generator().manual_seed(4)
@@ -168,12 +216,12 @@ def test_linear_bf16_library(kernels, M, N, K):
         ref = torch.empty(M, N, dtype=out_dtype)
         REF.linear(x, w, ref)
         out = torch.empty(M, N, dtype=out_dtype, device=DEV)
-        saved = kernels.skinny_gemm
-        kernels.skinny_gemm = False
+        saved = kernels.skinny_gemm, kernels.bf16_gemm
+        kernels.skinny_gemm, kernels.bf16_gemm = False, "cublas"
         try:
             kernels.linear(x.to(DEV), w.to(DEV), out)
         finally:
-            kernels.skinny_gemm = saved
+            kernels.skinny_gemm, kernels.bf16_gemm = saved
         assert_close(out, ref, REL[out_dtype])
 
 
