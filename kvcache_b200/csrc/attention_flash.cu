@@ -347,3 +347,44 @@ KVB_API int kvb_flash_prefill(const void* q, void* out, const void* k_pages, con
     flash_prefill_kernel<<<grid, 128, smem, stream>>>(p);
     return kvb_launch_status();
 }
+
+// ---------------------------------------------------------------------------------------------
+// The same decode attention for callers that cannot allocate (see no_alloc.h).
+// ---------------------------------------------------------------------------------------------
+#include "no_alloc.h"
+
+// Scratch of kvb_flash_decode_static: partial results first, tickets in the last KVB_STATIC_TICKET_BYTES.
+// In host code this name is only a handle for cudaGetSymbolAddress, never a device address.
+static __device__ __align__(256) unsigned char kvb_static_scratch[KVB_STATIC_SCRATCH_BYTES];
+
+int kvb_flash_decode_static(const void* q, void* out, const void* k_pages, const void* v_pages, const int* block_table,
+                            int table_stride, const int* items, int n_items, const int* seg_q_start,
+                            const int* seg_q_len, const int* seg_kv_len, int Hq, int Hkv, int page_size, int window,
+                            int nsplit, float scale, cudaStream_t stream) {
+    constexpr int MAX_DEVICES = 64;
+    static unsigned char* base_of_device[MAX_DEVICES] = {nullptr};
+    if (n_items <= 0) return KVB_OK;
+    if (Hkv < 1 || nsplit < 1) return KVB_ERR_SHAPE;
+    const size_t floats = (size_t)n_items * Hkv * nsplit * 16 * (D + 2);
+    const size_t tickets = (size_t)n_items * Hkv;
+    if (floats * sizeof(float) > KVB_STATIC_SCRATCH_BYTES - KVB_STATIC_TICKET_BYTES ||
+        tickets * sizeof(int) > KVB_STATIC_TICKET_BYTES)
+        return KVB_ERR_STATIC_SCRATCH;
+    int device = 0;
+    cudaError_t e = cudaGetDevice(&device);
+    if (e != cudaSuccess) return (int)e;
+    if (device < 0 || device >= MAX_DEVICES) return KVB_ERR_LIMIT;
+    if (!base_of_device[device]) {   // set-up, once per device, with that device current
+        unsigned char* base = nullptr;
+        e = cudaGetSymbolAddress((void**)&base, kvb_static_scratch);
+        if (e != cudaSuccess) return (int)e;
+        base_of_device[device] = base;
+    }
+    unsigned char* base = base_of_device[device];
+    int* ticket_ptr = reinterpret_cast<int*>(base + (KVB_STATIC_SCRATCH_BYTES - KVB_STATIC_TICKET_BYTES));
+    e = cudaMemsetAsync(ticket_ptr, 0, tickets * sizeof(int), stream);   // tickets start at zero, whatever the last call left
+    if (e != cudaSuccess) return (int)e;
+    return kvb_flash_decode(q, out, k_pages, v_pages, block_table, table_stride, items, n_items, seg_q_start, seg_q_len,
+                            seg_kv_len, reinterpret_cast<float*>(base), ticket_ptr, Hq, Hkv, page_size, window, nsplit,
+                            scale, stream);
+}
