@@ -101,9 +101,11 @@ def layer_window(config: dict, layer: int) -> Optional[int]:
 
 
 def block(x: torch.Tensor, weights: Dict[str, torch.Tensor], config: dict, layer: int,
-          positions: torch.Tensor) -> torch.Tensor:
+          positions: torch.Tensor, shared_kv=None, kv_out: Optional[list] = None) -> torch.Tensor:
     """One layer in the reference's order (apps/qwen_serve.cu:101-116): norm, q/k/v with bias,
-    rotation of q and k, attention, o_proj, residual, norm, gated feed-forward, residual."""
+    rotation of q and k, attention, o_proj, residual, norm, gated feed-forward, residual.
+    `shared_kv`: (k, v) of another layer call to attend to instead of this call's own;
+    `kv_out`: a list that receives this call's rotated keys and values."""
     p = f"model.layers.{layer}."
     Hq, Hkv = config["num_attention_heads"], config.get("num_key_value_heads", config["num_attention_heads"])
     D = config.get("head_dim") or config["hidden_size"] // Hq
@@ -114,6 +116,10 @@ def block(x: torch.Tensor, weights: Dict[str, torch.Tensor], config: dict, layer
     k = linear(n, weights[p + "self_attn.k_proj.weight"], weights[p + "self_attn.k_proj.bias"]).view(T, Hkv, D)
     v = linear(n, weights[p + "self_attn.v_proj.weight"], weights[p + "self_attn.v_proj.bias"]).view(T, Hkv, D)
     q, k = rope(q, positions, theta), rope(k, positions, theta)
+    if kv_out is not None:
+        kv_out.append((k, v))
+    if shared_kv is not None:
+        k, v = shared_kv
     a = attention(q, k, v, layer_window(config, layer)).reshape(T, Hq * D)
     x = x + linear(a, weights[p + "self_attn.o_proj.weight"])
     n = rms_norm(x, weights[p + "post_attention_layernorm.weight"], eps)

@@ -111,3 +111,68 @@ def test_batch_composition_does_not_change_logits(tmp_path, kernels, dtype):
                StepEntry(slots[2], others[1], [0]), StepEntry(slots[3], others[2], [])]
     together = runner.step(entries).clone()[:40]
     assert_close(together, alone, 1e-5 if dtype == "float32" else 2e-2)
+
+
+SHARPEN = {"B": 10.0, "C": 3.0}
+
+
+def _sharpened_folder(tmp_path, name):
+    """A tiny model whose query and key projections are scaled up, so that the softmax of every layer is peaked:
+    each row's output hangs on a few keys, often far away, and a key that is lost, doubled or taken from the wrong
+    page (a page's edge, a page that was used before, the far edge of a window) moves the logits by far more than
+    rounding - with plain random weights attention is nearly uniform and would average such a fault away.
+    The factors are chosen so that the plain implementation run in float32 still agrees with itself in float64
+    to better than 1e-5 (a sharper model amplifies float32 rounding itself), while changing one token anywhere in
+    the prompt moves the last logits by 5e-2 or more of their size."""
+    factor = SHARPEN[name]
+    from safetensors.torch import load_file, save_file
+    import os
+    folder = make_model_folder(tmp_path, name, seed=5, dtype=torch.bfloat16)
+    path = os.path.join(folder, "model.safetensors")
+    tensors = load_file(path)
+    for key in list(tensors):
+        if key.endswith("q_proj.weight") or key.endswith("k_proj.weight"):
+            tensors[key] = (tensors[key].float() * factor).to(torch.bfloat16)
+    save_file(tensors, path)
+    return folder
+
+
+@pytest.mark.parametrize("name", ["B", "C"])
+def test_sharp_attention_over_many_pages(tmp_path, kernels, name):
+    """float32 only: in bfloat16 the same sharpness amplifies the rounding of activations to the size of the
+    effect looked for; the bfloat16 attention kernels meet their far keys and window edges in test_kernels_gpu."""
+    dtype = "float32"
+    folder = _sharpened_folder(tmp_path, name)
+    config, weights = read_folder(folder)
+    runner = make_runner(folder, kernels, dtype=dtype, device=DEV, page_size=PAGE_SIZE[name], num_pages=80,
+                         max_tokens_per_step=512)
+    tokens = random_tokens(config["vocab_size"], 420, 8)
+    want = logits_of(config, weights, tokens)
+    # The plain model's attention really is peaked: otherwise this test shows nothing.
+    for far in (5, 200, 390):
+        probe = logits_of(config, weights, tokens[:far] + [(tokens[far] + 1) % config["vocab_size"]] + tokens[far + 1:])
+        assert (probe[-1] - want[-1]).abs().max() > 2e-2 * want[-1].abs().max()
+    rel = 1e-4
+    assert_close(replay_modes.whole(runner, tokens), want, rel, "whole")
+    assert_close(replay_modes.last_32_one_by_one(runner, tokens), want[-33:], rel, "one by one")
+    assert_close(replay_modes.portions(runner, tokens, [130, 2, 61, 7, 64, 3, 120, 33]), want, rel, "portions")
+    # Two requests side by side after the pages above were given back: every page they get was used before.
+    other = random_tokens(config["vocab_size"], 200, 9)
+    from kvcache_b200.engine.runner import StepEntry
+    a, b = runner.cache.admit(), runner.cache.admit()
+    got_a, got_b = [], []
+    at_a = at_b = 0
+    for na, nb in [(100, 1), (1, 150), (200, 2), (1, 47), (118, 0)]:
+        entries, parts = [], []
+        if na:
+            entries.append(StepEntry(a, tokens[at_a:at_a + na], list(range(na)))); parts.append(("a", na)); at_a += na
+        if nb:
+            entries.append(StepEntry(b, other[at_b:at_b + nb], list(range(nb)))); parts.append(("b", nb)); at_b += nb
+        out = runner.step(entries).clone()
+        at = 0
+        for who, n in parts:
+            (got_a if who == "a" else got_b).append(out[at:at + n]); at += n
+    assert at_a == 420 and at_b == 200
+    assert_close(torch.cat(got_a), want, rel, "mixed a")
+    assert_close(torch.cat(got_b), logits_of(config, weights, other), rel, "mixed b")
+    kernels.check_errors()

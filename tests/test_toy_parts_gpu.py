@@ -1,0 +1,159 @@
+"""A toy architecture defined here, in the test: a mixer with per-request state of its own, another position
+encoding, a layer of each kind - registered, built from a folder and stepped with no change to the framework."""
+import json
+import os
+from dataclasses import dataclass
+from typing import Any, Dict, Mapping
+
+import pytest
+import torch
+
+from helpers import assert_close
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+def _define():
+    from kvcache_b200.config.base import KeyReader, ModelConfig
+    from kvcache_b200.parts import (DecoderModel, GatedMLP, GQAAttention, LayerCall, Mixer, PositionEncoding, PreNormBlock,
+                                    RMSNorm, StateSpec)
+    from kvcache_b200.weights import TensorSpec
+
+    @dataclass(frozen=True)
+    class ToyConfig(ModelConfig):
+        width: int
+        vocab: int
+        inner: int
+        decay: float
+        eps: float
+
+        @classmethod
+        def from_dict(cls, data, where="config.json"):
+            r = KeyReader(data, where)
+            out = cls("ToyRunningMeanLM", r.integer("width"), r.integer("vocab"), r.integer("inner"), r.number("decay"),
+                      r.number("eps"))
+            r.finish()
+            return out
+
+        def to_dict(self) -> Dict[str, Any]:
+            return {"architectures": [self.architecture], "width": self.width, "vocab": self.vocab, "inner": self.inner,
+                    "decay": self.decay, "eps": self.eps}
+
+    class RunningMean(Mixer):
+        """delta[r] = W . s[r], s[r] = decay * s[r - 1] + x[r] over the request's rows: a state of fixed size that
+        has to survive from step to step, in the slot the cache manager gave the request."""
+
+        def __init__(self, width, decay, prefix, dtype):
+            self.width, self.decay, self.prefix, self.dtype = width, decay, prefix, dtype
+            self.w = None
+
+        def tensor_specs(self):
+            return {self.prefix + "mix.weight": TensorSpec((self.width, self.width))}
+
+        def bind(self, tensors: Mapping[str, torch.Tensor], device):
+            self.w = tensors[self.prefix + "mix.weight"].to(torch.float32).to(device)
+
+        def state_spec(self):
+            return StateSpec((self.width,), "float32")
+
+        def forward(self, x, ctx):
+            out = torch.empty_like(x)
+            host = ctx.batch.host
+            for start, count, slot in zip(host["q_start"], host["counts"], host["slots"]):
+                s = ctx.state[slot]
+                for r in range(start, start + count):
+                    s.mul_(self.decay).add_(x[r].float())
+                    out[r] = (self.w @ s).to(x.dtype)
+            return out
+
+    class AddedSinusoid(PositionEncoding):
+        """Adds sin(pos / 10) to every element of the embedded row: an encoding that acts at the embedding."""
+
+        def on_embed(self, h, ctx):
+            h.add_(torch.sin(ctx.batch.positions.float() / 10.0)[:, None])
+
+    def build(config, dtype="float32", device="cuda:0", max_positions=None):
+        c = config
+        blocks = [
+            PreNormBlock(c.width, RMSNorm(c.width, c.eps, "l0.n1"), RunningMean(c.width, c.decay, "l0.", dtype),
+                         RMSNorm(c.width, c.eps, "l0.n2"), GatedMLP(c.width, c.inner, activation="silu", prefix="l0.f.", dtype=dtype), dtype),
+            PreNormBlock(c.width, RMSNorm(c.width, c.eps, "l1.n1"),
+                         GQAAttention(c.width, 2, 1, c.width // 2, qkv_bias=False, out_bias=False, position=None, window=None,
+                                      prefix="l1.a.", dtype=dtype),
+                         RMSNorm(c.width, c.eps, "l1.n2"), GatedMLP(c.width, c.inner, activation="silu", prefix="l1.f.", dtype=dtype), dtype),
+        ]
+        return DecoderModel(config=c, dtype=dtype, vocab_size=c.vocab, width=c.width, embed_name="emb", head_name=None,
+                            blocks=blocks, schedule=[LayerCall(0, 0), LayerCall(1, 1)],
+                            final_norm=RMSNorm(c.width, c.eps, "final"), position=AddedSinusoid())
+
+    return ToyConfig, build
+
+
+def _plain(config, w, tokens):
+    """The toy model on one whole sequence, in float64."""
+    import plain_qwen2 as plain
+    W = {k: v.double() for k, v in w.items()}
+    T = len(tokens)
+    x = W["emb"][torch.tensor(tokens)] + torch.sin(torch.arange(T).double() / 10.0)[:, None]
+    n = plain.rms_norm(x, W["l0.n1"], config["eps"])
+    s, mixed = torch.zeros(config["width"], dtype=torch.float64), []
+    for r in range(T):
+        s = config["decay"] * s + n[r]
+        mixed.append(W["l0.mix.weight"] @ s)
+    x = x + torch.stack(mixed)
+    x = x + plain.swiglu(plain.rms_norm(x, W["l0.n2"], config["eps"]), W["l0.f.gate_proj.weight"], W["l0.f.up_proj.weight"],
+                         W["l0.f.down_proj.weight"])
+    n = plain.rms_norm(x, W["l1.n1"], config["eps"])
+    D = config["width"] // 2
+    q = plain.linear(n, W["l1.a.q_proj.weight"]).view(T, 2, D)
+    k = plain.linear(n, W["l1.a.k_proj.weight"]).view(T, 1, D)
+    v = plain.linear(n, W["l1.a.v_proj.weight"]).view(T, 1, D)
+    x = x + plain.linear(plain.attention(q, k, v).reshape(T, 2 * D), W["l1.a.o_proj.weight"])
+    x = x + plain.swiglu(plain.rms_norm(x, W["l1.n2"], config["eps"]), W["l1.f.gate_proj.weight"], W["l1.f.up_proj.weight"],
+                         W["l1.f.down_proj.weight"])
+    return plain.linear(plain.rms_norm(x, W["final"], config["eps"]), W["emb"])
+
+
+def test_toy_architecture_with_state_runs_through_the_unchanged_engine(tmp_path):
+    from safetensors.torch import load_file
+    from kvcache_b200.config import EngineOptions, register_architecture, unregister_architecture
+    from kvcache_b200.engine.core import EngineCore
+    from kvcache_b200.engine.runner import StepEntry
+    from kvcache_b200.weights import write_random_model
+    ToyConfig, build = _define()
+    register_architecture("ToyRunningMeanLM", ToyConfig, build)
+    try:
+        data = {"architectures": ["ToyRunningMeanLM"], "width": 32, "vocab": 50, "inner": 40, "decay": 0.8, "eps": 1e-5}
+        folder = write_random_model(os.path.join(tmp_path, "toy"), ToyConfig.from_dict(data), seed=1, dtype=torch.float32)
+        with open(os.path.join(folder, "config.json")) as fh:
+            assert json.load(fh)["architectures"] == ["ToyRunningMeanLM"]
+        weights = load_file(os.path.join(folder, "model.safetensors"))
+        core = EngineCore(folder, EngineOptions(dtype="float32", page_size=8, num_pages=16, max_running=2,
+                                                max_tokens_per_step=64, max_model_len=64, use_graphs=False))
+        entries = core.model.cache_entries()
+        assert entries[0].kv is None and entries[0].state.shape == (32,)       # the toy mixer: state, no pages
+        assert entries[1].kv is not None and entries[1].state is None          # attention: pages, no state
+        assert core.cache.states[0].shape == (2, 32)
+        a = [3, 14, 15, 9, 2, 6, 5, 35, 8, 9, 7, 9, 3, 2, 38, 4, 6]
+        b = [27, 18, 28, 18, 2, 8, 4, 5, 9, 0, 45]
+        want_a, want_b = _plain(data, weights, a), _plain(data, weights, b)
+        sa, sb = core.cache.admit(), core.cache.admit()
+        got_a, got_b = [], []
+        # a in portions and then token by token, b beside it: the state has to be carried in a's slot.
+        out = core.runner.step([StepEntry(sa, a[:5], range(5)), StepEntry(sb, b[:3], range(3))]).clone()
+        got_a.append(out[:5]); got_b.append(out[5:])
+        out = core.runner.step([StepEntry(sb, b[3:], range(8)), StepEntry(sa, a[5:7], range(2))]).clone()
+        got_b.append(out[:8]); got_a.append(out[8:])
+        for i in range(7, len(a)):
+            got_a.append(core.runner.step([StepEntry(sa, a[i:i + 1], [0])]).clone())
+        assert_close(torch.cat(got_a), want_a, 1e-4, "a")
+        assert_close(torch.cat(got_b), want_b, 1e-4, "b")
+        # A slot that is used again starts from a zeroed state.
+        core.cache.release(sa)
+        sc = core.cache.admit()
+        assert sc == sa and float(core.cache.states[0][sc].abs().sum()) == 0.0
+        again = core.runner.step([StepEntry(sc, b, range(len(b)))]).clone()
+        assert_close(again, want_b, 1e-4, "b in a's old slot")
+    finally:
+        unregister_architecture("ToyRunningMeanLM")
