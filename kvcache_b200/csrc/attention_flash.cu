@@ -42,6 +42,8 @@ struct DecodeParams {
 constexpr int MAX_SPLITS = 32;
 
 __global__ void __launch_bounds__(128) flash_decode_kernel(const DecodeParams p) {
+    pdl_wait();
+    pdl_launch_dependents();
     extern __shared__ __align__(16) unsigned char smem_raw[];
     bf16* smem = reinterpret_cast<bf16*>(smem_raw);
     __shared__ int ticket_s;
@@ -237,7 +239,7 @@ KVB_API int kvb_flash_decode(const void* q, void* out, const void* k_pages, cons
         configured = true;
     }
     dim3 grid(nsplit, Hkv, n_items);
-    flash_decode_kernel<<<grid, 128, smem, stream>>>(p);
+    kvb_launch(flash_decode_kernel, dim3(grid), dim3(128), smem, stream, p);
     return kvb_launch_status();
 }
 
@@ -261,6 +263,8 @@ struct PrefillParams {
 };
 
 __global__ void __launch_bounds__(128) flash_prefill_kernel(const PrefillParams p) {
+    pdl_wait();
+    pdl_launch_dependents();
     extern __shared__ __align__(16) unsigned char smem_raw[];
     bf16* smem = reinterpret_cast<bf16*>(smem_raw);
     const int tile = blockIdx.x, h = blockIdx.y;
@@ -344,7 +348,7 @@ KVB_API int kvb_flash_prefill(const void* q, void* out, const void* k_pages, con
         configured = true;
     }
     dim3 grid(n_tiles, Hq);
-    flash_prefill_kernel<<<grid, 128, smem, stream>>>(p);
+    kvb_launch(flash_prefill_kernel, dim3(grid), dim3(128), smem, stream, p);
     return kvb_launch_status();
 }
 

@@ -23,6 +23,8 @@ __global__ void paged_attention_generic_kernel(const T* __restrict__ q, const T*
                                                const int* __restrict__ row_segment, T* __restrict__ out, int Hq,
                                                int Hkv, int D, int page_size, int window, float scale,
                                                int* __restrict__ err) {
+    pdl_wait();
+    pdl_launch_dependents();
     extern __shared__ float smem[];
     float* q_s = smem;                    // [D]
     float* p_s = smem + D;                // [ATTN_THREADS]
@@ -103,11 +105,11 @@ KVB_API int kvb_paged_attention_generic(int dtype, const void* q, const void* k_
     const size_t smem = (size_t)(D + 2 * ATTN_THREADS + 33) * sizeof(float);
     dim3 grid(T, Hq);
     if (dtype == KVB_F32)
-        paged_attention_generic_kernel<float><<<grid, ATTN_THREADS, smem, stream>>>(
+        kvb_launch(paged_attention_generic_kernel<float>, dim3(grid), dim3(ATTN_THREADS), smem, stream, 
             (const float*)q, (const float*)k_pages, (const float*)v_pages, block_table, table_stride, positions,
             row_segment, (float*)out, Hq, Hkv, D, page_size, window, scale, err);
     else if (dtype == KVB_BF16)
-        paged_attention_generic_kernel<bf16><<<grid, ATTN_THREADS, smem, stream>>>(
+        kvb_launch(paged_attention_generic_kernel<bf16>, dim3(grid), dim3(ATTN_THREADS), smem, stream, 
             (const bf16*)q, (const bf16*)k_pages, (const bf16*)v_pages, block_table, table_stride, positions,
             row_segment, (bf16*)out, Hq, Hkv, D, page_size, window, scale, err);
     else

@@ -79,6 +79,41 @@ __device__ __forceinline__ float block_max(float v, float* scratch) {
     return scratch[32];
 }
 
+// Programmatic dependent launch: a kernel launched with `kvb_launch` may be placed on the SMs while the
+// kernel before it in the stream is still running; everything it does before `pdl_wait()` (parameter reads,
+// prefetching weights, which no kernel writes) overlaps the predecessor's tail, and `pdl_wait()` returns only
+// when the predecessor has completed and its writes are visible.  `pdl_launch_dependents()` lets the successor
+// be placed as soon as every block of this kernel has started.  Kernels launched the ordinary way see both as
+// no-ops.  KVB_PDL=0 in the environment turns the attribute off.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+#include <stdlib.h>
+static inline bool kvb_pdl_enabled() {
+    static int enabled = -1;
+    if (enabled < 0) {
+        const char* v = getenv("KVB_PDL");
+        enabled = (v && v[0] == '0') ? 0 : 1;
+    }
+    return enabled == 1;
+}
+
+template <typename... KArgs, typename... Args>
+static inline cudaError_t kvb_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                     Args... args) {
+    cudaLaunchConfig_t config = {};
+    config.gridDim = grid;
+    config.blockDim = block;
+    config.dynamicSmemBytes = smem;
+    config.stream = stream;
+    cudaLaunchAttribute attribute[1];
+    attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attribute[0].val.programmaticStreamSerializationAllowed = 1;
+    config.attrs = attribute;
+    config.numAttrs = kvb_pdl_enabled() ? 1 : 0;
+    return cudaLaunchKernelEx(&config, kernel, static_cast<KArgs>(args)...);
+}
+
 static inline int kvb_launch_status() {
     cudaError_t e = cudaGetLastError();
     return e == cudaSuccess ? KVB_OK : (int)e;

@@ -10,6 +10,8 @@
 template <typename T>
 __global__ void embed_kernel(const T* __restrict__ table, const int* __restrict__ ids, float* __restrict__ out,
                              int H, int V, int* __restrict__ err) {
+    pdl_wait();
+    pdl_launch_dependents();
     const int r = blockIdx.x;
     const int tok = ids[r];
     float* dst = out + (size_t)r * H;
@@ -27,9 +29,9 @@ KVB_API int kvb_embed(int dtype, const void* table, const int* ids, float* out, 
     if (T <= 0) return KVB_OK;
     const int threads = H >= 512 ? 256 : 128;
     if (dtype == KVB_F32)
-        embed_kernel<float><<<T, threads, 0, stream>>>((const float*)table, ids, out, H, V, err);
+        kvb_launch(embed_kernel<float>, dim3(T), dim3(threads), 0, stream, (const float*)table, ids, out, H, V, err);
     else if (dtype == KVB_BF16)
-        embed_kernel<bf16><<<T, threads, 0, stream>>>((const bf16*)table, ids, out, H, V, err);
+        kvb_launch(embed_kernel<bf16>, dim3(T), dim3(threads), 0, stream, (const bf16*)table, ids, out, H, V, err);
     else
         return KVB_ERR_DTYPE;
     return kvb_launch_status();
@@ -43,6 +45,8 @@ KVB_API int kvb_embed(int dtype, const void* table, const int* ids, float* out, 
 template <typename T>
 __global__ void add_rmsnorm_kernel(float* __restrict__ h, const T* __restrict__ delta, const float* __restrict__ w,
                                    T* __restrict__ out, const int* __restrict__ rows, int H, float eps) {
+    pdl_wait();
+    pdl_launch_dependents();
     __shared__ float scratch[33];
     const int o = blockIdx.x;
     const int r = rows ? rows[o] : o;
@@ -90,6 +94,8 @@ template <> struct Vec4<bf16> {
 template <typename T>
 __global__ void add_rmsnorm_vec_kernel(float* __restrict__ h, const T* __restrict__ delta, const float* __restrict__ w,
                                        T* __restrict__ out, const int* __restrict__ rows, int H, float eps) {
+    pdl_wait();
+    pdl_launch_dependents();
     __shared__ float scratch[33];
     const int o = blockIdx.x;
     const int r = rows ? rows[o] : o;
@@ -126,17 +132,17 @@ KVB_API int kvb_add_rmsnorm(int dtype, float* h, const void* delta, const float*
     const int threads = H >= 2048 ? 512 : (H >= 512 ? 256 : 128);
     const bool vec = H % 4 == 0 && ((((uintptr_t)h | (uintptr_t)w | (uintptr_t)out | (uintptr_t)delta) & 15) == 0);
     if (vec && dtype == KVB_F32) {
-        add_rmsnorm_vec_kernel<float><<<n_out, threads / 2, 0, stream>>>(h, (const float*)delta, w, (float*)out, rows, H, eps);
+        kvb_launch(add_rmsnorm_vec_kernel<float>, dim3(n_out), dim3(threads / 2), 0, stream, h, (const float*)delta, w, (float*)out, rows, H, eps);
         return kvb_launch_status();
     }
     if (vec && dtype == KVB_BF16) {
-        add_rmsnorm_vec_kernel<bf16><<<n_out, threads / 2, 0, stream>>>(h, (const bf16*)delta, w, (bf16*)out, rows, H, eps);
+        kvb_launch(add_rmsnorm_vec_kernel<bf16>, dim3(n_out), dim3(threads / 2), 0, stream, h, (const bf16*)delta, w, (bf16*)out, rows, H, eps);
         return kvb_launch_status();
     }
     if (dtype == KVB_F32)
-        add_rmsnorm_kernel<float><<<n_out, threads, 0, stream>>>(h, (const float*)delta, w, (float*)out, rows, H, eps);
+        kvb_launch(add_rmsnorm_kernel<float>, dim3(n_out), dim3(threads), 0, stream, h, (const float*)delta, w, (float*)out, rows, H, eps);
     else if (dtype == KVB_BF16)
-        add_rmsnorm_kernel<bf16><<<n_out, threads, 0, stream>>>(h, (const bf16*)delta, w, (bf16*)out, rows, H, eps);
+        kvb_launch(add_rmsnorm_kernel<bf16>, dim3(n_out), dim3(threads), 0, stream, h, (const bf16*)delta, w, (bf16*)out, rows, H, eps);
     else
         return KVB_ERR_DTYPE;
     return kvb_launch_status();
@@ -147,6 +153,8 @@ KVB_API int kvb_add_rmsnorm(int dtype, float* h, const void* delta, const float*
 // gate i at column 16 (i / 8) + i % 8 and up i eight columns further.
 template <typename T>
 __global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, int I, size_t total, int interleaved) {
+    pdl_wait();
+    pdl_launch_dependents();
     for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
          idx += (size_t)gridDim.x * blockDim.x) {
         const size_t r = idx / I;
@@ -160,6 +168,8 @@ __global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, i
 
 // Eight outputs per thread and step: 16-byte loads of gate and up, one 16-byte (bfloat16) store.
 __global__ void silu_mul_vec8_kernel(const bf16* __restrict__ gu, bf16* __restrict__ out, int I, size_t groups, int interleaved) {
+    pdl_wait();
+    pdl_launch_dependents();
     const int per_row = I >> 3;
     for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < groups; idx += (size_t)gridDim.x * blockDim.x) {
         const size_t r = idx / per_row;
@@ -191,13 +201,13 @@ KVB_API int kvb_silu_mul(int dtype, const void* gate_up, void* out, int T, int I
         const size_t groups = total / 8;
         size_t vblocks = (groups + threads - 1) / threads;
         if (vblocks > 148 * 16) vblocks = 148 * 16;
-        silu_mul_vec8_kernel<<<(int)vblocks, threads, 0, stream>>>((const bf16*)gate_up, (bf16*)out, I, groups, interleaved);
+        kvb_launch(silu_mul_vec8_kernel, dim3((int)vblocks), dim3(threads), 0, stream, (const bf16*)gate_up, (bf16*)out, I, groups, interleaved);
         return kvb_launch_status();
     }
     if (dtype == KVB_F32)
-        silu_mul_kernel<float><<<(int)blocks, threads, 0, stream>>>((const float*)gate_up, (float*)out, I, total, interleaved);
+        kvb_launch(silu_mul_kernel<float>, dim3((int)blocks), dim3(threads), 0, stream, (const float*)gate_up, (float*)out, I, total, interleaved);
     else if (dtype == KVB_BF16)
-        silu_mul_kernel<bf16><<<(int)blocks, threads, 0, stream>>>((const bf16*)gate_up, (bf16*)out, I, total, interleaved);
+        kvb_launch(silu_mul_kernel<bf16>, dim3((int)blocks), dim3(threads), 0, stream, (const bf16*)gate_up, (bf16*)out, I, total, interleaved);
     else
         return KVB_ERR_DTYPE;
     return kvb_launch_status();

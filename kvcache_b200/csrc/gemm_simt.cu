@@ -19,6 +19,8 @@ template <typename TIn, typename TOut>
 __global__ void __launch_bounds__(256) gemm_simt_kernel(const TIn* __restrict__ x, const TIn* __restrict__ w,
                                                         const float* __restrict__ bias, TOut* __restrict__ y, int M,
                                                         int N, int K) {
+    pdl_wait();
+    pdl_launch_dependents();
     __shared__ float xs[BK][BM + 4];
     __shared__ float ws[BK][BN + 4];
     const int tid = threadIdx.x;
@@ -83,11 +85,11 @@ KVB_API int kvb_gemm_simt(int in_dtype, int out_dtype, const void* x, const void
     dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
     if (grid.y > 65535) return KVB_ERR_LIMIT;
     if (in_dtype == KVB_F32 && out_dtype == KVB_F32)
-        gemm_simt_kernel<float, float><<<grid, 256, 0, stream>>>((const float*)x, (const float*)w, bias, (float*)y, M, N, K);
+        kvb_launch(gemm_simt_kernel<float, float>, dim3(grid), dim3(256), 0, stream, (const float*)x, (const float*)w, bias, (float*)y, M, N, K);
     else if (in_dtype == KVB_BF16 && out_dtype == KVB_BF16)
-        gemm_simt_kernel<bf16, bf16><<<grid, 256, 0, stream>>>((const bf16*)x, (const bf16*)w, bias, (bf16*)y, M, N, K);
+        kvb_launch(gemm_simt_kernel<bf16, bf16>, dim3(grid), dim3(256), 0, stream, (const bf16*)x, (const bf16*)w, bias, (bf16*)y, M, N, K);
     else if (in_dtype == KVB_BF16 && out_dtype == KVB_F32)
-        gemm_simt_kernel<bf16, float><<<grid, 256, 0, stream>>>((const bf16*)x, (const bf16*)w, bias, (float*)y, M, N, K);
+        kvb_launch(gemm_simt_kernel<bf16, float>, dim3(grid), dim3(256), 0, stream, (const bf16*)x, (const bf16*)w, bias, (float*)y, M, N, K);
     else
         return KVB_ERR_DTYPE;
     return kvb_launch_status();

@@ -45,6 +45,20 @@ __global__ void __launch_bounds__(256) gemm_skinny_kernel(const bf16* __restrict
     const int per_warp = (kblocks + warps - 1) / warps;
     const int kb_begin = min(kblocks, warp * per_warp), kb_end = min(kblocks, kb_begin + per_warp);
 
+    // Before waiting for the kernel that makes x: pull this warp's slice of the weights (which no kernel
+    // writes) towards L2, so that the predecessor's tail and this kernel's memory latency overlap.
+    {
+        const int slice_bytes = (kb_end - kb_begin) * 64;
+        const int lines = (slice_bytes + 127) / 128;
+        for (int i = lane; i < 16 * RT * lines; i += 32) {
+            const int row = min(N - 1, n0 + i / lines);
+            const char* p = reinterpret_cast<const char*>(w + (size_t)row * K + kb_begin * 32) + (i % lines) * 128;
+            asm volatile("prefetch.global.L2 [%0];" ::"l"(p));
+        }
+    }
+    pdl_wait();
+    pdl_launch_dependents();
+
     float acc[RT][NT][4];
 #pragma unroll
     for (int r = 0; r < RT; ++r)
@@ -145,7 +159,7 @@ int launch(const bf16* x, const bf16* w, const float* bias, TOut* y, int M, int 
         if (e != cudaSuccess) return (int)e;
     }
     const int blocks = (N + 16 * RT - 1) / (16 * RT);
-    kernel<<<blocks, warps * 32, smem, stream>>>(x, w, bias, y, M, N, K, x_stride);
+    kvb_launch(kernel, dim3(blocks), dim3(warps * 32), smem, stream, x, w, bias, y, M, N, K, x_stride);
     return kvb_launch_status();
 }
 

@@ -19,6 +19,8 @@ __global__ void qkv_rope_append_kernel(const T* __restrict__ qkv, const float* _
                                        int table_stride, T* __restrict__ k_pages, T* __restrict__ v_pages,
                                        T* __restrict__ q_out, int Hq, int Hkv, int D, int page_size, int write_kv,
                                        int* __restrict__ err) {
+    pdl_wait();
+    pdl_launch_dependents();
     const int r = blockIdx.x;
     const int width = (Hq + 2 * Hkv) * D;
     const int pos = positions[r];
@@ -75,6 +77,8 @@ __global__ void qkv_rope_append_vec8_kernel(const bf16* __restrict__ qkv, const 
                                             int table_stride, bf16* __restrict__ k_pages, bf16* __restrict__ v_pages,
                                             bf16* __restrict__ q_out, int Hq, int Hkv, int D, int page_size, int write_kv,
                                             int* __restrict__ err) {
+    pdl_wait();
+    pdl_launch_dependents();
     const int r = blockIdx.x;
     const int width = (Hq + 2 * Hkv) * D;
     const int pos = positions[r];
@@ -157,17 +161,17 @@ KVB_API int kvb_qkv_rope_append(int dtype, const void* qkv, const float* bias, c
     const int threads = width >= 1024 ? 256 : 128;
     const uintptr_t addresses = (uintptr_t)qkv | (uintptr_t)k_pages | (uintptr_t)v_pages | (uintptr_t)q_out;
     if (dtype == KVB_BF16 && D % 8 == 0 && rot_half % 8 == 0 && (addresses & 15) == 0) {
-        qkv_rope_append_vec8_kernel<<<T, width >= 2048 ? 256 : 128, 0, stream>>>(
+        kvb_launch(qkv_rope_append_vec8_kernel, dim3(T), dim3(width >= 2048 ? 256 : 128), 0, stream, 
             (const bf16*)qkv, bias, cos_t, sin_t, rot_half, table_len, positions, row_segment, block_table, table_stride,
             (bf16*)k_pages, (bf16*)v_pages, (bf16*)q_out, Hq, Hkv, D, page_size, write_kv, err);
         return kvb_launch_status();
     }
     if (dtype == KVB_F32)
-        qkv_rope_append_kernel<float><<<T, threads, 0, stream>>>(
+        kvb_launch(qkv_rope_append_kernel<float>, dim3(T), dim3(threads), 0, stream, 
             (const float*)qkv, bias, cos_t, sin_t, rot_half, table_len, positions, row_segment, block_table,
             table_stride, (float*)k_pages, (float*)v_pages, (float*)q_out, Hq, Hkv, D, page_size, write_kv, err);
     else if (dtype == KVB_BF16)
-        qkv_rope_append_kernel<bf16><<<T, threads, 0, stream>>>(
+        kvb_launch(qkv_rope_append_kernel<bf16>, dim3(T), dim3(threads), 0, stream, 
             (const bf16*)qkv, bias, cos_t, sin_t, rot_half, table_len, positions, row_segment, block_table,
             table_stride, (bf16*)k_pages, (bf16*)v_pages, (bf16*)q_out, Hq, Hkv, D, page_size, write_kv, err);
     else

@@ -38,6 +38,8 @@ __device__ __forceinline__ void better(float& bv, int& bi, float v, int i) {
 __global__ void sample_stage1_kernel(const float* __restrict__ logits, int V, const float* __restrict__ temperature,
                                      const unsigned long long* __restrict__ seeds, const int* __restrict__ counters,
                                      float* __restrict__ part_val, int* __restrict__ part_idx, int parts) {
+    pdl_wait();
+    pdl_launch_dependents();
     __shared__ float sv[256];
     __shared__ int si[256];
     const int row = blockIdx.y, part = blockIdx.x;
@@ -74,6 +76,8 @@ __global__ void sample_stage1_kernel(const float* __restrict__ logits, int V, co
 
 __global__ void sample_stage2_kernel(const float* __restrict__ part_val, const int* __restrict__ part_idx, int parts,
                                      int* __restrict__ out) {
+    pdl_wait();
+    pdl_launch_dependents();
     // One warp per row; parts <= 1024.
     const int row = blockIdx.x;
     float bv = -FLT_MAX; int bi = 0x7fffffff;
@@ -103,7 +107,7 @@ KVB_API int kvb_sample(const float* logits, int R, int V, const float* temperatu
     if (V <= 0) return KVB_ERR_SHAPE;
     const int parts = kvb_sample_parts(V);
     dim3 grid(parts, R);
-    sample_stage1_kernel<<<grid, 256, 0, stream>>>(logits, V, temperature, seeds, counters, part_val, part_idx, parts);
-    sample_stage2_kernel<<<R, 32, 0, stream>>>(part_val, part_idx, parts, out);
+    kvb_launch(sample_stage1_kernel, dim3(grid), dim3(256), 0, stream, logits, V, temperature, seeds, counters, part_val, part_idx, parts);
+    kvb_launch(sample_stage2_kernel, dim3(R), dim3(32), 0, stream, part_val, part_idx, parts, out);
     return kvb_launch_status();
 }

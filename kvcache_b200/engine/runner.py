@@ -103,8 +103,7 @@ class ModelRunner:
         self._staging_events = [None] * ring
         self._ring = 0
         self._graphs: Dict[int, _DecodeGraph] = {}
-        parts = kernels.sample_parts(model.vocab_size)
-        self._sample_parts = parts
+        self._sample_parts = None       # asked of the sampling module when a step first samples
         self.steps_run = 0
         self.last_h2d_bytes = 0
         self.graph_replays = 0
@@ -209,6 +208,8 @@ class ModelRunner:
     def _sample(self, logits: torch.Tensor, layout: StepLayout, workspace: Workspace) -> torch.Tensor:
         R = logits.shape[0]
         dev = self._meta_device
+        if self._sample_parts is None:
+            self._sample_parts = self.kernels.sample_parts(self.model.vocab_size)
         tokens = workspace.buffer("sample.tokens", (R,), torch.int32)
         self.kernels.sample(logits, layout.view(dev, "sample_temperature").view(torch.float32),
                             layout.view(dev, "sample_seed").view(torch.int64), layout.view(dev, "sample_counter"), tokens,
