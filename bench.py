@@ -65,7 +65,7 @@ class ClockSampler:
     def start(self):
         try:
             self.proc = subprocess.Popen(["nvidia-smi", "-i", "0", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
-                                          "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+                                          "-lms", "20"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             threading.Thread(target=self._read, daemon=True).start()
         except OSError:
             self.proc = None
@@ -115,7 +115,7 @@ def fill_cache_randomly(core, slots, context):
         group.v_pool.normal_(0.0, 1.0, generator=g)
 
 
-def time_decode(folder, batch, context, steps, warmup, use_graphs=True):
+def time_decode(folder, batch, context, steps, warmup, use_graphs=True, sampler=None):
     """Device-timed decode steps at `batch` requests of about `context` cached tokens each."""
     import torch
     from kvcache_b200.config.options import EngineOptions
@@ -133,6 +133,9 @@ def time_decode(folder, batch, context, steps, warmup, use_graphs=True):
     for _ in range(warmup):
         loop.step()
     torch.cuda.synchronize()
+    if sampler is not None:
+        sampler.start()                               # clocks are sampled during the timed region only
+        time.sleep(0.05)
     launches_before = loop.launches
     begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     begin.record()
@@ -140,12 +143,13 @@ def time_decode(folder, batch, context, steps, warmup, use_graphs=True):
         loop.step()
     end.record()
     torch.cuda.synchronize()
+    clocks = sampler.stop() if sampler is not None else None
     core.kernels.check_errors()
     ms = begin.elapsed_time(end)
     mean_context = start_len + warmup + (steps - 1) / 2.0 + 1
     step_bytes = core.model.decode_weight_bytes() + batch * mean_context * core.cache.kv_bytes_per_token()
     result = {"ms_per_step": ms / steps, "tok_s": batch * steps / (ms / 1e3), "bytes_per_step": step_bytes,
-              "launches": loop.launches - launches_before}
+              "launches": loop.launches - launches_before, "clocks": clocks}
     del loop, core
     torch.cuda.empty_cache()
     return result
@@ -205,7 +209,7 @@ def time_e2e(folder, batch, context, steps, warmup):
     wall = time.perf_counter()
     begin.record()
     for _ in range(steps):
-        llm.step()
+        llm.step()                                   # plans and launches a step, reads the tokens of the one before
     end.record()
     torch.cuda.synchronize()
     wall = time.perf_counter() - wall
@@ -218,7 +222,7 @@ def time_e2e(folder, batch, context, steps, warmup):
 def main() -> int:
     parser = argparse.ArgumentParser()
     parser.add_argument("--gpus", type=int, default=1)
-    parser.add_argument("--steps", type=int, default=128)
+    parser.add_argument("--steps", type=int, default=256)
     parser.add_argument("--warmup", type=int, default=8)
     parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
     parser.add_argument("--layers", type=int, default=QWEN25_05B["num_hidden_layers"])
@@ -242,10 +246,9 @@ def main() -> int:
     peaks = load_peaks()
     with tempfile.TemporaryDirectory() as tmp:
         folder = make_folder(tmp, args.layers)
-        sampler = ClockSampler()
-        sampler.start()
-        main_run = time_decode(folder, args.batch, CONTEXT, args.steps, args.warmup, use_graphs=not args.no_graphs)
-        clocks = sampler.stop()
+        main_run = time_decode(folder, args.batch, CONTEXT, args.steps, args.warmup, use_graphs=not args.no_graphs,
+                               sampler=ClockSampler())
+        clocks = main_run["clocks"]
         points = {}
         if not args.skip_points:
             for b in (1, 64):

@@ -96,6 +96,16 @@ class CacheManager:
             worst = max(worst, need - g.pages.allocator.num_free)
         return max(0, worst)
 
+    def page_delta(self, slot: int, count: int) -> List[int]:
+        """Pages each group would take, net of those it gives back, if `count` tokens were appended to `slot`."""
+        start = int(self.lengths[slot])
+        out = []
+        for g in self.groups:
+            g.pages._check_length(start + count)
+            release, take, _, _ = g.pages.plan(slot, start, start + count)
+            out.append(len(take) - len(release))
+        return out
+
     def extend(self, additions: Sequence[Tuple[int, int]]) -> None:
         """Makes room for `count` more tokens of every `(slot, count)`: first gives back the
         pages that windows have passed, then takes new ones.  Raises OutOfPages, changing

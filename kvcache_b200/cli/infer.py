@@ -43,7 +43,8 @@ def main(argv=None) -> int:
     params = SamplingParams(max_new_tokens=args.max_new, temperature=args.temperature, seed=args.seed, ignore_eos=True)
     request = llm.scheduler.add_request(prompt, params)
     times = []
-    while llm.scheduler.has_work():
+    llm.pipelined = False                            # each step is timed with its tokens read, as the reference does
+    while llm.has_work():
         start = time.perf_counter()
         llm.step()
         times.append((time.perf_counter() - start) * 1e6)

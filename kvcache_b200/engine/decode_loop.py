@@ -21,7 +21,6 @@ class DecodeLoop:
         self.temperature, self.seed = temperature, seed
         self.runner = core.runner
         self.runner.use_graphs = use_graphs and core.device.type == "cuda"
-        self._tokens = None
         self._count = 0
 
     @property
@@ -29,13 +28,13 @@ class DecodeLoop:
         return self.core.kernels.launches
 
     def set_tokens(self, tokens: torch.Tensor) -> None:
-        self._tokens = tokens.to(self.core.device, torch.int32)
+        """The first step's input ids, placed where a previous step would have left its samples."""
+        self.runner.last_tokens[:len(self.slots)].copy_(tokens.to(self.core.device, torch.int32))
 
     def step(self) -> torch.Tensor:
         """One token for every slot; returns the device tensor of the tokens just sampled."""
-        entries = [StepEntry(slot, (0,), (0,), (self.temperature, self.seed + i, self._count))
+        entries = [StepEntry(slot, (0,), (0,), (self.temperature, self.seed + i, self._count), token_from_last=i)
                    for i, slot in enumerate(self.slots)]
-        _, tokens = self.runner.step(entries, sample=True, token_source=self._tokens)
-        self._tokens = tokens
+        _, tokens = self.runner.step(entries, sample=True)
         self._count += 1
         return tokens

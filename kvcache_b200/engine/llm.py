@@ -8,7 +8,6 @@ from typing import Dict, List, Optional, Sequence, Union
 
 from ..config.options import EngineOptions
 from ..sampling.params import SamplingParams
-from ..sampling.sampler import TokenReader
 from .core import EngineCore
 from .runner import StepEntry
 from .scheduler import Request, Scheduler
@@ -27,8 +26,9 @@ class LLM:
         self.options = options
         self.core = EngineCore(model, options, kernels=kernels)
         self.config = self.core.config
-        self.reader = TokenReader(self.core.device, options.max_running)
         self.scheduler = self._new_scheduler()
+        self._pending = None            # the step whose tokens have not been read yet
+        self.pipelined = True           # plan and launch a step before reading the one before it
         self.last_stats = None
         self.last_seconds = 0.0
 
@@ -38,17 +38,50 @@ class LLM:
                          chunk_size=o.chunk_size, max_model_len=self.core.max_model_len, admission=o.admission,
                          default_eos=getattr(self.config, "eos_token_ids", ()))
 
-    def step(self) -> List[Request]:
-        """One scheduler iteration: plan, run, sample, record.  Returns finished requests."""
+    def has_work(self) -> bool:
+        return self.scheduler.has_work() or self._pending is not None
+
+    def _launch(self):
+        """Plans and launches one step; returns (pieces, a function that waits for its tokens) or None."""
         pieces = self.scheduler.schedule()
         if not pieces:
-            return []
+            return None
         entries = [StepEntry(p.request.slot, p.tokens, [p.count - 1] if p.samples else [],
-                             (p.request.params.temperature, p.request.params.seed, len(p.request.output)))
+                             (p.request.params.temperature, p.request.params.seed, p.output_index),
+                             token_from_last=p.token_from_last)
                    for p in pieces]
         _, tokens = self.core.runner.step(entries, sample=True)
-        sampled = self.reader.read(tokens) if tokens is not None else []
-        return self.scheduler.update(pieces, sampled)
+        self.scheduler.launched(pieces)
+        count = sum(1 for p in pieces if p.samples)
+        wait = self.core.runner.read_tokens_async(count) if count else (lambda: [])
+        return pieces, wait
+
+    def _must_wait_before_planning(self) -> bool:
+        """Preemption recomputes a request from its tokens, so all of them must be known: with optimistic
+        admission the pipeline is drained whenever pages are about to run short."""
+        return (self.options.admission == "optimistic"
+                and self.core.cache.free_pages() <= len(self.scheduler.running) + 1)
+
+    def step(self) -> List[Request]:
+        """One scheduler iteration.  The step is planned and launched before the previous step's tokens are
+        read, so the host's work overlaps the device's; returns the requests that the tokens read in this
+        call finished."""
+        done: List[Request] = []
+        if self._pending is not None and self._must_wait_before_planning():
+            done += self._drain()
+        launched = self._launch()
+        done += self._drain()
+        self._pending = launched
+        if not self.pipelined:
+            done += self._drain()
+        return done
+
+    def _drain(self) -> List[Request]:
+        if self._pending is None:
+            return []
+        pieces, wait = self._pending
+        self._pending = None
+        return self.scheduler.commit(pieces, wait())
 
     def generate(self, prompts: Sequence[Sequence[int]],
                  params: Union[SamplingParams, Sequence[SamplingParams], None] = None) -> List[List[int]]:
@@ -58,12 +91,14 @@ class LLM:
         if len(per_prompt) != len(prompts):
             raise ValueError("one SamplingParams per prompt, or one for all")
         self.scheduler = self._new_scheduler()
+        self._pending = None
         requests = [self.scheduler.add_request(p, sp) for p, sp in zip(prompts, per_prompt)]
         start = time.perf_counter()
-        while self.scheduler.has_work():
+        while self.has_work():
             before = self.scheduler.stats.steps
             self.step()
-            if self.scheduler.stats.steps == before and self.scheduler.has_work() and not self.scheduler.running:
+            if (self.scheduler.stats.steps == before and self._pending is None and self.scheduler.has_work()
+                    and not self.scheduler.running):
                 raise RuntimeError("the scheduler made no progress (a waiting request fits neither slots nor pages)")
         self.core.kernels.check_errors()
         self.last_seconds = time.perf_counter() - start

@@ -37,6 +37,7 @@ class StepEntry:
     tokens: Sequence[int]
     want: Sequence[int] = ()
     sampling: Optional[Tuple[float, int, int]] = None
+    token_from_last: int = -1      # >= 0: the entry's single token is the previous step's sampled token at this index
 
 
 def _align4(n: int) -> int:
@@ -49,7 +50,7 @@ class StepLayout:
     SECTIONS = (("token_ids", "T", 1), ("positions", "T", 1), ("row_segment", "T", 1), ("seg_q_start", "S", 1),
                 ("seg_q_len", "S", 1), ("seg_kv_len", "S", 1), ("seg_slot", "S", 1), ("wanted_rows", "R", 1),
                 ("sample_temperature", "R", 1), ("sample_counter", "R", 1), ("sample_seed", "R", 2),
-                ("decode_items", "S", 1), ("prefill_tiles", "TILES", 2))
+                ("decode_items", "S", 1), ("prefill_tiles", "TILES", 2), ("token_src", "T", 1))
     TILE_ROWS = 64
 
     def __init__(self, T: int, S: int, R: int, table_width: int, num_groups: int):
@@ -104,6 +105,11 @@ class ModelRunner:
         self._ring = 0
         self._graphs: Dict[int, _DecodeGraph] = {}
         self._sample_parts = None       # asked of the sampling module when a step first samples
+        # Tokens the last sampling step chose, in the order of its wanted places.  The next step may take its
+        # input ids from here (StepEntry.token_from_last) without the host ever seeing them.
+        self.last_tokens = torch.zeros(max(self.max_segments, 1), dtype=torch.int32, device=self.device)
+        self._token_host = [torch.zeros(max(self.max_segments, 1), dtype=torch.int32, pin_memory=self._on_cuda) for _ in range(3)]
+        self._token_ring = 0
         self.steps_run = 0
         self.last_h2d_bytes = 0
         self.graph_replays = 0
@@ -143,11 +149,19 @@ class ModelRunner:
         q_start = np.zeros(S, dtype=np.int32)
         np.cumsum(counts_np[:-1], out=q_start[1:])
         if T == S:                                   # one token per request: no concatenation needed
-            layout.view(host, "token_ids")[:] = [e.tokens[0] for e in entries]
+            layout.view(host, "token_ids")[:] = [max(e.tokens[0], 0) for e in entries]
+            layout.view(host, "token_src")[:] = [e.token_from_last for e in entries]
             row_segment = np.arange(S, dtype=np.int32)
             layout.view(host, "positions")[:] = starts_np
         else:
-            layout.view(host, "token_ids")[:] = np.concatenate([np.asarray(e.tokens, dtype=np.int32) for e in entries])
+            layout.view(host, "token_ids")[:] = np.maximum(np.concatenate([np.asarray(e.tokens, dtype=np.int32) for e in entries]), 0)
+            src = layout.view(host, "token_src")
+            src[:] = -1
+            for i, e in enumerate(entries):
+                if e.token_from_last >= 0:
+                    if counts[i] != 1:
+                        raise ValueError("token_from_last applies to an entry of one token")
+                    src[q_start[i]] = e.token_from_last
             row_segment = np.repeat(np.arange(S, dtype=np.int32), counts_np)
             layout.view(host, "positions")[:] = np.arange(T, dtype=np.int32) - q_start[row_segment] + starts_np[row_segment]
         layout.view(host, "row_segment")[:] = row_segment
@@ -197,6 +211,7 @@ class ModelRunner:
             row_segment=layout.view(dev, "row_segment"), seg_q_start=layout.view(dev, "seg_q_start"),
             seg_q_len=layout.view(dev, "seg_q_len"), seg_kv_len=layout.view(dev, "seg_kv_len"),
             seg_slot=layout.view(dev, "seg_slot"), wanted_rows=layout.view(dev, "wanted_rows"),
+            token_src=layout.view(dev, "token_src"), last_tokens=self.last_tokens,
             decode_items=layout.view(dev, "decode_items")[:n_items], num_decode_items=n_items,
             prefill_tiles=layout.view(dev, "prefill_tiles")[:2 * n_tiles].view(-1, 2), num_prefill_tiles=n_tiles,
             max_q_len=int(counts_np.max()), max_kv_len=int((starts_np + counts_np).max()),
@@ -210,7 +225,9 @@ class ModelRunner:
         dev = self._meta_device
         if self._sample_parts is None:
             self._sample_parts = self.kernels.sample_parts(self.model.vocab_size)
-        tokens = workspace.buffer("sample.tokens", (R,), torch.int32)
+        if R > self.last_tokens.shape[0]:
+            raise ValueError(f"{R} places to sample in one step; the runner was made for {self.last_tokens.shape[0]}")
+        tokens = self.last_tokens[:R]
         self.kernels.sample(logits, layout.view(dev, "sample_temperature").view(torch.float32),
                             layout.view(dev, "sample_seed").view(torch.int64), layout.view(dev, "sample_counter"), tokens,
                             workspace.buffer("sample.part_val", (R * self._sample_parts,), torch.float32),
@@ -229,7 +246,11 @@ class ModelRunner:
             return found
         ws = self.graph_workspace
         moved = ws.moved
-        self._forward(batch, view, layout, ws, True)          # sizes the buffers; writes what the replay rewrites
+        # A first run outside the graph sizes the buffers.  It writes what the replay writes again - except that
+        # sampling overwrites `last_tokens`, which this very step may read its ids from: put them back.
+        saved = self.last_tokens.clone()
+        self._forward(batch, view, layout, ws, True)
+        self.last_tokens.copy_(saved)
         if ws.moved != moved:
             self._graphs.clear()                              # a buffer moved: graphs that hold its old address go
         torch.cuda.synchronize(self.device)
@@ -245,16 +266,29 @@ class ModelRunner:
         self._graphs[B] = found
         return found
 
-    def step(self, entries: Sequence[StepEntry], sample: bool = False, token_source: Optional[torch.Tensor] = None):
+    def read_tokens_async(self, count: int):
+        """Starts the copy of the last step's sampled tokens to the host; returns a function that waits for
+        it and gives the int32 array.  Steps launched in between do not disturb the copy."""
+        index = self._token_ring
+        self._token_ring = (self._token_ring + 1) % len(self._token_host)
+        host = self._token_host[index]
+        host[:count].copy_(self.last_tokens[:count], non_blocking=True)
+        if not self._on_cuda:
+            return lambda: host[:count].numpy().copy()
+        event = torch.cuda.Event()
+        event.record()
+
+        def wait():
+            event.synchronize()
+            return host[:count].numpy().copy()
+        return wait
+
+    def step(self, entries: Sequence[StepEntry], sample: bool = False):
         """Runs the entries as one batch.  Returns float32 logits [wanted places, vocab] in the
         order of the entries and of their `want` lists - or, with `sample`, the pair
-        (logits, int32 tokens sampled at those places, on the device).  The tensors are
-        views of buffers the next step overwrites.  `token_source`: a device tensor of this
-        step's token ids that replaces the ids of the entries (tokens the previous step
-        sampled, which the host has not read yet)."""
+        (logits, int32 tokens sampled at those places, on the device: `last_tokens`).  The
+        tensors are views of buffers the next step overwrites."""
         batch, view, layout = self.prepare(entries)
-        if token_source is not None:
-            batch.token_ids.copy_(token_source[:batch.num_tokens], non_blocking=True)
         decode_only = sample and self.use_graphs and batch.num_tokens == batch.num_segments == batch.num_wanted
         if decode_only:
             found = self._decode_graph(batch, view, layout)

@@ -12,6 +12,13 @@ request is checked for its end right after sampling, so `max_new = 1` yields one
 reference yields two, qwen_serve.cu:192-203); and a request that can never fit is refused
 when it is submitted (the reference's loop would spin forever, qwen_serve.cu:195,201).
 
+Pipelining.  A step's sampled tokens need not be known on the host before the next step is
+planned: `launched(pieces)` records that a step is on its way (its sampling requests get a
+placeholder token, which the next step reads on the device), `commit(pieces, tokens)` fills the
+placeholders in when the tokens arrive and ends requests.  A request whose end token arrives
+after it was already given a place in the following step simply has that step's token dropped.
+`update` is the two in one, for callers that wait for every step.
+
 When pages run out.  `admission="reserve"` (default): they cannot, because every admitted
 request's worst case is held back.  `admission="optimistic"`: a request is admitted when its
 next portion fits; if a later step lacks pages, the newest running request is preempted - its
@@ -48,6 +55,9 @@ class Request:
     finish_reason: Optional[str] = None
     preemptions: int = 0
     reserved: Optional[List[int]] = None   # pages held back for it in each group (reserve policy)
+    inflight: int = 0              # placeholders at the end of `output`: sampled, not yet known on the host
+    last_index: int = -1           # where the step that sampled the newest placeholder put it (device order)
+    finishing: bool = False        # its last token is on its way: it takes no part in further steps
 
     @property
     def tokens(self) -> List[int]:
@@ -58,6 +68,9 @@ class Request:
         return len(self.prompt) + len(self.output)
 
 
+PLACEHOLDER = -1
+
+
 @dataclass
 class Piece:
     """One request's share of a step."""
@@ -65,6 +78,8 @@ class Piece:
     start: int                     # first position run in this step
     count: int
     samples: bool                  # the piece ends at the request's last token: a token is sampled
+    output_index: int = -1         # which element of request.output the sampled token becomes
+    token_from_last: int = -1      # >= 0: its (single) token is the previous step's sampled token at this index
 
     @property
     def tokens(self) -> List[int]:
@@ -176,17 +191,36 @@ class Scheduler:
         under the token budget and the pages that are free.  May preempt (optimistic policy)."""
         budget = self.max_tokens_per_step
         pieces: List[Piece] = []
-        additions: List[Tuple[int, int]] = []
+        groups = self.cache.groups
+        need = [0] * len(groups)          # pages the pieces placed so far take, net of what they give back
+
+        def delta(request: Request, count: int) -> List[int]:
+            return self.cache.page_delta(request.slot, count)
 
         def fits(request: Request, count: int) -> bool:
-            return self.cache.pages_short(additions + [(request.slot, count)]) == 0
+            d = delta(request, count)
+            return all(need[g] + d[g] <= groups[g].pages.allocator.num_free for g in range(len(groups)))
 
         def place(request: Request, count: int) -> None:
             nonlocal budget
             start = request.num_computed
-            pieces.append(Piece(request, start, count, start + count == request.num_tokens))
-            additions.append((request.slot, count))
+            d = delta(request, count)
+            for g in range(len(groups)):
+                need[g] += d[g]
+            from_last = request.last_index if (request.inflight and count == 1 and start == request.num_tokens - 1) else -1
+            pieces.append(Piece(request, start, count, start + count == request.num_tokens,
+                                output_index=len(request.output), token_from_last=from_last))
             budget -= count
+
+        def recount() -> None:
+            nonlocal budget
+            for g in range(len(groups)):
+                need[g] = 0
+            for p in pieces:
+                d = delta(p.request, p.count)
+                for g in range(len(groups)):
+                    need[g] += d[g]
+            budget = self.max_tokens_per_step - sum(p.count for p in pieces)
 
         # Running requests, oldest first: decodes take one token, prompts a portion.
         index = 0
@@ -194,7 +228,7 @@ class Scheduler:
             request = self.running[index]
             remaining = request.num_tokens - request.num_computed
             count = min(remaining, self.chunk_size, budget)
-            if count <= 0:
+            if count <= 0 or request.finishing:
                 index += 1
                 continue
             while not fits(request, count):
@@ -203,8 +237,7 @@ class Scheduler:
                     break
                 # Drop what the victim had been given in this step.
                 pieces[:] = [p for p in pieces if p.request is not victim]
-                additions[:] = [(p.request.slot, p.count) for p in pieces]
-                budget = self.max_tokens_per_step - sum(p.count for p in pieces)
+                recount()
             if not fits(request, count):
                 smaller = count
                 while smaller > 1 and not fits(request, smaller):
@@ -238,12 +271,11 @@ class Scheduler:
         return pieces
 
     # ---- after the step ----------------------------------------------------
-    def update(self, pieces: Sequence[Piece], sampled: Sequence[int]) -> List[Request]:
-        """Records the step: `sampled` holds one token for every piece with `samples`, in
-        order.  Returns the requests that finished."""
-        done: List[Request] = []
-        it = iter(sampled)
+    def launched(self, pieces: Sequence[Piece]) -> None:
+        """The step is on its way to the device: positions advance, sampling requests get a placeholder
+        for the token to come, and a request whose last token this is takes no part in later steps."""
         self.stats.steps += 1
+        k = 0
         for piece in pieces:
             request = piece.request
             request.num_computed += piece.count
@@ -253,18 +285,48 @@ class Scheduler:
                 self.stats.prefill_tokens += piece.count
             if not piece.samples:
                 continue
+            piece.output_index = len(request.output)
+            request.output.append(PLACEHOLDER)
+            request.inflight += 1
+            request.last_index = k
+            k += 1
+            if len(request.output) >= request.params.max_new_tokens or request.num_tokens >= self.max_model_len:
+                request.finishing = True
+        self.stats.peak_pages = max(self.stats.peak_pages, self.cache.used_pages())
+
+    def commit(self, pieces: Sequence[Piece], sampled: Sequence[int]) -> List[Request]:
+        """The step's tokens have arrived: `sampled` holds one for every piece with `samples`, in order.
+        Returns the requests that finished."""
+        done: List[Request] = []
+        it = iter(sampled)
+        for piece in pieces:
+            if not piece.samples:
+                continue
             token = int(next(it))
-            request.output.append(token)
+            request = piece.request
+            if request.state == FINISHED or piece.output_index >= len(request.output):
+                continue                      # it ended on an earlier token; this one was computed in vain
+            request.output[piece.output_index] = token
+            request.inflight -= 1
             self.stats.generated += 1
             if token in request.eos:
                 reason = "eos"
-            elif len(request.output) >= request.params.max_new_tokens:
+                del request.output[piece.output_index + 1:]      # a placeholder of the step that followed
+            elif piece.output_index + 1 >= request.params.max_new_tokens:
                 reason = "length"
-            elif request.num_tokens >= self.max_model_len:
+            elif len(request.prompt) + piece.output_index + 1 >= self.max_model_len:
                 reason = "model_length"
             else:
                 continue
+            request.inflight = 0
             self._retire(request, reason)
             done.append(request)
-        self.stats.peak_pages = max(self.stats.peak_pages, self.cache.used_pages())
         return done
+
+    def has_inflight(self) -> bool:
+        return any(r.inflight for r in self.running)
+
+    def update(self, pieces: Sequence[Piece], sampled: Sequence[int]) -> List[Request]:
+        """`launched` and `commit` in one, for a caller that waits for every step's tokens."""
+        self.launched(pieces)
+        return self.commit(pieces, sampled)

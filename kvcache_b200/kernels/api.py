@@ -31,7 +31,7 @@ class KernelError(RuntimeError):
 class KernelSet:
     """Operators of a step.  Shapes: T rows, H width, all tensors contiguous.
 
-    embed(table[V,H], ids[T]) -> h[T,H] float32
+    embed(table[V,H], ids[T], src[T], last) -> h[T,H] float32; row r takes last[src[r]] instead of ids[r] where src[r] >= 0
     add_rmsnorm(h, delta, weight, eps, out, rows):
         rows is None: h[r] += delta[r] (if delta is given); out[r] = h[r] * rsqrt(mean(h[r]^2) + eps) * weight
         rows given:   v = h[rows[i]] + delta[rows[i]];      out[i] = v * rsqrt(mean(v^2) + eps) * weight
@@ -78,7 +78,7 @@ def _check(code: int, what: str) -> None:
 
 _SIGNATURES = {
     "elementwise": {
-        "kvb_embed": [_c_int, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_void_p, _c_void_p],
+        "kvb_embed": [_c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_void_p, _c_void_p],
         "kvb_add_rmsnorm": [_c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_float, _c_void_p],
         "kvb_silu_mul": [_c_int, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_void_p],
     },
@@ -178,11 +178,13 @@ class CudaKernels(KernelSet):
             raise KernelError("a kernel flagged bad input: " + "; ".join(reasons))
 
     # ---- operators ---------------------------------------------------------
-    def embed(self, table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor) -> None:
+    def embed(self, table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor, src: Optional[torch.Tensor] = None,
+              last: Optional[torch.Tensor] = None) -> None:
+        """out[r] = table[ids[r]], or table[last[src[r]]] where src[r] >= 0 (a token still on the device)."""
         T, H = out.shape
         self.launches += 1
-        _check(self._elementwise.kvb_embed(_dtype_code(table.dtype), _ptr(table), _ptr(ids), _ptr(out), T, H,
-                                           table.shape[0], _ptr(self.error_word), self._stream()), "embed")
+        _check(self._elementwise.kvb_embed(_dtype_code(table.dtype), _ptr(table), _ptr(ids), _ptr(src), _ptr(last), _ptr(out),
+                                           T, H, table.shape[0], _ptr(self.error_word), self._stream()), "embed")
 
     def add_rmsnorm(self, h: torch.Tensor, delta: Optional[torch.Tensor], weight: torch.Tensor, eps: float,
                     out: torch.Tensor, rows: Optional[torch.Tensor] = None) -> None:

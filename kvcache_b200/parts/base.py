@@ -73,6 +73,8 @@ class StepBatch:
     seg_kv_len: torch.Tensor         # int32 [S]   tokens of the request cached after this step
     seg_slot: torch.Tensor           # int32 [S]   the request's state slot
     wanted_rows: torch.Tensor        # int32 [R]   rows whose logits are returned
+    token_src: Optional[torch.Tensor] = None     # int32 [T]: >= 0: the row's token is last_tokens[token_src[r]]
+    last_tokens: Optional[torch.Tensor] = None   # int32: tokens the previous step sampled, still on the device
     # Attention work lists: segments that bring one token, and 64-row tiles (segment, first row)
     # of the segments that bring more.
     decode_items: Optional[torch.Tensor] = None    # int32 [num_decode_items]

@@ -119,7 +119,7 @@ class DecoderModel:
         [batch.num_wanted, vocab] for `batch.wanted_rows`."""
         T, R = batch.num_tokens, batch.num_wanted
         h = workspace.buffer("model.h", (T, self.width), torch.float32)
-        kernels.embed(self.embed, batch.token_ids, h)
+        kernels.embed(self.embed, batch.token_ids, h, batch.token_src, batch.last_tokens)
         base = LayerContext(batch=batch, kernels=kernels, workspace=workspace)
         if self.position is not None:
             self.position.on_embed(h, base)

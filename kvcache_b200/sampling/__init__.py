@@ -1,4 +1,3 @@
 from .params import SamplingParams
-from .sampler import TokenReader
 
-__all__ = ["SamplingParams", "TokenReader"]
+__all__ = ["SamplingParams"]

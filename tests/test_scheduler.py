@@ -159,3 +159,34 @@ def test_accounting_over_many_requests():
     assert s.stats.finished == 64 and s.stats.generated == sum(r.params.max_new_tokens for r in reqs)
     assert s.stats.peak_pages <= 64 and s.stats.peak_running <= 8 and s.cache.used_pages() == 0
     assert s.stats.prefill_tokens == sum(len(r.prompt) for r in reqs)
+
+
+def test_pipelined_steps_with_late_tokens():
+    """A step is planned while the tokens of the one before are still on their way: placeholders stand in,
+    the next step takes the token from the device, an end token that arrives late drops the token computed
+    after it, and a request at its length limit is not planned again."""
+    s = _scheduler(_cache(), default_eos=(9,))
+    a = s.add_request([1, 2, 3], SamplingParams(max_new_tokens=3))
+    b = s.add_request([4, 5], SamplingParams(max_new_tokens=8))
+
+    def launch():
+        pieces = s.schedule()
+        s.cache.extend([(p.request.slot, p.count) for p in pieces])
+        s.launched(pieces)
+        return pieces
+    first = launch()
+    assert [(p.request.id, p.count, p.samples, p.token_from_last) for p in first] == [(0, 3, True, -1), (1, 2, True, -1)]
+    assert a.output == [-1] and b.output == [-1] and a.inflight == 1
+    second = launch()                                   # planned before the first step's tokens are known
+    assert [(p.request.id, p.start, p.count, p.token_from_last) for p in second] == [(0, 3, 1, 0), (1, 2, 1, 1)]
+    assert second[0].tokens == [-1]
+    s.commit(first, [5, 9])                             # b's first token is its end token
+    assert a.output == [5, -1] and b.output == [9] and b.state == "finished" and b.finish_reason == "eos"
+    third = launch()                                    # a's last token: afterwards it is not planned again
+    assert [(p.request.id, p.token_from_last) for p in third] == [(0, 0)] and a.finishing
+    assert s.commit(second, [6, 7]) == []               # 7 was computed for b after its end: dropped
+    assert a.output == [5, 6, -1] and b.output == [9]
+    assert launch() == []
+    done = s.commit(third, [8])
+    assert [r.id for r in done] == [0] and a.output == [5, 6, 8] and a.finish_reason == "length"
+    assert not s.has_work() and s.cache.used_pages() == 0 and s.stats.generated == 4

@@ -23,8 +23,11 @@ class TorchKernels:
     def check_errors(self) -> None:
         pass
 
-    def embed(self, table, ids, out):
-        out.copy_(table[ids.long()].to(torch.float32))
+    def embed(self, table, ids, out, src=None, last=None):
+        ids = ids.long()
+        if src is not None:
+            ids = torch.where(src >= 0, last[src.clamp(min=0).long()].long(), ids)
+        out.copy_(table[ids].to(torch.float32))
 
     def add_rmsnorm(self, h, delta, weight, eps, out, rows=None):
         f = self.f
