@@ -102,6 +102,60 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t* r) {
     asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
 }
 
+// One thread's 32 consecutive accumulator columns (row m, columns n .. n + 31) on their way to memory: bias and
+// conversion, or the gated activation on interleaved gate/up columns.
+template <typename TOut, bool SWIGLU>
+__device__ __forceinline__ void store_chunk(const uint32_t* r, const float* __restrict__ bias, TOut* __restrict__ y, int m,
+                                            int n, int N) {
+    if (SWIGLU) {
+        // columns n .. n+7 gate, n+8 .. n+15 up, twice per 32: 16 outputs at column n / 2
+        TOut* out = y + (size_t)m * (N >> 1) + (n >> 1);
+        float v[16];
+#pragma unroll
+        for (int blk = 0; blk < 2; ++blk)
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const float gate = __uint_as_float(r[16 * blk + i]), up = __uint_as_float(r[16 * blk + 8 + i]);
+                v[8 * blk + i] = __fdividef(gate, 1.f + __expf(-gate)) * up;
+            }
+        if (n + 32 <= N && sizeof(TOut) == 2 && (N & 15) == 0) {
+            uint32_t packed[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                __nv_bfloat162 p2 = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+                packed[i] = *reinterpret_cast<uint32_t*>(&p2);
+            }
+            reinterpret_cast<uint4*>(out)[0] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+            reinterpret_cast<uint4*>(out)[1] = make_uint4(packed[4], packed[5], packed[6], packed[7]);
+        } else {
+#pragma unroll
+            for (int blk = 0; blk < 2; ++blk)
+#pragma unroll
+                for (int i = 0; i < 8; ++i)
+                    if (n + 16 * blk + 8 + i < N) out[8 * blk + i] = from_f32<TOut>(v[8 * blk + i]);
+        }
+    } else {
+        TOut* out = y + (size_t)m * N + n;
+        if (n + 32 <= N && sizeof(TOut) == 2 && (N & 7) == 0) {
+            uint32_t packed[16];
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+                const float a = __uint_as_float(r[2 * i]) + (bias ? __ldg(bias + n + 2 * i) : 0.f);
+                const float bb = __uint_as_float(r[2 * i + 1]) + (bias ? __ldg(bias + n + 2 * i + 1) : 0.f);
+                __nv_bfloat162 v2 = __floats2bfloat162_rn(a, bb);
+                packed[i] = *reinterpret_cast<uint32_t*>(&v2);
+            }
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+                reinterpret_cast<uint4*>(out)[i] = make_uint4(packed[4 * i], packed[4 * i + 1], packed[4 * i + 2], packed[4 * i + 3]);
+        } else {
+#pragma unroll
+            for (int i = 0; i < 32; ++i)
+                if (n + i < N) out[i] = from_f32<TOut>(__uint_as_float(r[i]) + (bias ? __ldg(bias + n + i) : 0.f));
+        }
+    }
+}
+
 template <int STAGES>
 struct Shared {
     uint64_t full[STAGES];
@@ -210,53 +264,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
                 tmem_ld32(tmem + ((uint32_t)(quarter * 32) << 16) + b * BN + c * 32, r);
                 const int n = n0 + c * 32;
                 if (m >= M || n >= N) continue;
-                if (SWIGLU) {
-                    // columns n .. n+7 gate, n+8 .. n+15 up, twice per 32: 16 outputs at column n / 2
-                    TOut* out = y + (size_t)m * (N >> 1) + (n >> 1);
-                    float v[16];
-#pragma unroll
-                    for (int blk = 0; blk < 2; ++blk)
-#pragma unroll
-                        for (int i = 0; i < 8; ++i) {
-                            const float gate = __uint_as_float(r[16 * blk + i]), up = __uint_as_float(r[16 * blk + 8 + i]);
-                            v[8 * blk + i] = gate / (1.f + __expf(-gate)) * up;
-                        }
-                    if (n + 32 <= N && sizeof(TOut) == 2 && (N & 15) == 0) {
-                        uint32_t packed[8];
-#pragma unroll
-                        for (int i = 0; i < 8; ++i) {
-                            __nv_bfloat162 p2 = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
-                            packed[i] = *reinterpret_cast<uint32_t*>(&p2);
-                        }
-                        reinterpret_cast<uint4*>(out)[0] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
-                        reinterpret_cast<uint4*>(out)[1] = make_uint4(packed[4], packed[5], packed[6], packed[7]);
-                    } else {
-#pragma unroll
-                        for (int blk = 0; blk < 2; ++blk)
-#pragma unroll
-                            for (int i = 0; i < 8; ++i)
-                                if (n + 16 * blk + 8 + i < N) out[8 * blk + i] = from_f32<TOut>(v[8 * blk + i]);
-                    }
-                } else {
-                    TOut* out = y + (size_t)m * N + n;
-                    if (n + 32 <= N && sizeof(TOut) == 2 && (N & 7) == 0) {
-                        uint32_t packed[16];
-#pragma unroll
-                        for (int i = 0; i < 16; ++i) {
-                            const float a = __uint_as_float(r[2 * i]) + (bias ? __ldg(bias + n + 2 * i) : 0.f);
-                            const float bb = __uint_as_float(r[2 * i + 1]) + (bias ? __ldg(bias + n + 2 * i + 1) : 0.f);
-                            __nv_bfloat162 v2 = __floats2bfloat162_rn(a, bb);
-                            packed[i] = *reinterpret_cast<uint32_t*>(&v2);
-                        }
-#pragma unroll
-                        for (int i = 0; i < 4; ++i)
-                            reinterpret_cast<uint4*>(out)[i] = make_uint4(packed[4 * i], packed[4 * i + 1], packed[4 * i + 2], packed[4 * i + 3]);
-                    } else {
-#pragma unroll
-                        for (int i = 0; i < 32; ++i)
-                            if (n + i < N) out[i] = from_f32<TOut>(__uint_as_float(r[i]) + (bias ? __ldg(bias + n + i) : 0.f));
-                    }
-                }
+                store_chunk<TOut, SWIGLU>(r, bias, y, m, n, N);
             }
             // This warp has read its part of the accumulator: hand it back to the MMA warp.
             asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
@@ -276,6 +284,164 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
     if (warp == 1) {
         asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem), "r"(2 * BN) : "memory");
+    }
+}
+
+
+// ---------------------------------------------------------------------------------------------------------
+// The same product with two SMs on one tile (tcgen05 cta_group::2).  A cluster of two blocks owns a 256 x 256
+// tile of y: block r of the pair loads rows m0 + 128 r .. + 127 of x and rows n0 + 128 r .. + 127 of W, so each
+// SM brings 32 KB per K block where two independent 128 x 256 tiles would bring 48 KB each - the operand traffic
+// from L2, which bounds the one-SM kernel, drops by a third.  The even block of the pair (the leader) issues the
+// MMAs for both; they read A from each block's own shared memory into that block's tensor memory and the two
+// halves of B from both.  Barriers: "full" lives in the leader and counts the bytes of both blocks' TMA loads;
+// "empty" and "accumulator full" are signalled in both blocks by multicast commits; "accumulator empty" lives in
+// the leader and collects the epilogue warps of both blocks.
+// ---------------------------------------------------------------------------------------------------------
+constexpr uint32_t PEER_BIT_MASK = 0xFEFFFFFFu;     // a shared::cluster address with this bit cleared names the even block of the pair
+
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\nbarrier.cluster.wait.acquire.aligned;\n" ::: "memory");
+}
+__device__ __forceinline__ void tma_load_2d_pair(void* dst, const CUtensorMap* map, int x, int y, uint64_t* leader_bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];\n"
+        ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(leader_bar) & PEER_BIT_MASK), "r"(x), "r"(y) : "memory");
+}
+__device__ __forceinline__ void umma_pair(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n}\n"
+        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void umma_commit_pair(uint64_t* bar) {      // arrives on the barrier at this offset in both blocks
+    const uint16_t mask = 3;
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;\n"
+                 ::"r"(smem_u32(bar)), "h"(mask) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_leader(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];\n" ::"r"(smem_u32(bar) & PEER_BIT_MASK) : "memory");
+}
+
+template <typename TOut, bool SWIGLU>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1)
+gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
+                         const float* __restrict__ bias, TOut* __restrict__ y, int M, int N, int K, int* __restrict__ err) {
+    constexpr int BN = 256, HALF_N = 128;
+    constexpr int B_BYTES = HALF_N * BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;     // per block
+    constexpr int STAGES = 6;
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char* tiles = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    __shared__ Shared<STAGES> sh;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_ctarank();
+    const bool leader = rank == 0;
+    const int pair = blockIdx.x >> 1, num_pairs = gridDim.x >> 1;
+    const int m_blocks = (M + 2 * BM - 1) / (2 * BM), n_blocks = (N + BN - 1) / BN;
+    const int num_tiles = m_blocks * n_blocks;
+    const int kblocks = (K + BK - 1) / BK;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) { mbar_init(&sh.full[s], 1); mbar_init(&sh.empty[s], 1); }
+        for (int b = 0; b < 2; ++b) { mbar_init(&sh.accum_full[b], 1); mbar_init(&sh.accum_empty[b], 8); }
+        sh.failed = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+    }
+    if (warp == 1) {   // both blocks of the pair take part in the allocation: two accumulators of 256 columns in each
+        asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_u32(&sh.tmem_base)), "r"(2 * BN) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;\n" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+    __syncthreads();
+    cluster_sync_all();              // the peer's barriers exist before anything is signalled across
+    asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+    const uint32_t tmem = sh.tmem_base;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            asm volatile("prefetch.tensormap [%0];\n" ::"l"(&map_x) : "memory");
+            asm volatile("prefetch.tensormap [%0];\n" ::"l"(&map_w) : "memory");
+            uint32_t it = 0;
+            bool ok = true;
+            for (int tile = pair; tile < num_tiles && ok; tile += num_pairs) {
+                const int m0 = (tile % m_blocks) * 2 * BM + rank * BM, n0 = (tile / m_blocks) * BN + rank * HALF_N;
+                for (int kb = 0; kb < kblocks; ++kb, ++it) {
+                    const int s = it % STAGES;
+                    const uint32_t round = it / STAGES;
+                    if (round > 0 && !mbar_wait(&sh.empty[s], (round - 1) & 1)) { atomicOr(err, KVB_DEV_TIMEOUT); sh.failed = 1; ok = false; break; }
+                    if (leader) mbar_expect_tx(&sh.full[s], 2 * STAGE_BYTES);      // the bytes of both blocks
+                    tma_load_2d_pair(tiles + s * STAGE_BYTES, &map_x, kb * BK, m0, &sh.full[s]);
+                    tma_load_2d_pair(tiles + s * STAGE_BYTES + A_BYTES, &map_w, kb * BK, n0, &sh.full[s]);
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0 && leader) {
+            constexpr uint32_t idesc = instr_desc(2 * BM, BN);
+            uint32_t it = 0, local = 0;
+            bool ok = true;
+            for (int tile = pair; tile < num_tiles && ok; tile += num_pairs, ++local) {
+                const int b = local & 1;
+                const uint32_t use = local >> 1;
+                if (use > 0 && !mbar_wait(&sh.accum_empty[b], (use - 1) & 1)) { atomicOr(err, KVB_DEV_TIMEOUT); sh.failed = 1; ok = false; break; }
+                asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+                const uint32_t acc = tmem + b * BN;
+                for (int kb = 0; kb < kblocks; ++kb, ++it) {
+                    const int s = it % STAGES;
+                    if (!mbar_wait(&sh.full[s], (it / STAGES) & 1)) { atomicOr(err, KVB_DEV_TIMEOUT); sh.failed = 1; ok = false; break; }
+                    asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+                    const uint32_t a_addr = smem_u32(tiles + s * STAGE_BYTES), b_addr = a_addr + A_BYTES;
+                    const uint64_t adesc = smem_desc(a_addr), bdesc = smem_desc(b_addr);
+#pragma unroll
+                    for (int k = 0; k < BK / 16; ++k)
+                        umma_pair(acc, adesc + 2 * k, bdesc + 2 * k, idesc, (kb | k) != 0 ? 1u : 0u);
+                    umma_commit_pair(&sh.empty[s]);
+                }
+                umma_commit_pair(&sh.accum_full[b]);
+            }
+        }
+    } else {
+        const int quarter = warp & 3;
+        uint32_t local = 0;
+        bool ok = true;
+        for (int tile = pair; tile < num_tiles && ok; tile += num_pairs, ++local) {
+            const int m0 = (tile % m_blocks) * 2 * BM + rank * BM, n0 = (tile / m_blocks) * BN;
+            const int b = local & 1;
+            const int m = m0 + quarter * 32 + lane;
+            ok = mbar_wait(&sh.accum_full[b], (local >> 1) & 1);
+            if (!ok) { if (lane == 0) { atomicOr(err, KVB_DEV_TIMEOUT); sh.failed = 1; } break; }
+            asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+#pragma unroll 1
+            for (int c = 0; c < BN / 32; ++c) {
+                uint32_t r[32];
+                tmem_ld32(tmem + ((uint32_t)(quarter * 32) << 16) + b * BN + c * 32, r);
+                const int n = n0 + c * 32;
+                if (m >= M || n >= N) continue;
+                store_chunk<TOut, SWIGLU>(r, bias, y, m, n, N);
+            }
+            asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+            __syncwarp();
+            if (lane == 0) mbar_arrive_leader(&sh.accum_empty[b]);
+        }
+    }
+
+    // Teardown: nobody leaves while the partner may still read this block's shared memory or signal its barriers.
+    asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+    __syncthreads();
+    if (sh.failed && threadIdx.x == 0 && leader) {
+        for (int s = 0; s < STAGES; ++s) mbar_wait(&sh.full[s], 0);
+    }
+    __syncthreads();
+    cluster_sync_all();
+    if (warp == 1) {
+        asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;\n" ::"r"(tmem), "r"(2 * BN) : "memory");
     }
 }
 
@@ -307,6 +473,16 @@ static int make_map(CUtensorMap* map, const void* base, int rows, int cols, int 
                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     return r == CUDA_SUCCESS ? KVB_OK : KVB_ERR_SHAPE;
+}
+
+#include <stdlib.h>
+static bool pair_mode() {        // KVB_TCGEN05_PAIR=0 keeps every tile on one SM
+    static int mode = -1;
+    if (mode < 0) {
+        const char* v = getenv("KVB_TCGEN05_PAIR");
+        mode = (v && v[0] == '0') ? 0 : 1;
+    }
+    return mode == 1;
 }
 
 static int sm_count() {
@@ -341,10 +517,35 @@ static int launch(const void* x, const void* w, const float* bias, TOut* y, int 
     return kvb_launch_status();
 }
 
-// 256-wide tiles halve the shared-memory traffic per product, but only pay when there are enough of them.
+template <typename TOut, bool SWIGLU>
+static int launch_pair(const void* x, const void* w, const float* bias, TOut* y, int M, int N, int K, int* err, cudaStream_t stream) {
+    CUtensorMap mx, mw;
+    int rc = make_map(&mx, x, M, K, BM);
+    if (rc != KVB_OK) return rc;
+    rc = make_map(&mw, w, N, K, 128);
+    if (rc != KVB_OK) return rc;
+    const size_t smem = (size_t)6 * (A_BYTES + 128 * BK * 2) + 1024;
+    auto kernel = gemm_tcgen05_pair_kernel<TOut, SWIGLU>;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+        configured = true;
+    }
+    const int tiles = ((M + 2 * BM - 1) / (2 * BM)) * ((N + 255) / 256);
+    int pairs = sm_count() / 2;
+    if (tiles < pairs) pairs = tiles;
+    kernel<<<2 * pairs, THREADS, smem, stream>>>(mx, mw, bias, y, M, N, K, err);
+    return kvb_launch_status();
+}
+
+// Two SMs on a 256 x 256 tile where there are enough such tiles; else 256-wide tiles on one SM (they halve the
+// shared-memory traffic per product, but only pay when there are enough of them); else 128-wide tiles.
 template <typename TOut, bool SWIGLU>
 static int dispatch(const void* x, const void* w, const float* bias, TOut* y, int M, int N, int K, int* err, cudaStream_t stream) {
     const int wide_tiles = ((M + BM - 1) / BM) * ((N + 255) / 256);
+    const int pair_tiles = ((M + 2 * BM - 1) / (2 * BM)) * ((N + 255) / 256);
+    if (pair_mode() && pair_tiles >= sm_count()) return launch_pair<TOut, SWIGLU>(x, w, bias, y, M, N, K, err, stream);
     if (wide_tiles >= sm_count()) return launch<256, TOut, SWIGLU>(x, w, bias, y, M, N, K, err, stream);
     return launch<128, TOut, SWIGLU>(x, w, bias, y, M, N, K, err, stream);
 }
