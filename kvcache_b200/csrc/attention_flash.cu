@@ -12,6 +12,7 @@ using namespace flash;
 
 #define DECODE_STAGES (KVB_HEAD_DIM <= 64 ? 3 : 2)
 #define PREFILL_STAGES 2
+#define PREFILL_MAX_UNITS 16
 
 // ---------------------------------------------------------------------------------------------
 // Decode: one block of four warps per (item, kv head, split).  An item is a segment whose
@@ -244,9 +245,14 @@ KVB_API int kvb_flash_decode(const void* q, void* out, const void* k_pages, cons
 }
 
 // ---------------------------------------------------------------------------------------------
-// Prefill: one block of four warps per (tile, query head); a tile is 64 consecutive query
-// positions of one segment (16 per warp).  Key tiles run from the first key the tile's first
-// row sees to the last row's own position; a warp skips key tiles that none of its rows see.
+// Prefill: one block of four warps per (unit, query head).  A tile is 64 consecutive query positions of one
+// segment (16 per warp); its keys run from the first key its first row sees to its last row's own position.
+// Causal tiles differ in length by a factor of the sequence length over 64, so a tile is cut into units of a
+// bounded number of key tiles (`nsplit` units; the host chooses it from the tile's length): units are what the
+// grid is made of, and they are all about the same size.  A tile with one unit stores its rows directly;
+// otherwise each unit leaves (m, l, acc) of its rows in scratch and the last unit of a (tile, head) to finish
+// (a ticket counter) merges them in unit order, as the decode kernel does with its splits.
+// A warp skips key tiles that none of its rows see.
 // ---------------------------------------------------------------------------------------------
 struct PrefillParams {
     const bf16* q;
@@ -254,10 +260,13 @@ struct PrefillParams {
     const bf16* k_pages;
     const bf16* v_pages;
     const int* block_table;
-    const int* tiles;          // [n_tiles, 2]: segment, first row of the tile within the segment
+    const int* units;          // [n_units, 8]: segment, first row of the tile, unit, units of the tile, tile id, index of the tile's first unit
     const int* seg_q_start;
     const int* seg_q_len;
     const int* seg_kv_len;
+    float* part_o;             // [n_units, Hq, 64, D]
+    float* part_ml;            // [n_units, Hq, 64, 2]
+    int* tickets;              // [n_tiles, Hq], zero between launches
     int table_stride, Hq, Hkv, page_size, page_shift, window;
     float scale_log2;
 };
@@ -267,16 +276,24 @@ __global__ void __launch_bounds__(128) flash_prefill_kernel(const PrefillParams 
     pdl_launch_dependents();
     extern __shared__ __align__(16) unsigned char smem_raw[];
     bf16* smem = reinterpret_cast<bf16*>(smem_raw);
-    const int tile = blockIdx.x, h = blockIdx.y;
-    const int seg = p.tiles[2 * tile], row0 = p.tiles[2 * tile + 1];
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2;
+    __shared__ int ticket_s;
+    const int unit = blockIdx.x, h = blockIdx.y;
+    const int* u = p.units + 8 * unit;
+    const int seg = u[0], row0 = u[1], split = u[2], nsplit = u[3], tile_id = u[4], unit0 = u[5];
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
     const int hk = h / (p.Hq / p.Hkv);
     const int q_start = p.seg_q_start[seg], q_len = p.seg_q_len[seg], kv_len = p.seg_kv_len[seg];
     const int first_pos = kv_len - q_len;                    // position of the segment's first row
     const int tile_rows = min(64, q_len - row0);
     const int pos_first = first_pos + row0, pos_last = first_pos + row0 + tile_rows - 1;
     const int key_lo = (p.window > 0 && pos_first - p.window + 1 > 0) ? pos_first - p.window + 1 : 0;
-    const int kt_begin = key_lo / KT, kt_end = pos_last / KT + 1;
+    const int tile_begin = key_lo / KT, tile_end = pos_last / KT + 1;
+    const int num_tiles = tile_end - tile_begin;
+    const int per_split = (num_tiles + nsplit - 1) / nsplit;
+    const int n_valid = (num_tiles + per_split - 1) / per_split;   // units of this tile that have keys (a window may leave fewer)
+    if (split >= n_valid) return;
+    const int kt_begin = tile_begin + split * per_split;
+    const int kt_end = min(tile_end, kt_begin + per_split);
     const int n = kt_end - kt_begin;
 
     KVSource src{p.k_pages, p.v_pages, p.block_table + (size_t)seg * p.table_stride, hk, p.Hkv, p.page_size, p.page_shift};
@@ -312,33 +329,114 @@ __global__ void __launch_bounds__(128) flash_prefill_kernel(const PrefillParams 
         const int key0 = (kt_begin + i) * KT;
         if (warp_rows > 0 && key0 <= warp_pos_last && key0 + KT > warp_key_lo)
             rows_tile_auto<KT>(w, smem + (2 * s) * TILE_ELEMS, smem + (2 * s + 1) * TILE_ELEMS, key0, p.window, p.scale_log2,
-                           warp_pos_first, warp_pos_last, warp_rows == 16);
+                               warp_pos_first, warp_pos_last, warp_rows == 16);
         __syncthreads();
     }
     rows_finish_sum(w);
     auto out_row = [&](int r) -> bf16* {
         return wrow0 + r < q_len ? p.out + ((size_t)(q_start + wrow0 + r) * p.Hq + h) * D : nullptr;
     };
-    rows_store(w, out_row);
+    if (n_valid == 1) {
+        rows_store(w, out_row);
+        return;
+    }
+    // Leave this unit's (m, l, acc) for its 64 rows, then take a ticket.
+    {
+        float* po = p.part_o + ((size_t)(unit0 + split) * p.Hq + h) * 64 * D;
+        float* pml = p.part_ml + ((size_t)(unit0 + split) * p.Hq + h) * 64 * 2;
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+            const int row = warp * 16 + g + 8 * r;
+#pragma unroll
+            for (int i = 0; i < NT_O; ++i)
+                *reinterpret_cast<float2*>(po + row * D + i * 8 + 2 * t) = make_float2(w.o[i][2 * r], w.o[i][2 * r + 1]);
+            if (t == 0) *reinterpret_cast<float2*>(pml + row * 2) = make_float2(w.m[r], w.l[r]);
+        }
+    }
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) ticket_s = atomicAdd(p.tickets + tile_id * p.Hq + h, 1);
+    __syncthreads();
+    if (ticket_s != n_valid - 1) return;
+    __threadfence();
+    if (tid == 0) p.tickets[tile_id * p.Hq + h] = 0;
+    // Merge in unit order.  weight[row][s] = 2^(m_s - M) / sum_s 2^(m_s - M) l_s; out = sum_s weight_s acc_s.
+    float* wgt = reinterpret_cast<float*>(smem_raw);           // [64][PREFILL_MAX_UNITS]
+    if (tid < tile_rows) {
+        const int row = tid;
+        float M = NEG_INF;
+        float ms[PREFILL_MAX_UNITS], ls[PREFILL_MAX_UNITS];
+#pragma unroll
+        for (int s = 0; s < PREFILL_MAX_UNITS; ++s) {
+            if (s < n_valid) {
+                const float2 ml = __ldcg(reinterpret_cast<const float2*>(p.part_ml + (((size_t)(unit0 + s) * p.Hq + h) * 64 + row) * 2));
+                ms[s] = ml.x; ls[s] = ml.y;
+            } else {
+                ms[s] = NEG_INF; ls[s] = 0.f;
+            }
+            M = fmaxf(M, ms[s]);
+        }
+        const float base = M == NEG_INF ? 0.f : M;
+        float L = 0.f;
+#pragma unroll
+        for (int s = 0; s < PREFILL_MAX_UNITS; ++s) {
+            ms[s] = exp2f(ms[s] - base);
+            L += ms[s] * ls[s];
+        }
+        const float inv = L > 0.f ? 1.f / L : 0.f;
+#pragma unroll
+        for (int s = 0; s < PREFILL_MAX_UNITS; ++s) wgt[row * PREFILL_MAX_UNITS + s] = ms[s] * inv;
+    }
+    __syncthreads();
+    for (int idx = tid; idx < tile_rows * (D / 4); idx += 128) {
+        const int row = idx / (D / 4), d = (idx - row * (D / 4)) * 4;
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int s0 = 0; s0 < n_valid; s0 += 8) {
+            float4 v[8];
+#pragma unroll
+            for (int x = 0; x < 8; ++x)
+                v[x] = s0 + x < n_valid
+                           ? __ldcg(reinterpret_cast<const float4*>(p.part_o + (((size_t)(unit0 + s0 + x) * p.Hq + h) * 64 + row) * D + d))
+                           : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+            for (int x = 0; x < 8; ++x) {
+                const float ws = s0 + x < n_valid ? wgt[row * PREFILL_MAX_UNITS + s0 + x] : 0.f;
+                acc.x += ws * v[x].x; acc.y += ws * v[x].y; acc.z += ws * v[x].z; acc.w += ws * v[x].w;
+            }
+        }
+        bf16* o = p.out + ((size_t)(q_start + row0 + row) * p.Hq + h) * D + d;
+        *reinterpret_cast<uint2*>(o) = make_uint2(pack_bf16(acc.x, acc.y), pack_bf16(acc.z, acc.w));
+    }
 }
 
+// `units`: int32 [n_units, 8] (see PrefillParams); `scratch`: n_units * Hq * 64 * (D + 2) floats (only read and
+// written for tiles of more than one unit); `tickets`: n_tiles * Hq ints, zero before the first launch.
+// A tile may have at most PREFILL_MAX_UNITS units.
+KVB_API int kvb_flash_prefill_max_units() { return PREFILL_MAX_UNITS; }
+
 KVB_API int kvb_flash_prefill(const void* q, void* out, const void* k_pages, const void* v_pages,
-                              const int* block_table, int table_stride, const int* tiles, int n_tiles,
-                              const int* seg_q_start, const int* seg_q_len, const int* seg_kv_len, int Hq, int Hkv,
-                              int page_size, int window, float scale, cudaStream_t stream) {
-    if (n_tiles <= 0) return KVB_OK;
+                              const int* block_table, int table_stride, const int* units, int n_units,
+                              const int* seg_q_start, const int* seg_q_len, const int* seg_kv_len, float* scratch,
+                              int* tickets, int Hq, int Hkv, int page_size, int window, float scale, cudaStream_t stream) {
+    if (n_units <= 0) return KVB_OK;
     if (Hkv < 1 || Hq % Hkv != 0) return KVB_ERR_SHAPE;
     if (page_size < 1 || (page_size & (page_size - 1)) != 0) return KVB_ERR_SHAPE;
     if (Hq > 65535) return KVB_ERR_LIMIT;
     PrefillParams p;
     p.q = (const bf16*)q; p.out = (bf16*)out; p.k_pages = (const bf16*)k_pages; p.v_pages = (const bf16*)v_pages;
-    p.block_table = block_table; p.tiles = tiles; p.seg_q_start = seg_q_start; p.seg_q_len = seg_q_len;
-    p.seg_kv_len = seg_kv_len; p.table_stride = table_stride; p.Hq = Hq; p.Hkv = Hkv; p.page_size = page_size;
+    p.block_table = block_table; p.units = units; p.seg_q_start = seg_q_start; p.seg_q_len = seg_q_len;
+    p.seg_kv_len = seg_kv_len;
+    p.part_o = scratch;
+    p.part_ml = scratch + (size_t)n_units * Hq * 64 * D;
+    p.tickets = tickets;
+    p.table_stride = table_stride; p.Hq = Hq; p.Hkv = Hkv; p.page_size = page_size;
     p.page_shift = 0;
     while ((1 << p.page_shift) < page_size) ++p.page_shift;
     p.window = window;
     p.scale_log2 = scale * 1.4426950408889634f;
-    const size_t smem = (size_t)PREFILL_STAGES * 2 * TILE_ELEMS * sizeof(bf16);
+    size_t smem = (size_t)PREFILL_STAGES * 2 * TILE_ELEMS * sizeof(bf16);
+    const size_t merge = (size_t)64 * PREFILL_MAX_UNITS * sizeof(float);
+    if (merge > smem) smem = merge;
     static bool configured = false;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(flash_prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -347,7 +445,7 @@ KVB_API int kvb_flash_prefill(const void* q, void* out, const void* k_pages, con
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
-    dim3 grid(n_tiles, Hq);
+    dim3 grid(n_units, Hq);
     kvb_launch(flash_prefill_kernel, dim3(grid), dim3(128), smem, stream, p);
     return kvb_launch_status();
 }

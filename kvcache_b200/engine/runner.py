@@ -44,19 +44,47 @@ def _align4(n: int) -> int:
     return (n + 3) & ~3
 
 
+PREFILL_TILE_ROWS = 64          # query rows of a prefill attention tile
+PREFILL_KEY_TILE = 64           # keys the kernel takes at a time
+PREFILL_MAX_UNITS = 16          # most units one tile may be cut into (csrc/attention_flash.cu)
+PREFILL_UNITS_WANTED = 256      # about this many units beyond one per tile, however long the prompts
+
+
+def plan_prefill_units(segments):
+    """The work list of prefill attention.  `segments`: (segment index, tokens cached before the step, tokens
+    it brings) for every segment of more than one token.  A tile is 64 consecutive rows of a segment; a tile
+    whose rows see many keys is cut into units of about equal numbers of key tiles, so that the blocks of the
+    grid - one per (unit, head) - all have about the same work although causal tiles do not.
+    Returns (int32 array [units, 8]: segment, first row, unit, units of the tile, tile id, first unit of the
+    tile, 0, 0; number of tiles)."""
+    tiles = []
+    for seg, start, count in segments:
+        for row0 in range(0, count, PREFILL_TILE_ROWS):
+            rows = min(PREFILL_TILE_ROWS, count - row0)
+            tiles.append((seg, row0, (start + row0 + rows - 1) // PREFILL_KEY_TILE + 1))
+    total = sum(k for _, _, k in tiles)
+    per_unit = max(4, -(-total // PREFILL_UNITS_WANTED))
+    units = []
+    for tile_id, (seg, row0, key_tiles) in enumerate(tiles):
+        nsplit = max(1, min(PREFILL_MAX_UNITS, -(-key_tiles // per_unit)))
+        first = len(units)
+        for split in range(nsplit):
+            units.append((seg, row0, split, nsplit, tile_id, first, 0, 0))
+    return np.asarray(units, dtype=np.int32).reshape(-1, 8), len(tiles)
+
+
 class StepLayout:
     """Where each array of a step's metadata lies in the packed int32 buffer."""
 
     SECTIONS = (("token_ids", "T", 1), ("positions", "T", 1), ("row_segment", "T", 1), ("seg_q_start", "S", 1),
                 ("seg_q_len", "S", 1), ("seg_kv_len", "S", 1), ("seg_slot", "S", 1), ("wanted_rows", "R", 1),
                 ("sample_temperature", "R", 1), ("sample_counter", "R", 1), ("sample_seed", "R", 2),
-                ("decode_items", "S", 1), ("prefill_tiles", "TILES", 2), ("token_src", "T", 1))
-    TILE_ROWS = 64
+                ("decode_items", "S", 1), ("prefill_tiles", "UNITS", 8), ("token_src", "T", 1))
 
     def __init__(self, T: int, S: int, R: int, table_width: int, num_groups: int):
         self.T, self.S, self.R = T, S, R
         self.table_width, self.num_groups = table_width, num_groups
-        sizes = {"T": T, "S": S, "R": R, "TILES": T // self.TILE_ROWS + S}
+        sizes = {"T": T, "S": S, "R": R, "UNITS": 2 * (T // PREFILL_TILE_ROWS + S) + PREFILL_UNITS_WANTED}
         offset = 0
         self.offsets = {}
         for name, dim, words in self.SECTIONS:
@@ -186,17 +214,17 @@ class ModelRunner:
         for g in range(len(self.cache.groups)):
             layout.table(host, g)[:] = self.cache.table_rows(g, slots)
         if T == S:
-            n_items, n_tiles = S, 0
+            n_items, n_units, n_tiles = S, 0, 0
             layout.view(host, "decode_items")[:] = row_segment
         else:
             single = counts_np == 1
             items = np.nonzero(single)[0].astype(np.int32)
             n_items = len(items)
             layout.view(host, "decode_items")[:n_items] = items
-            tiles = [(i, r) for i in np.nonzero(~single)[0] for r in range(0, counts[i], StepLayout.TILE_ROWS)]
-            n_tiles = len(tiles)
-            if n_tiles:
-                layout.view(host, "prefill_tiles")[:2 * n_tiles] = np.asarray(tiles, dtype=np.int32).reshape(-1)
+            units, n_tiles = plan_prefill_units([(int(i), starts[i], counts[i]) for i in np.nonzero(~single)[0]])
+            n_units = len(units)
+            if n_units:
+                layout.view(host, "prefill_tiles")[:8 * n_units] = units.reshape(-1)
 
         dev = self._meta_device
         dev[:layout.total].copy_(staging[:layout.total], non_blocking=True)
@@ -213,7 +241,8 @@ class ModelRunner:
             seg_slot=layout.view(dev, "seg_slot"), wanted_rows=layout.view(dev, "wanted_rows"),
             token_src=layout.view(dev, "token_src"), last_tokens=self.last_tokens,
             decode_items=layout.view(dev, "decode_items")[:n_items], num_decode_items=n_items,
-            prefill_tiles=layout.view(dev, "prefill_tiles")[:2 * n_tiles].view(-1, 2), num_prefill_tiles=n_tiles,
+            prefill_tiles=layout.view(dev, "prefill_tiles")[:8 * n_units].view(-1, 8), num_prefill_units=n_units,
+            num_prefill_tiles=n_tiles,
             max_q_len=int(counts_np.max()), max_kv_len=int((starts_np + counts_np).max()),
             host={"counts": counts_np, "starts": starts_np, "q_start": q_start, "slots": slots})
         view = self.cache.step_view([layout.table(dev, g) for g in range(len(self.cache.groups))])

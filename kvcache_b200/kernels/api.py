@@ -107,7 +107,7 @@ _SIGNATURES = {
                              _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float,
                              _c_void_p],
         "kvb_flash_prefill": [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_int, _c_void_p,
-                              _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_float, _c_void_p],
+                              _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_float, _c_void_p],
     },
     "sampling": {
         "kvb_sample_parts": [_c_int],
@@ -289,13 +289,16 @@ class CudaKernels(KernelSet):
         if (self.flash_attention and q.dtype == torch.bfloat16 and D % 16 == 0 and D <= 128 and num_heads // Hkv <= 16
                 and workspace is not None and batch.decode_items is not None):
             lib = self._flash_library(D)
-            if batch.num_prefill_tiles:
+            if batch.num_prefill_units:
+                units = batch.num_prefill_units
+                scratch = workspace.buffer("attn.prefill_scratch", (units * num_heads * 64 * (D + 2),), torch.float32)
+                tickets = workspace.zeros("attn.prefill_tickets", (max(batch.num_prefill_tiles, 1) * num_heads,), torch.int32)
                 self.launches += 1
                 _check(lib.kvb_flash_prefill(
                     _ptr(q), _ptr(out), _ptr(kv.k_pages), _ptr(kv.v_pages), _ptr(kv.block_table), kv.block_table.shape[1],
-                    _ptr(batch.prefill_tiles), batch.num_prefill_tiles, _ptr(batch.seg_q_start), _ptr(batch.seg_q_len),
-                    _ptr(batch.seg_kv_len), num_heads, Hkv, kv.page_size, spec.window or 0, float(scale), self._stream()),
-                    "flash_prefill")
+                    _ptr(batch.prefill_tiles), units, _ptr(batch.seg_q_start), _ptr(batch.seg_q_len),
+                    _ptr(batch.seg_kv_len), _ptr(scratch), _ptr(tickets), num_heads, Hkv, kv.page_size, spec.window or 0,
+                    float(scale), self._stream()), "flash_prefill")
             n = batch.num_decode_items
             if n:
                 # Sized by the longest request the block table allows, not by this step's lengths, so that the

@@ -75,11 +75,12 @@ class StepBatch:
     wanted_rows: torch.Tensor        # int32 [R]   rows whose logits are returned
     token_src: Optional[torch.Tensor] = None     # int32 [T]: >= 0: the row's token is last_tokens[token_src[r]]
     last_tokens: Optional[torch.Tensor] = None   # int32: tokens the previous step sampled, still on the device
-    # Attention work lists: segments that bring one token, and 64-row tiles (segment, first row)
-    # of the segments that bring more.
+    # Attention work lists: segments that bring one token, and, for the segments that bring more, units of
+    # 64-row tiles (see engine.runner.plan_prefill_units).
     decode_items: Optional[torch.Tensor] = None    # int32 [num_decode_items]
-    prefill_tiles: Optional[torch.Tensor] = None   # int32 [num_prefill_tiles, 2]
+    prefill_tiles: Optional[torch.Tensor] = None   # int32 [num_prefill_units, 8]
     num_decode_items: int = 0
+    num_prefill_units: int = 0
     num_prefill_tiles: int = 0
     max_q_len: int = 1               # host copies, for launch shapes
     max_kv_len: int = 1

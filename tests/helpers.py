@@ -53,10 +53,11 @@ def paged_scenario(segments, *, num_kv_heads: int, head_dim: int, page_size: int
     q_start = np.cumsum([0] + [n for _, n in segments[:-1]]).astype(np.int32)
     dev = lambda a: torch.as_tensor(a, dtype=torch.int32).to(device)
     items = [i for i, (_, n) in enumerate(segments) if n == 1]
-    tiles = [(i, r) for i, (_, n) in enumerate(segments) if n > 1 for r in range(0, n, 64)]
+    from kvcache_b200.engine.runner import plan_prefill_units
+    units, n_tiles = plan_prefill_units([(i, s, n) for i, (s, n) in enumerate(segments) if n > 1])
     batch = StepBatch(
         decode_items=dev(items), num_decode_items=len(items),
-        prefill_tiles=dev(np.asarray(tiles).reshape(-1, 2)), num_prefill_tiles=len(tiles),
+        prefill_tiles=dev(units), num_prefill_units=len(units), num_prefill_tiles=n_tiles,
         num_tokens=T, num_segments=S, num_wanted=0, token_ids=dev(np.zeros(T)), positions=dev(pos),
         row_segment=dev(row_seg), seg_q_start=dev(q_start), seg_q_len=dev([n for _, n in segments]),
         seg_kv_len=dev([s + n for s, n in segments]), seg_slot=dev(np.arange(S)), wanted_rows=dev([]),

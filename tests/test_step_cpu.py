@@ -52,3 +52,22 @@ def test_mixed_with_page_reuse(tmp_path, name):
     got = replay_modes.mixed(runner, seqs)
     for k, tokens in seqs.items():
         assert_close(got[k], logits_of(config, weights, tokens), REL, k)
+
+
+def test_prefill_work_list():
+    """Tiles of 64 rows; long tiles are cut into units of about equal numbers of key tiles."""
+    from kvcache_b200.engine.runner import plan_prefill_units
+    units, n_tiles = plan_prefill_units([(0, 0, 2048), (3, 100, 2)])
+    assert n_tiles == 33 and units.shape[1] == 8
+    by_tile = {}
+    for seg, row0, split, nsplit, tile_id, first, _, _ in units.tolist():
+        by_tile.setdefault(tile_id, []).append((seg, row0, split, nsplit, first))
+    assert len(by_tile) == n_tiles
+    for tile_id, rows in by_tile.items():
+        nsplit = rows[0][3]
+        assert [r[2] for r in rows] == list(range(nsplit)) and len({r[4] for r in rows}) == 1
+        assert 1 <= nsplit <= 16
+    assert by_tile[0][0][3] == 1 and by_tile[31][0][3] == 8 and by_tile[32][0][:2] == (3, 0)   # 32 key tiles in units of 4
+    # However long the prompt, the list stays bounded.
+    units, n_tiles = plan_prefill_units([(0, 0, 32768)])
+    assert n_tiles == 512 and len(units) <= 2 * 512 + 256
