@@ -79,12 +79,13 @@ class StepLayout:
     SECTIONS = (("token_ids", "T", 1), ("positions", "T", 1), ("row_segment", "T", 1), ("seg_q_start", "S", 1),
                 ("seg_q_len", "S", 1), ("seg_kv_len", "S", 1), ("seg_slot", "S", 1), ("wanted_rows", "R", 1),
                 ("sample_temperature", "R", 1), ("sample_counter", "R", 1), ("sample_seed", "R", 2),
-                ("decode_items", "S", 1), ("prefill_tiles", "UNITS", 8), ("token_src", "T", 1))
+                ("decode_items", "S", 1), ("prefill_tiles", "UNITS", 8), ("token_src", "T", 1), ("tc_tiles", "TILES128", 2))
 
     def __init__(self, T: int, S: int, R: int, table_width: int, num_groups: int):
         self.T, self.S, self.R = T, S, R
         self.table_width, self.num_groups = table_width, num_groups
-        sizes = {"T": T, "S": S, "R": R, "UNITS": 2 * (T // PREFILL_TILE_ROWS + S) + PREFILL_UNITS_WANTED}
+        sizes = {"T": T, "S": S, "R": R, "UNITS": 2 * (T // PREFILL_TILE_ROWS + S) + PREFILL_UNITS_WANTED,
+                 "TILES128": T // 128 + S}
         offset = 0
         self.offsets = {}
         for name, dim, words in self.SECTIONS:
@@ -214,7 +215,7 @@ class ModelRunner:
         for g in range(len(self.cache.groups)):
             layout.table(host, g)[:] = self.cache.table_rows(g, slots)
         if T == S:
-            n_items, n_units, n_tiles = S, 0, 0
+            n_items, n_units, n_tiles, n_tc = S, 0, 0, 0
             layout.view(host, "decode_items")[:] = row_segment
         else:
             single = counts_np == 1
@@ -225,6 +226,12 @@ class ModelRunner:
             n_units = len(units)
             if n_units:
                 layout.view(host, "prefill_tiles")[:8 * n_units] = units.reshape(-1)
+            # The same segments as tiles of 128 rows, longest first, for the tensor-memory kernel.
+            tc = [(int(i), r) for i in np.nonzero(~single)[0] for r in range(0, counts[i], 128)]
+            tc.sort(key=lambda t: -(starts[t[0]] + t[1]))
+            n_tc = len(tc)
+            if n_tc:
+                layout.view(host, "tc_tiles")[:2 * n_tc] = np.asarray(tc, dtype=np.int32).reshape(-1)
 
         dev = self._meta_device
         dev[:layout.total].copy_(staging[:layout.total], non_blocking=True)
@@ -242,7 +249,7 @@ class ModelRunner:
             token_src=layout.view(dev, "token_src"), last_tokens=self.last_tokens,
             decode_items=layout.view(dev, "decode_items")[:n_items], num_decode_items=n_items,
             prefill_tiles=layout.view(dev, "prefill_tiles")[:8 * n_units].view(-1, 8), num_prefill_units=n_units,
-            num_prefill_tiles=n_tiles,
+            num_prefill_tiles=n_tiles, tc_tiles=layout.view(dev, "tc_tiles")[:2 * n_tc].view(-1, 2), num_tc_tiles=n_tc,
             max_q_len=int(counts_np.max()), max_kv_len=int((starts_np + counts_np).max()),
             host={"counts": counts_np, "starts": starts_np, "q_start": q_start, "slots": slots})
         view = self.cache.step_view([layout.table(dev, g) for g in range(len(self.cache.groups))])

@@ -32,12 +32,14 @@ MODULES: Dict[str, dict] = {
     "gemm_simt": {"src": "gemm_simt.cu", "deps": ["common.cuh"]},
     "sampling": {"src": "sampling.cu", "deps": ["common.cuh"]},
     "gemm_skinny": {"src": "gemm_skinny.cu", "deps": ["common.cuh"]},
-    "gemm_tcgen05": {"src": "gemm_tcgen05.cu", "deps": ["common.cuh"]},
+    "gemm_tcgen05": {"src": "gemm_tcgen05.cu", "deps": ["common.cuh", "tc_common.cuh"]},
     # Compiled per head size: variant "d<head_dim>" with -DKVB_HEAD_DIM=<head_dim>.
     "attention_flash": {"src": "attention_flash.cu", "deps": ["common.cuh", "flash_core.cuh", "no_alloc.h"]},
+    "attention_tc": {"src": "attention_tc.cu", "deps": ["common.cuh", "tc_common.cuh"]},
 }
 # Variants that `build_all` makes for modules compiled per size.
-DEFAULT_VARIANTS = {"attention_flash": [("d64", ["-DKVB_HEAD_DIM=64"]), ("d128", ["-DKVB_HEAD_DIM=128"])]}
+DEFAULT_VARIANTS = {"attention_flash": [("d64", ["-DKVB_HEAD_DIM=64"]), ("d128", ["-DKVB_HEAD_DIM=128"])],
+                    "attention_tc": [("d64", ["-DKVB_HEAD_DIM=64"]), ("d128", ["-DKVB_HEAD_DIM=128"])]}
 
 _loaded: Dict[str, ctypes.CDLL] = {}
 _lock = threading.Lock()

@@ -55,7 +55,9 @@ def paged_scenario(segments, *, num_kv_heads: int, head_dim: int, page_size: int
     items = [i for i, (_, n) in enumerate(segments) if n == 1]
     from kvcache_b200.engine.runner import plan_prefill_units
     units, n_tiles = plan_prefill_units([(i, s, n) for i, (s, n) in enumerate(segments) if n > 1])
+    tc = [(i, r) for i, (s, n) in enumerate(segments) if n > 1 for r in range(0, n, 128)]
     batch = StepBatch(
+        tc_tiles=dev(np.asarray(tc, dtype=np.int32).reshape(-1, 2)), num_tc_tiles=len(tc),
         decode_items=dev(items), num_decode_items=len(items),
         prefill_tiles=dev(units), num_prefill_units=len(units), num_prefill_tiles=n_tiles,
         num_tokens=T, num_segments=S, num_wanted=0, token_ids=dev(np.zeros(T)), positions=dev(pos),

@@ -293,7 +293,7 @@ FLASH_SCENARIOS = SCENARIOS[:6] + [
 
 
 @pytest.mark.parametrize("scenario", FLASH_SCENARIOS)
-def test_paged_attention_flash(kernels, scenario):
+def test_paged_attention_flash(kernels, request, scenario):
     from kvcache_b200.engine.workspace import Workspace
     segments, Hq, Hkv, D, page, window = scenario
     dtype = torch.bfloat16
@@ -304,6 +304,9 @@ def test_paged_attention_flash(kernels, scenario):
     ref = torch.empty(T, Hq * D, dtype=dtype)
     REF.paged_attention(q, batch, kv, ref, Hq, D ** -0.5)
     ws = Workspace(DEV)
+    saved_tc = kernels.tc_attention_min_rows
+    kernels.tc_attention_min_rows = None                 # this test is about the mma.sync kernels
+    request.addfinalizer(lambda: setattr(kernels, "tc_attention_min_rows", saved_tc))
     for wanted, min_tiles in ((148 * 4, 4), (3, 4), (100000, 1)):   # default; one split; as many as allowed
         kernels.decode_ctas_wanted, kernels.decode_min_tiles = wanted, min_tiles
         out = torch.full((T, Hq * D), float("nan"), dtype=dtype, device=DEV)
@@ -314,6 +317,45 @@ def test_paged_attention_flash(kernels, scenario):
         if name in ws._buffers:
             assert int(ws._buffers[name].sum()) == 0, name
     kernels.check_errors()
+
+
+TC_SCENARIOS = [
+    # (segments (cached, new), Hq, Hkv, D, page, window)
+    ([(0, 128)], 2, 1, 64, 16, None),
+    ([(0, 300)], 4, 2, 64, 16, None),
+    ([(0, 700), (100, 70), (515, 2)], 14, 2, 64, 16, None),
+    ([(1000, 130), (0, 64)], 4, 4, 128, 16, None),
+    ([(0, 520)], 3, 1, 128, 64, None),
+    ([(300, 400)], 6, 2, 64, 8, 150),                       # window: pages behind it are not held
+    ([(0, 257)], 2, 2, 64, 64, 64),
+]
+
+
+@pytest.mark.parametrize("scenario", TC_SCENARIOS)
+def test_paged_attention_tc(kernels, request, scenario):
+    """The tensor-memory prefill attention against float64 on the same bfloat16 inputs.  Pages behind a window
+    are dropped from the block table, as the cache manager does, so the kernel must not touch them."""
+    from kvcache_b200.engine.workspace import Workspace
+    segments, Hq, Hkv, D, page, window = scenario
+    dtype = torch.bfloat16
+    batch, kv = paged_scenario(segments, num_kv_heads=Hkv, head_dim=D, page_size=page, dtype=dtype, device="cpu",
+                               window=window, seed=22)
+    T = batch.num_tokens
+    q = torch.randn(T, Hq * D, generator=torch.Generator().manual_seed(23)).to(dtype)
+    ref = torch.empty(T, Hq * D, dtype=dtype)
+    REF.paged_attention(q, batch, kv, ref, Hq, D ** -0.5)
+    if window:
+        for i, (cached, new) in enumerate(segments):
+            gone = max(0, cached - window + 1) // page
+            kv.block_table[i, :gone] = -1
+    saved = kernels.tc_attention_min_rows
+    kernels.tc_attention_min_rows = 2
+    request.addfinalizer(lambda: setattr(kernels, "tc_attention_min_rows", saved))
+    out = torch.full((T, Hq * D), float("nan"), dtype=dtype, device=DEV)
+    kernels.paged_attention(q.to(DEV), batch_to(batch, DEV), clone_kv(kv, DEV), out, Hq, D ** -0.5, Workspace(DEV))
+    kernels.check_errors()
+    rows = torch.cat([torch.arange(n) + sum(m for _, m in segments[:i]) for i, (_, n) in enumerate(segments) if n > 1])
+    assert_close(out[rows], ref[rows], REL[dtype])
 
 
 def test_flash_attention_sees_one_far_key_and_the_window_edge(kernels):
