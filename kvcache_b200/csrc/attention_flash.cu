@@ -42,9 +42,31 @@ struct DecodeParams {
 
 constexpr int MAX_SPLITS = 32;
 
+#ifdef KVB_TRACE
+// Debug build only: nanosecond time stamps of the phases of every block, read back with kvb_flash_trace_read.
+__device__ long long kvb_trace_buf[8192 * 8];
+__device__ __forceinline__ long long trace_now() {
+    long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+#define TRACE(i)                                                                                              \
+    if (threadIdx.x == 0) {                                                                                   \
+        const int cta = (blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x;                       \
+        if (cta < 8192) kvb_trace_buf[cta * 8 + (i)] = trace_now();                                           \
+    }
+KVB_API int kvb_flash_trace_read(long long* host, int count) {
+    return (int)cudaMemcpyFromSymbol(host, kvb_trace_buf, sizeof(long long) * count);
+}
+#else
+#define TRACE(i)
+#endif
+
 __global__ void __launch_bounds__(128) flash_decode_kernel(const DecodeParams p) {
+    TRACE(0)
     pdl_wait();
     pdl_launch_dependents();
+    TRACE(1)
     extern __shared__ __align__(16) unsigned char smem_raw[];
     bf16* smem = reinterpret_cast<bf16*>(smem_raw);
     __shared__ int ticket_s;
@@ -90,6 +112,7 @@ __global__ void __launch_bounds__(128) flash_decode_kernel(const DecodeParams p)
         cp_async_commit();
         cp_async_wait<STAGES - 1>();
         __syncthreads();
+        if (i == 0) { TRACE(2) }
         const int s = i % STAGES;
         // Of every tile each warp takes 16 keys and keeps its own running (m, l, acc).  Rows that do not
         // exist (beyond rows) have zero queries and are never stored, so only the positions of existing rows
@@ -104,6 +127,7 @@ __global__ void __launch_bounds__(128) flash_decode_kernel(const DecodeParams p)
         __syncthreads();
     }
     rows_finish_sum(w);
+    TRACE(3)
 
     // The four warps' results meet in shared memory (the stages are free now).
     float* wo = reinterpret_cast<float*>(smem_raw);            // [4][16][D]
@@ -149,6 +173,7 @@ __global__ void __launch_bounds__(128) flash_decode_kernel(const DecodeParams p)
     __syncthreads();
     if (tid == 0) ticket_s = atomicAdd(p.tickets + item * p.Hkv + hk, 1);
     __syncthreads();
+    TRACE(4)
     if (ticket_s != n_valid - 1) return;
     __threadfence();
     if (tid == 0) p.tickets[item * p.Hkv + hk] = 0;
@@ -177,6 +202,7 @@ __global__ void __launch_bounds__(128) flash_decode_kernel(const DecodeParams p)
         for (int s = 0; s < n_valid; ++s) wgt[row * MAX_SPLITS + s] *= inv;
     }
     __syncthreads();
+    TRACE(5)
     for (int idx = tid; idx < rows * (D / 4); idx += 128) {
         const int row = idx / (D / 4), d = (idx - row * (D / 4)) * 4;
         const float* po = p.part_o + (slot * 16 + row) * D + d;
@@ -196,6 +222,7 @@ __global__ void __launch_bounds__(128) flash_decode_kernel(const DecodeParams p)
         bf16* o = p.out + ((size_t)(q_start + row / G) * p.Hq + hk * G + row % G) * D + d;
         *reinterpret_cast<uint2*>(o) = make_uint2(pack_bf16(acc.x, acc.y), pack_bf16(acc.z, acc.w));
     }
+    TRACE(6)
 }
 
 // Bytes of scratch for `items` items: partial outputs, partial (m, l), tickets.
@@ -241,6 +268,213 @@ KVB_API int kvb_flash_decode(const void* q, void* out, const void* k_pages, cons
     }
     dim3 grid(nsplit, Hkv, n_items);
     kvb_launch(flash_decode_kernel, dim3(grid), dim3(128), smem, stream, p);
+    return kvb_launch_status();
+}
+
+// ---------------------------------------------------------------------------------------------
+// Decode with the splits of one (item, kv head) as a thread-block cluster: the same scan as above, but the
+// splits meet through distributed shared memory.  Each block leaves its (m, l, acc) in its own shared memory;
+// after a cluster barrier block s merges rows s, s + nsplit, ... from all blocks, in split order, and stores
+// them.  No scratch in global memory, no counter, no block that is left alone with the merge.
+//
+// Keys and values that earlier steps wrote do not depend on the kernel before this one in the stream, so the
+// step's segment data, the block table and the first tiles are fetched before the wait on that kernel; only
+// the queries, and tiles that hold this step's own keys, are read after it.
+// ---------------------------------------------------------------------------------------------
+// Stages of keys/values in shared memory: two blocks share an SM.  (A block that takes most of an SM's shared
+// memory to request its whole split at once was measured slower: clusters of such blocks wait long for a place.)
+#define CLUSTER_STAGES (KVB_HEAD_DIM <= 64 ? 5 : 3)
+constexpr int MAX_CLUSTER = 8;      // the portable limit; clusters of 16 were measured slower (they wait long for a place)
+
+template <int STAGES>
+__global__ void __launch_bounds__(128) flash_decode_cluster_kernel(const __grid_constant__ DecodeParams p) {
+    TRACE(0)
+#ifdef KVB_TRACE
+    if (threadIdx.x == 0) { unsigned smid; asm volatile("mov.u32 %0, %%smid;" : "=r"(smid)); const int cta = (blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x; if (cta < 8192) kvb_trace_buf[cta * 8 + 7] = smid; }
+#endif
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    bf16* smem = reinterpret_cast<bf16*>(smem_raw);
+    const int split = blockIdx.x, hk = blockIdx.y, item = blockIdx.z;       // the cluster spans x: split is the rank
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
+    const int G = p.Hq / p.Hkv;
+    // Written by the host's copy at the start of the step: safe to read before the wait.
+    const int seg = p.items ? p.items[item] : item;
+    const int q_start = p.seg_q_start[seg], q_len = p.seg_q_len[seg], kv_len = p.seg_kv_len[seg];
+    const int rows = q_len * G;
+    const int first_pos = kv_len - q_len;
+    const int key_lo = (p.window > 0 && first_pos - p.window + 1 > 0) ? first_pos - p.window + 1 : 0;
+    const int tile_begin = key_lo / KT, tile_end = (kv_len + KT - 1) / KT;
+    const int num_tiles = tile_end - tile_begin;
+    const int per_split = (num_tiles + p.nsplit - 1) / p.nsplit;
+    const int my_begin = tile_begin + split * per_split;
+    const int my_end = min(tile_end, my_begin + per_split);
+    const int n = max(0, my_end - my_begin);                                // a split may be empty; it still joins the barriers
+
+    KVSource src{p.k_pages, p.v_pages, p.block_table + (size_t)seg * p.table_stride, hk, p.Hkv, p.page_size, p.page_shift};
+    // The tiles of the prologue are old if all their keys lie before this step's first position.
+    const bool early = (my_begin + min(n, STAGES - 1)) * KT <= first_pos;
+    if (early) {
+#pragma unroll
+        for (int s = 0; s < STAGES - 1; ++s) {
+            if (s < n) load_tile(smem + (2 * s) * TILE_ELEMS, smem + (2 * s + 1) * TILE_ELEMS, src, (my_begin + s) * KT, key_lo, kv_len);
+            cp_async_commit();
+        }
+    }
+    pdl_wait();
+    pdl_launch_dependents();
+    TRACE(1)
+    if (!early) {
+#pragma unroll
+        for (int s = 0; s < STAGES - 1; ++s) {
+            if (s < n) load_tile(smem + (2 * s) * TILE_ELEMS, smem + (2 * s + 1) * TILE_ELEMS, src, (my_begin + s) * KT, key_lo, kv_len);
+            cp_async_commit();
+        }
+    }
+    WarpRows w;
+    rows_init(w);
+    auto q_row = [&](int r) -> const bf16* {
+        return r < rows ? p.q + ((size_t)(q_start + r / G) * p.Hq + hk * G + r % G) * D : nullptr;
+    };
+    rows_load_q(w, q_row);
+    w.pos[0] = g < rows ? first_pos + g / G : -1;
+    w.pos[1] = g + 8 < rows ? first_pos + (g + 8) / G : -1;
+
+    for (int i = 0; i < n; ++i) {
+        const int ahead = i + STAGES - 1;
+        if (ahead < n) {
+            const int s = ahead % STAGES;
+            load_tile(smem + (2 * s) * TILE_ELEMS, smem + (2 * s + 1) * TILE_ELEMS, src, (my_begin + ahead) * KT, key_lo, kv_len);
+        }
+        cp_async_commit();
+        cp_async_wait<STAGES - 1>();
+        __syncthreads();
+        if (i == 0) { TRACE(2) }
+        const int s = i % STAGES;
+        const int key0 = (my_begin + i) * KT + warp * 16;
+        if (key0 < kv_len)
+            rows_tile_auto<16>(w, smem + (2 * s) * TILE_ELEMS + warp * 16 * STRIDE,
+                               smem + (2 * s + 1) * TILE_ELEMS + warp * 16 * STRIDE, key0, p.window, p.scale_log2,
+                               first_pos, kv_len - 1, true);
+        __syncthreads();
+    }
+    cp_async_wait<0>();
+    rows_finish_sum(w);
+    TRACE(3)
+
+    // The four warps' results meet in shared memory (the stages are free now), then the block's own result.
+    float* wo = reinterpret_cast<float*>(smem_raw);            // [4][16][D]
+    float* wml = wo + 4 * 16 * D;                              // [4][16][2]
+    float* res_o = wml + 4 * 16 * 2;                           // [16][D]   this block's acc
+    float* res_ml = res_o + 16 * D;                            // [16][2]   this block's (m, l)
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        const int row = g + 8 * r;
+#pragma unroll
+        for (int i = 0; i < NT_O; ++i)
+            *reinterpret_cast<float2*>(wo + (warp * 16 + row) * D + i * 8 + 2 * t) = make_float2(w.o[i][2 * r], w.o[i][2 * r + 1]);
+        if (t == 0) { wml[(warp * 16 + row) * 2] = w.m[r]; wml[(warp * 16 + row) * 2 + 1] = w.l[r]; }
+    }
+    __syncthreads();
+    for (int idx = tid; idx < rows * D; idx += 128) {
+        const int row = idx / D, d = idx - row * D;
+        float M = NEG_INF;
+#pragma unroll
+        for (int x = 0; x < 4; ++x) M = fmaxf(M, wml[(x * 16 + row) * 2]);
+        const float base = M == NEG_INF ? 0.f : M;
+        float L = 0.f, acc = 0.f;
+#pragma unroll
+        for (int x = 0; x < 4; ++x) {
+            const float e = exp2f(wml[(x * 16 + row) * 2] - base);
+            L += e * wml[(x * 16 + row) * 2 + 1];
+            acc += e * wo[(x * 16 + row) * D + d];
+        }
+        if (p.nsplit == 1) {
+            p.out[((size_t)(q_start + row / G) * p.Hq + hk * G + row % G) * D + d] = __float2bfloat16_rn(L > 0.f ? acc / L : 0.f);
+        } else {
+            res_o[row * D + d] = acc;
+            if (d == 0) { res_ml[row * 2] = M; res_ml[row * 2 + 1] = L; }
+        }
+    }
+    if (p.nsplit == 1) return;
+
+    cluster_sync_all();                                        // every block's result is in its shared memory
+    TRACE(4)
+    // Block s takes rows s, s + nsplit, ...; a thread takes four columns of one row.
+    // weight_s = 2^(m_s - M) / sum_s 2^(m_s - M) l_s; out = sum_s weight_s acc_s, added in split order.
+    const int my_rows = rows > split ? (rows - split + p.nsplit - 1) / p.nsplit : 0;
+    for (int idx = tid; idx < my_rows * (D / 4); idx += 128) {
+        const int row = split + (idx / (D / 4)) * p.nsplit, d = (idx % (D / 4)) * 4;
+        float2 ml[MAX_CLUSTER];
+        float4 v[MAX_CLUSTER];
+#pragma unroll
+        for (int s = 0; s < MAX_CLUSTER; ++s) {
+            if (s < p.nsplit) {
+                ml[s] = peer_ld2(peer_smem(res_ml + row * 2, s));
+                v[s] = peer_ld4(peer_smem(res_o + row * D + d, s));
+            } else {
+                ml[s] = make_float2(NEG_INF, 0.f);
+                v[s] = make_float4(0.f, 0.f, 0.f, 0.f);
+            }
+        }
+        float M = NEG_INF;
+#pragma unroll
+        for (int s = 0; s < MAX_CLUSTER; ++s) M = fmaxf(M, ml[s].x);
+        const float base = M == NEG_INF ? 0.f : M;
+        float L = 0.f;
+        float e[MAX_CLUSTER];
+#pragma unroll
+        for (int s = 0; s < MAX_CLUSTER; ++s) {
+            e[s] = exp2f(ml[s].x - base);
+            L += e[s] * ml[s].y;
+        }
+        const float inv = L > 0.f ? 1.f / L : 0.f;
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+        for (int s = 0; s < MAX_CLUSTER; ++s) {
+            const float ws = e[s] * inv;
+            acc.x += ws * v[s].x; acc.y += ws * v[s].y; acc.z += ws * v[s].z; acc.w += ws * v[s].w;
+        }
+        bf16* o = p.out + ((size_t)(q_start + row / G) * p.Hq + hk * G + row % G) * D + d;
+        *reinterpret_cast<uint2*>(o) = make_uint2(pack_bf16(acc.x, acc.y), pack_bf16(acc.z, acc.w));
+    }
+    TRACE(5)
+    cluster_sync_all();                                        // no block leaves while another still reads its result
+    TRACE(6)
+}
+
+// The splits as a cluster: nsplit 1..8, no scratch.
+KVB_API int kvb_flash_decode_cluster(const void* q, void* out, const void* k_pages, const void* v_pages,
+                                     const int* block_table, int table_stride, const int* items, int n_items,
+                                     const int* seg_q_start, const int* seg_q_len, const int* seg_kv_len, int Hq, int Hkv,
+                                     int page_size, int window, int nsplit, float scale, cudaStream_t stream) {
+    if (n_items <= 0) return KVB_OK;
+    if (Hkv < 1 || Hq % Hkv != 0 || Hq / Hkv > 16) return KVB_ERR_SHAPE;
+    if (page_size < 1 || (page_size & (page_size - 1)) != 0) return KVB_ERR_SHAPE;
+    if (nsplit < 1 || nsplit > MAX_CLUSTER || n_items > 65535 || Hkv > 65535) return KVB_ERR_LIMIT;
+    DecodeParams p;
+    p.q = (const bf16*)q; p.out = (bf16*)out; p.k_pages = (const bf16*)k_pages; p.v_pages = (const bf16*)v_pages;
+    p.block_table = block_table; p.items = items; p.seg_q_start = seg_q_start; p.seg_q_len = seg_q_len;
+    p.seg_kv_len = seg_kv_len;
+    p.part_o = nullptr; p.part_ml = nullptr; p.tickets = nullptr;
+    p.table_stride = table_stride; p.Hq = Hq; p.Hkv = Hkv; p.page_size = page_size;
+    p.page_shift = 0;
+    while ((1 << p.page_shift) < page_size) ++p.page_shift;
+    p.window = window; p.nsplit = nsplit;
+    p.scale_log2 = scale * 1.4426950408889634f;
+    auto kernel = flash_decode_cluster_kernel<CLUSTER_STAGES>;
+    size_t smem = (size_t)CLUSTER_STAGES * 2 * TILE_ELEMS * sizeof(bf16);
+    const size_t merge = (size_t)(5 * 16 * D + 5 * 16 * 2) * sizeof(float);
+    if (merge > smem) smem = merge;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+        e = cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+        if (e != cudaSuccess) return (int)e;
+        configured = true;
+    }
+    dim3 grid(nsplit, Hkv, n_items);
+    kvb_launch_cluster(kernel, dim3(grid), dim3(128), (unsigned)nsplit, smem, stream, p);
     return kvb_launch_status();
 }
 

@@ -12,7 +12,10 @@
 // leaves the sum unchanged).
 //
 // A block owns 16 * RT consecutive rows of W (columns of y); its warps split K and add their
-// partial sums in shared memory in warp order, so a result does not depend on the grid.
+// partial sums in shared memory in warp order.  When W has too few rows to give every SM a block
+// (N of a hidden size), K is also split over the `ksplit` blocks of a thread-block cluster, whose
+// sums meet through distributed shared memory and are added in rank order.  The split depends on
+// the shape alone, so a result does not depend on the batch or the grid.
 //
 // Fused output (`swiglu` = 1): W is the gate/up matrix with rows interleaved in eights - rows 16 b .. 16 b + 7
 // are gate rows 8 b .. 8 b + 7 and rows 16 b + 8 .. 16 b + 15 the up rows of the same indices - so a thread
@@ -34,16 +37,29 @@ __device__ __forceinline__ uint4 ld_stream(const void* p) {      // weights: rea
     return v;
 }
 
+constexpr int BLOCKS_WANTED = 148 * 2;
+
+// Weights that products after this one will stream (up to two ranges).  The blocks of this kernel ask for
+// them to be brought into L2 while they wait for their own input: the wait falls into the time of the kernel
+// before, which may be one that leaves the memory system idle.
+struct Upcoming {
+    const char* ptr[2];
+    long long bytes[2];
+};
+
 template <int RT, int NT, bool ACT, typename TOut>
 __global__ void __launch_bounds__(256) gemm_skinny_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w,
                                                           const float* __restrict__ bias, TOut* __restrict__ y, int M,
-                                                          int N, int K, int x_stride) {
-    extern __shared__ __align__(16) float red[];          // [warps][RT][NT][32 lanes][4]
+                                                          int N, int K, int x_stride, int ksplit, Upcoming up) {
+    extern __shared__ __align__(16) float red[];          // [warps + 1][RT][NT][32 lanes][4]
     const int warps = blockDim.x >> 5, warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
-    const int n0 = blockIdx.x * 16 * RT;
+    const int rank = blockIdx.x % ksplit;                  // the cluster spans x
+    const int n0 = (blockIdx.x / ksplit) * 16 * RT;
     const int kblocks = K / 32;                            // K is a multiple of 32 (checked by the launcher)
-    const int per_warp = (kblocks + warps - 1) / warps;
-    const int kb_begin = min(kblocks, warp * per_warp), kb_end = min(kblocks, kb_begin + per_warp);
+    const int per_block = (kblocks + ksplit - 1) / ksplit;
+    const int block_begin = min(kblocks, rank * per_block), block_end = min(kblocks, block_begin + per_block);
+    const int per_warp = (block_end - block_begin + warps - 1) / warps;
+    const int kb_begin = min(block_end, block_begin + warp * per_warp), kb_end = min(block_end, kb_begin + per_warp);
 
     // Before waiting for the kernel that makes x: pull this warp's slice of the weights (which no kernel
     // writes) towards L2, so that the predecessor's tail and this kernel's memory latency overlap.
@@ -55,6 +71,12 @@ __global__ void __launch_bounds__(256) gemm_skinny_kernel(const bf16* __restrict
             const char* p = reinterpret_cast<const char*>(w + (size_t)row * K + kb_begin * 32) + (i % lines) * 128;
             asm volatile("prefetch.global.L2 [%0];" ::"l"(p));
         }
+    }
+#pragma unroll
+    for (int u = 0; u < 2; ++u) {
+        const long long lines = (up.bytes[u] + 127) / 128;
+        for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < lines; i += (long long)gridDim.x * blockDim.x)
+            asm volatile("prefetch.global.L2 [%0];" ::"l"(up.ptr[u] + i * 128));
     }
     pdl_wait();
     pdl_launch_dependents();
@@ -119,11 +141,33 @@ __global__ void __launch_bounds__(256) gemm_skinny_kernel(const bf16* __restrict
 #pragma unroll
         for (int j = 0; j < NT; ++j) mine[(r * NT + j) * 32] = make_float4(acc[r][j][0], acc[r][j][1], acc[r][j][2], acc[r][j][3]);
     __syncthreads();
-    for (int idx = threadIdx.x; idx < RT * NT * 32; idx += blockDim.x) {
-        float4 s = reinterpret_cast<const float4*>(red)[idx];
-        for (int wi = 1; wi < warps; ++wi) {
-            const float4 v = reinterpret_cast<const float4*>(red)[(size_t)wi * RT * NT * 32 + idx];
-            s.x += v.x; s.y += v.y; s.z += v.z; s.w += v.w;
+    float4* total = reinterpret_cast<float4*>(red) + (size_t)warps * RT * NT * 32;     // this block's sums
+    if (ksplit > 1) {
+        for (int idx = threadIdx.x; idx < RT * NT * 32; idx += blockDim.x) {
+            float4 s = reinterpret_cast<const float4*>(red)[idx];
+            for (int wi = 1; wi < warps; ++wi) {
+                const float4 v = reinterpret_cast<const float4*>(red)[(size_t)wi * RT * NT * 32 + idx];
+                s.x += v.x; s.y += v.y; s.z += v.z; s.w += v.w;
+            }
+            total[idx] = s;
+        }
+        cluster_sync_all();
+    }
+    // With a cluster, block `rank` finishes the fragments idx = rank, rank + ksplit, ...
+    for (int idx = threadIdx.x * ksplit + rank; idx < RT * NT * 32; idx += blockDim.x * ksplit) {
+        float4 s;
+        if (ksplit > 1) {
+            s = peer_ld4(peer_smem(total + idx, 0));
+            for (int r = 1; r < ksplit; ++r) {
+                const float4 v = peer_ld4(peer_smem(total + idx, r));
+                s.x += v.x; s.y += v.y; s.z += v.z; s.w += v.w;
+            }
+        } else {
+            s = reinterpret_cast<const float4*>(red)[idx];
+            for (int wi = 1; wi < warps; ++wi) {
+                const float4 v = reinterpret_cast<const float4*>(red)[(size_t)wi * RT * NT * 32 + idx];
+                s.x += v.x; s.y += v.y; s.z += v.z; s.w += v.w;
+            }
         }
         // idx = (r * NT + j) * 32 + lane'; the fragment holds y[m = 8 j + 2 t' (+1)][n = n0 + 16 r + g' (+8)].
         const int l2 = idx & 31, rj = idx >> 5, r = rj / NT, j = rj - r * NT, g2 = l2 >> 2, t2 = l2 & 3;
@@ -147,37 +191,46 @@ __global__ void __launch_bounds__(256) gemm_skinny_kernel(const bf16* __restrict
             }
         }
     }
+    if (ksplit > 1) cluster_sync_all();                    // no block leaves while another still reads its sums
 }
 
 template <int RT, int NT, bool ACT, typename TOut>
-int launch(const bf16* x, const bf16* w, const float* bias, TOut* y, int M, int N, int K, int x_stride, int warps,
+int launch(const bf16* x, const bf16* w, const float* bias, TOut* y, int M, int N, int K, int x_stride, const Upcoming& up,
            cudaStream_t stream) {
-    const size_t smem = (size_t)warps * RT * NT * 32 * 4 * sizeof(float);
+    const int kblocks = K / 32;
+    const int blocks = (N + 16 * RT - 1) / (16 * RT);
+    // K over a cluster while that still leaves blocks wanted and every warp of a block something to do.
+    int ksplit = 1;
+    while (ksplit < 8 && blocks * ksplit * 2 <= BLOCKS_WANTED && kblocks / (ksplit * 2) >= 4) ksplit *= 2;
+    // Warps split a block's share of K: enough of them to keep loads in flight, not so many that a warp has nothing to do.
+    const int warps = kblocks / ksplit >= 32 ? 8 : 4;
+    const size_t smem = (size_t)(warps + 1) * RT * NT * 32 * 4 * sizeof(float);
     auto kernel = gemm_skinny_kernel<RT, NT, ACT, TOut>;
     if (smem > 48 * 1024) {
         cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return (int)e;
     }
-    const int blocks = (N + 16 * RT - 1) / (16 * RT);
-    kvb_launch(kernel, dim3(blocks), dim3(warps * 32), smem, stream, x, w, bias, y, M, N, K, x_stride);
+    if (ksplit > 1)
+        kvb_launch_cluster(kernel, dim3(blocks * ksplit), dim3(warps * 32), (unsigned)ksplit, smem, stream, x, w, bias, y, M, N,
+                           K, x_stride, ksplit, up);
+    else
+        kvb_launch(kernel, dim3(blocks), dim3(warps * 32), smem, stream, x, w, bias, y, M, N, K, x_stride, ksplit, up);
     return kvb_launch_status();
 }
 
 template <bool ACT, typename TOut>
-int dispatch(const bf16* x, const bf16* w, const float* bias, TOut* y, int M, int N, int K, int x_stride, cudaStream_t stream) {
-    // Warps split K: enough of them to keep loads in flight, not so many that a warp has nothing to do.
-    const int kblocks = K / 32;
-    const int warps = kblocks >= 64 ? 8 : 4;
+int dispatch(const bf16* x, const bf16* w, const float* bias, TOut* y, int M, int N, int K, int x_stride, const Upcoming& up,
+             cudaStream_t stream) {
     // Rows of W per block: two 16-row tiles when there are plenty of blocks anyway.
     const bool wide = N >= 16 * 2 * 148 * 4;
-    if (M <= 8) return wide ? launch<2, 1, ACT, TOut>(x, w, bias, y, M, N, K, x_stride, warps, stream)
-                            : launch<1, 1, ACT, TOut>(x, w, bias, y, M, N, K, x_stride, warps, stream);
-    if (M <= 16) return wide ? launch<2, 2, ACT, TOut>(x, w, bias, y, M, N, K, x_stride, warps, stream)
-                             : launch<1, 2, ACT, TOut>(x, w, bias, y, M, N, K, x_stride, warps, stream);
-    if (M <= 32) return wide ? launch<2, 4, ACT, TOut>(x, w, bias, y, M, N, K, x_stride, warps, stream)
-                             : launch<1, 4, ACT, TOut>(x, w, bias, y, M, N, K, x_stride, warps, stream);
-    return wide ? launch<2, 8, ACT, TOut>(x, w, bias, y, M, N, K, x_stride, warps, stream)
-                : launch<1, 8, ACT, TOut>(x, w, bias, y, M, N, K, x_stride, warps, stream);
+    if (M <= 8) return wide ? launch<2, 1, ACT, TOut>(x, w, bias, y, M, N, K, x_stride, up, stream)
+                            : launch<1, 1, ACT, TOut>(x, w, bias, y, M, N, K, x_stride, up, stream);
+    if (M <= 16) return wide ? launch<2, 2, ACT, TOut>(x, w, bias, y, M, N, K, x_stride, up, stream)
+                             : launch<1, 2, ACT, TOut>(x, w, bias, y, M, N, K, x_stride, up, stream);
+    if (M <= 32) return wide ? launch<2, 4, ACT, TOut>(x, w, bias, y, M, N, K, x_stride, up, stream)
+                             : launch<1, 4, ACT, TOut>(x, w, bias, y, M, N, K, x_stride, up, stream);
+    return wide ? launch<2, 8, ACT, TOut>(x, w, bias, y, M, N, K, x_stride, up, stream)
+                : launch<1, 8, ACT, TOut>(x, w, bias, y, M, N, K, x_stride, up, stream);
 }
 
 }  // namespace skinny
@@ -185,8 +238,10 @@ int dispatch(const bf16* x, const bf16* w, const float* bias, TOut* y, int M, in
 // x: [M, K] bfloat16; w: [N, K] bfloat16; bias: float32 [N] or null; y: [M, N] bfloat16 (out_dtype 1) or float32
 // (out_dtype 0) - or, with swiglu = 1, [M, N / 2] from interleaved gate/up rows (N a multiple of 16, no bias).
 // Refuses M > 64, K not a multiple of 32, misaligned operands.
+// `up0`/`up1` (+ bytes; may be null/0): weights that later products will stream, to be brought into L2 meanwhile.
 KVB_API int kvb_gemm_skinny(int out_dtype, int act, const void* x, const void* w, const float* bias, void* y, int M,
-                            int N, int K, cudaStream_t stream) {
+                            int N, int K, const void* up0, long long up0_bytes, const void* up1, long long up1_bytes,
+                            cudaStream_t stream) {
     if (M <= 0 || N <= 0) return KVB_OK;
     if (M > 64 || K <= 0 || K % 32 != 0) return KVB_ERR_SHAPE;
     if (((uintptr_t)x | (uintptr_t)w) & 15) return KVB_ERR_ALIGN;
@@ -194,11 +249,14 @@ KVB_API int kvb_gemm_skinny(int out_dtype, int act, const void* x, const void* w
     const bf16* wb = (const bf16*)w;
     if (act && (N % 16 != 0 || bias != nullptr)) return KVB_ERR_SHAPE;
     const int x_stride = K;
+    skinny::Upcoming up;
+    up.ptr[0] = (const char*)up0; up.bytes[0] = up0 ? up0_bytes : 0;
+    up.ptr[1] = (const char*)up1; up.bytes[1] = up1 ? up1_bytes : 0;
     if (out_dtype == KVB_BF16)
-        return act ? skinny::dispatch<true, bf16>(xb, wb, bias, (bf16*)y, M, N, K, x_stride, stream)
-                   : skinny::dispatch<false, bf16>(xb, wb, bias, (bf16*)y, M, N, K, x_stride, stream);
+        return act ? skinny::dispatch<true, bf16>(xb, wb, bias, (bf16*)y, M, N, K, x_stride, up, stream)
+                   : skinny::dispatch<false, bf16>(xb, wb, bias, (bf16*)y, M, N, K, x_stride, up, stream);
     if (out_dtype == KVB_F32)
-        return act ? skinny::dispatch<true, float>(xb, wb, bias, (float*)y, M, N, K, x_stride, stream)
-                   : skinny::dispatch<false, float>(xb, wb, bias, (float*)y, M, N, K, x_stride, stream);
+        return act ? skinny::dispatch<true, float>(xb, wb, bias, (float*)y, M, N, K, x_stride, up, stream)
+                   : skinny::dispatch<false, float>(xb, wb, bias, (float*)y, M, N, K, x_stride, up, stream);
     return KVB_ERR_DTYPE;
 }

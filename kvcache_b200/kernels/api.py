@@ -16,7 +16,7 @@ import torch
 from ..parts.base import PagedKVView, StepBatch
 from . import build
 
-_c_int, _c_float, _c_void_p = ctypes.c_int, ctypes.c_float, ctypes.c_void_p
+_c_int, _c_float, _c_void_p, _c_longlong = ctypes.c_int, ctypes.c_float, ctypes.c_void_p, ctypes.c_longlong
 
 DEVICE_ERRORS = {8: "a wait inside a kernel ran out (a pipeline stalled); the step's results are not valid",
                  1: "a token id outside the vocabulary",
@@ -96,7 +96,8 @@ _SIGNATURES = {
         "kvb_gemm_simt": [_c_int, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_void_p],
     },
     "gemm_skinny": {
-        "kvb_gemm_skinny": [_c_int, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_void_p],
+        "kvb_gemm_skinny": [_c_int, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_void_p,
+                            _c_longlong, _c_void_p, _c_longlong, _c_void_p],
     },
     "gemm_tcgen05": {
         "kvb_gemm_tcgen05": [_c_int, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_void_p, _c_void_p],
@@ -106,6 +107,9 @@ _SIGNATURES = {
         "kvb_flash_decode": [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_int, _c_void_p,
                              _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float,
                              _c_void_p],
+        "kvb_flash_decode_cluster": [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_int,
+                                     _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float,
+                                     _c_void_p],
         "kvb_flash_prefill": [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_int, _c_void_p,
                               _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_float, _c_void_p],
     },
@@ -170,7 +174,12 @@ class CudaKernels(KernelSet):
         # (bfloat16, head size 64 or 128, pages of 8..64 tokens); None turns it off.
         self.tc_attention_min_rows: Optional[int] = 64
         self.flash_attention = True          # bfloat16, head sizes 16..128: tensor-core kernels
-        self.decode_ctas_wanted = 148 * 4    # the split over the keys aims at this many blocks in flight
+        # Decode attention splits the keys of a request over blocks.  "cluster": the splits (at most 8) are a
+        # thread-block cluster and merge through distributed shared memory; "ticket": up to 32 splits leave
+        # partial results in scratch and the last one to finish merges them.
+        self.decode_merge = "cluster"
+        self.decode_cluster_max = 8          # the kernel's limit
+        self.decode_ctas_wanted = 148 * 2    # the split over the keys aims at this many blocks in flight
         self.decode_min_tiles = 4            # ... but gives a split at least this many 64-key tiles
         self.sm_count = torch.cuda.get_device_properties(self.device).multi_processor_count
         self.error_word = torch.zeros(1, dtype=torch.int32, device=self.device)
@@ -210,15 +219,27 @@ class CudaKernels(KernelSet):
         _check(self._elementwise.kvb_silu_mul(_dtype_code(out.dtype), _ptr(gate_up), _ptr(out), T, I,
                                               1 if interleaved else 0, self._stream()), "silu_mul")
 
-    def gate_up_act(self, x: torch.Tensor, w_gate_up: torch.Tensor, out: torch.Tensor, workspace, interleaved: bool) -> None:
+    @staticmethod
+    def _upcoming_args(upcoming) -> tuple:
+        """(pointer, bytes) of the first two tensors of `upcoming` for the small-M product's prefetch."""
+        args = []
+        for t in list(upcoming or ())[:2]:
+            args += [_ptr(t), t.numel() * t.element_size()]
+        while len(args) < 4:
+            args += [_ptr(None), 0]
+        return tuple(args)
+
+    def gate_up_act(self, x: torch.Tensor, w_gate_up: torch.Tensor, out: torch.Tensor, workspace, interleaved: bool,
+                    upcoming: Optional[Sequence[torch.Tensor]] = None) -> None:
         """out[M, I] = silu(x Wg^T) * (x Wu^T); `w_gate_up` [2 I, K] holds gate and up rows one after the
-        other, or interleaved in eights (see csrc/gemm_skinny.cu)."""
+        other, or interleaved in eights (see csrc/gemm_skinny.cu).  `upcoming`: as in `linear`."""
         M, K = x.shape
         I = out.shape[1]
         if interleaved and self._skinny(x.dtype, M, K):
             self.launches += 1
             _check(self._gemm_skinny.kvb_gemm_skinny(_dtype_code(out.dtype), 1, _ptr(x), _ptr(w_gate_up), _ptr(None),
-                                                     _ptr(out), M, 2 * I, K, self._stream()), "gate_up_act (skinny)")
+                                                     _ptr(out), M, 2 * I, K, *self._upcoming_args(upcoming),
+                                                     self._stream()), "gate_up_act (skinny)")
             return
         if interleaved and self._tcgen05(x, w_gate_up, out, fused=True):
             self.launches += 1
@@ -242,8 +263,10 @@ class CudaKernels(KernelSet):
             return fused and -(-x.shape[0] // 256) * -(-w.shape[0] // 256) >= self.sm_count
         return self.bf16_gemm == "tcgen05"
 
-    def linear(self, x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bias: Optional[torch.Tensor] = None) -> None:
-        """out = x . w^T + bias."""
+    def linear(self, x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bias: Optional[torch.Tensor] = None,
+               upcoming: Optional[Sequence[torch.Tensor]] = None) -> None:
+        """out = x . w^T + bias.  `upcoming`: weights that products after this one will read (a hint: the
+        small-M kernel asks for the first two to be brought into L2 while it waits for x; others ignore it)."""
         M = x.shape[0]
         N, K = w.shape
         if x.shape[1] != K or tuple(out.shape) != (M, N):
@@ -251,7 +274,8 @@ class CudaKernels(KernelSet):
         self.launches += 1
         if self._skinny(x.dtype, M, K):
             _check(self._gemm_skinny.kvb_gemm_skinny(_dtype_code(out.dtype), 0, _ptr(x), _ptr(w), _ptr(bias),
-                                                     _ptr(out), M, N, K, self._stream()), "linear (skinny)")
+                                                     _ptr(out), M, N, K, *self._upcoming_args(upcoming), self._stream()),
+                   "linear (skinny)")
             return
         if self._tcgen05(x, w, out):
             _check(self._gemm_tc.kvb_gemm_tcgen05(_dtype_code(out.dtype), 0, _ptr(x), _ptr(w), _ptr(bias), _ptr(out), M, N, K,
@@ -324,7 +348,17 @@ class CudaKernels(KernelSet):
                 # Sized by the longest request the block table allows, not by this step's lengths, so that the
                 # split (and with it the rounding) is the same in every step and under a CUDA graph.
                 tiles = -(-(kv.block_table.shape[1] * kv.page_size) // 64)
-                nsplit = max(1, min(32, self.decode_ctas_wanted // (n * Hkv), tiles // self.decode_min_tiles))
+                if self.decode_merge == "cluster":
+                    nsplit = max(1, min(self.decode_cluster_max, self.decode_ctas_wanted // (n * Hkv),
+                                        tiles // self.decode_min_tiles))
+                    self.launches += 1
+                    _check(lib.kvb_flash_decode_cluster(
+                        _ptr(q), _ptr(out), _ptr(kv.k_pages), _ptr(kv.v_pages), _ptr(kv.block_table),
+                        kv.block_table.shape[1], _ptr(batch.decode_items), n, _ptr(batch.seg_q_start),
+                        _ptr(batch.seg_q_len), _ptr(batch.seg_kv_len), num_heads, Hkv, kv.page_size, spec.window or 0,
+                        nsplit, float(scale), self._stream()), "flash_decode_cluster")
+                    return
+                nsplit = max(1, min(32, 2 * self.decode_ctas_wanted // (n * Hkv), tiles // self.decode_min_tiles))
                 scratch = workspace.buffer("attn.decode_scratch", (n * Hkv * nsplit * 16 * (D + 2),), torch.float32)
                 tickets = workspace.zeros("attn.decode_tickets", (n * Hkv,), torch.int32)
                 self.launches += 1

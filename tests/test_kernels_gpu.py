@@ -100,7 +100,8 @@ def test_gemm_simt(kernels, in_dtype, out_dtype, M, N, K):
 
 
 @pytest.mark.parametrize("M,N,K", [(1, 256, 64), (3, 331, 96), (8, 1152, 896), (8, 896, 4864), (9, 40, 32), (16, 9728, 896),
-                                   (17, 1000, 320), (33, 151936, 64), (64, 1152, 896), (64, 200, 4864), (5, 20000, 128)])
+                                   (17, 1000, 320), (33, 151936, 64), (64, 1152, 896), (64, 200, 4864), (5, 20000, 128),
+                                   (2, 48, 1024), (5, 100, 736)])     # K over a cluster of 8; uneven shares of K
 def test_gemm_skinny(kernels, request, M, N, K):
     g = torch.Generator().manual_seed(16)
     x = torch.randn(M, K, generator=g).to(torch.bfloat16)
@@ -307,12 +308,17 @@ def test_paged_attention_flash(kernels, request, scenario):
     saved_tc = kernels.tc_attention_min_rows
     kernels.tc_attention_min_rows = None                 # this test is about the mma.sync kernels
     request.addfinalizer(lambda: setattr(kernels, "tc_attention_min_rows", saved_tc))
-    for wanted, min_tiles in ((148 * 4, 4), (3, 4), (100000, 1)):   # default; one split; as many as allowed
-        kernels.decode_ctas_wanted, kernels.decode_min_tiles = wanted, min_tiles
-        out = torch.full((T, Hq * D), float("nan"), dtype=dtype, device=DEV)
-        kernels.paged_attention(q.to(DEV), batch_to(batch, DEV), clone_kv(kv, DEV), out, Hq, D ** -0.5, ws)
-        assert_close(out, ref, REL[dtype], f"decode_ctas_wanted={wanted}")
-    kernels.decode_ctas_wanted, kernels.decode_min_tiles = 148 * 4, 4
+    saved = (kernels.decode_merge, kernels.decode_ctas_wanted, kernels.decode_min_tiles)
+    request.addfinalizer(lambda: [setattr(kernels, n, v) for n, v in
+                                  zip(("decode_merge", "decode_ctas_wanted", "decode_min_tiles"), saved)])
+    for merge in ("cluster", "ticket"):                  # the splits of a request as a cluster, or through scratch
+        kernels.decode_merge = merge
+        # default; one split; as many as allowed; a number of splits that does not divide the rows
+        for wanted, min_tiles in ((saved[1], saved[2]), (3, 4), (100000, 1), (5 * len(segments) * Hkv, 1)):
+            kernels.decode_ctas_wanted, kernels.decode_min_tiles = wanted, min_tiles
+            out = torch.full((T, Hq * D), float("nan"), dtype=dtype, device=DEV)
+            kernels.paged_attention(q.to(DEV), batch_to(batch, DEV), clone_kv(kv, DEV), out, Hq, D ** -0.5, ws)
+            assert_close(out, ref, REL[dtype], f"decode_merge={merge} decode_ctas_wanted={wanted}")
     for name in ("attn.decode_tickets", "attn.prefill_tickets"):
         if name in ws._buffers:
             assert int(ws._buffers[name].sum()) == 0, name
