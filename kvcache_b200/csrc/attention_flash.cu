@@ -42,25 +42,6 @@ struct DecodeParams {
 
 constexpr int MAX_SPLITS = 32;
 
-#ifdef KVB_TRACE
-// Debug build only: nanosecond time stamps of the phases of every block, read back with kvb_flash_trace_read.
-__device__ long long kvb_trace_buf[8192 * 8];
-__device__ __forceinline__ long long trace_now() {
-    long long t;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-    return t;
-}
-#define TRACE(i)                                                                                              \
-    if (threadIdx.x == 0) {                                                                                   \
-        const int cta = (blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x;                       \
-        if (cta < 8192) kvb_trace_buf[cta * 8 + (i)] = trace_now();                                           \
-    }
-KVB_API int kvb_flash_trace_read(long long* host, int count) {
-    return (int)cudaMemcpyFromSymbol(host, kvb_trace_buf, sizeof(long long) * count);
-}
-#else
-#define TRACE(i)
-#endif
 
 __global__ void __launch_bounds__(128) flash_decode_kernel(const DecodeParams p) {
     TRACE(0)

@@ -160,3 +160,24 @@ static inline int kvb_launch_status() {
     cudaError_t e = cudaGetLastError();
     return e == cudaSuccess ? KVB_OK : (int)e;
 }
+
+#ifdef KVB_TRACE
+// Debug builds only (-DKVB_TRACE): nanosecond time stamps of the phases of every block of the module's last
+// kernel, slot i of block b at [b * 8 + i]; read back with kvb_trace_read.
+__device__ long long kvb_trace_buf[8192 * 8];
+__device__ __forceinline__ long long trace_now() {
+    long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+#define TRACE(i)                                                                                              \
+    if (threadIdx.x == 0) {                                                                                   \
+        const int cta = (blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x;                       \
+        if (cta < 8192) kvb_trace_buf[cta * 8 + (i)] = trace_now();                                           \
+    }
+KVB_API int kvb_trace_read(long long* host, int count) {
+    return (int)cudaMemcpyFromSymbol(host, kvb_trace_buf, sizeof(long long) * count);
+}
+#else
+#define TRACE(i)
+#endif

@@ -93,38 +93,73 @@ template <> struct Vec4<bf16> {
     }
 };
 
+// Four elements per thread and step.  A thread keeps its (up to) KEEP chunks of the row in registers between
+// the sum of squares and the scaling, and reads the norm's weight - which no kernel writes - before it waits
+// for the kernel that makes `delta`; rows longer than KEEP * 4 * blockDim are read a second time.
 template <typename T>
 __global__ void add_rmsnorm_vec_kernel(float* __restrict__ h, const T* __restrict__ delta, const float* __restrict__ w,
                                        T* __restrict__ out, const int* __restrict__ rows, int H, float eps) {
-    pdl_wait();
-    pdl_launch_dependents();
+    constexpr int KEEP = 2;
     __shared__ float scratch[33];
     const int o = blockIdx.x;
-    const int r = rows ? rows[o] : o;
+    const int r = rows ? rows[o] : o;                      // written by the host's copy at the start of the step
+    float4 ww[KEEP];
+#pragma unroll
+    for (int k = 0; k < KEEP; ++k) {
+        const int i = (threadIdx.x + k * blockDim.x) * 4;
+        ww[k] = i < H ? *reinterpret_cast<const float4*>(w + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    pdl_wait();
+    pdl_launch_dependents();
     float* hr = h + (size_t)r * H;
     const T* dr = delta ? delta + (size_t)r * H : nullptr;
+    float4 kept[KEEP];
     float ss = 0.f;
-    for (int i = threadIdx.x * 4; i < H; i += blockDim.x * 4) {
+    auto fetch = [&](int i) {
         float4 v = *reinterpret_cast<const float4*>(hr + i);
         if (dr) {
             const float4 d = Vec4<T>::load(dr + i);
             v.x += d.x; v.y += d.y; v.z += d.z; v.w += d.w;
-            if (!rows) *reinterpret_cast<float4*>(hr + i) = v;
         }
-        // Summed in the order of the scalar kernel's thread: element by element.
+        return v;
+    };
+    auto square = [&](const float4& v) {                   // summed element by element, as the scalar kernel's thread does
         ss += v.x * v.x; ss += v.y * v.y; ss += v.z * v.z; ss += v.w * v.w;
+    };
+#pragma unroll
+    for (int k = 0; k < KEEP; ++k) {
+        const int i = (threadIdx.x + k * blockDim.x) * 4;
+        if (i < H) {
+            kept[k] = fetch(i);
+            if (dr && !rows) *reinterpret_cast<float4*>(hr + i) = kept[k];
+            square(kept[k]);
+        }
+    }
+    for (int i = (threadIdx.x + KEEP * blockDim.x) * 4; i < H; i += blockDim.x * 4) {
+        const float4 v = fetch(i);
+        if (dr && !rows) *reinterpret_cast<float4*>(hr + i) = v;
+        square(v);
     }
     const float total = block_sum(ss, scratch);
     const float inv = 1.f / sqrtf(total / (float)H + eps);
     T* orow = out + (size_t)o * H;
-    for (int i = threadIdx.x * 4; i < H; i += blockDim.x * 4) {
+#pragma unroll
+    for (int k = 0; k < KEEP; ++k) {
+        const int i = (threadIdx.x + k * blockDim.x) * 4;
+        if (i < H) {
+            const float4 v = kept[k], g = ww[k];
+            Vec4<T>::store(orow + i, make_float4(v.x * inv * g.x, v.y * inv * g.y, v.z * inv * g.z, v.w * inv * g.w));
+        }
+    }
+    for (int i = (threadIdx.x + KEEP * blockDim.x) * 4; i < H; i += blockDim.x * 4) {
+        // Beyond what the registers keep: read again (after an in-place update the row already holds the sum).
         float4 v = *reinterpret_cast<const float4*>(hr + i);
         if (rows && dr) {
             const float4 d = Vec4<T>::load(dr + i);
             v.x += d.x; v.y += d.y; v.z += d.z; v.w += d.w;
         }
-        const float4 ww = *reinterpret_cast<const float4*>(w + i);
-        Vec4<T>::store(orow + i, make_float4(v.x * inv * ww.x, v.y * inv * ww.y, v.z * inv * ww.z, v.w * inv * ww.w));
+        const float4 g = *reinterpret_cast<const float4*>(w + i);
+        Vec4<T>::store(orow + i, make_float4(v.x * inv * g.x, v.y * inv * g.y, v.z * inv * g.z, v.w * inv * g.w));
     }
 }
 
@@ -133,12 +168,14 @@ KVB_API int kvb_add_rmsnorm(int dtype, float* h, const void* delta, const float*
     if (n_out <= 0) return KVB_OK;
     const int threads = H >= 2048 ? 512 : (H >= 512 ? 256 : 128);
     const bool vec = H % 4 == 0 && ((((uintptr_t)h | (uintptr_t)w | (uintptr_t)out | (uintptr_t)delta) & 15) == 0);
+    // One chunk of four per thread where the row allows it.
+    const int vec_threads = H / 4 >= 1024 ? 1024 : (H / 4 + 31) / 32 * 32;
     if (vec && dtype == KVB_F32) {
-        kvb_launch(add_rmsnorm_vec_kernel<float>, dim3(n_out), dim3(threads / 2), 0, stream, h, (const float*)delta, w, (float*)out, rows, H, eps);
+        kvb_launch(add_rmsnorm_vec_kernel<float>, dim3(n_out), dim3(vec_threads), 0, stream, h, (const float*)delta, w, (float*)out, rows, H, eps);
         return kvb_launch_status();
     }
     if (vec && dtype == KVB_BF16) {
-        kvb_launch(add_rmsnorm_vec_kernel<bf16>, dim3(n_out), dim3(threads / 2), 0, stream, h, (const bf16*)delta, w, (bf16*)out, rows, H, eps);
+        kvb_launch(add_rmsnorm_vec_kernel<bf16>, dim3(n_out), dim3(vec_threads), 0, stream, h, (const bf16*)delta, w, (bf16*)out, rows, H, eps);
         return kvb_launch_status();
     }
     if (dtype == KVB_F32)

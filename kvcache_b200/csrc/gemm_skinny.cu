@@ -23,6 +23,12 @@
 // (the reference's k_silu_mul, src/qwen_kernels.cu:102-105, without the round trip through memory).
 #include "common.cuh"
 
+#ifdef KVB_TRACE
+#define SKINNY_TRACE(i) if (N == KVB_TRACE_N) { TRACE(i) }     // debug builds: the product with this many outputs
+#else
+#define SKINNY_TRACE(i)
+#endif
+
 namespace skinny {
 
 __device__ __forceinline__ void mma_bf16(float* c, uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
@@ -39,18 +45,11 @@ __device__ __forceinline__ uint4 ld_stream(const void* p) {      // weights: rea
 
 constexpr int BLOCKS_WANTED = 148 * 2;
 
-// Weights that products after this one will stream (up to two ranges).  The blocks of this kernel ask for
-// them to be brought into L2 while they wait for their own input: the wait falls into the time of the kernel
-// before, which may be one that leaves the memory system idle.
-struct Upcoming {
-    const char* ptr[2];
-    long long bytes[2];
-};
-
 template <int RT, int NT, bool ACT, typename TOut>
 __global__ void __launch_bounds__(256) gemm_skinny_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w,
                                                           const float* __restrict__ bias, TOut* __restrict__ y, int M,
-                                                          int N, int K, int x_stride, int ksplit, Upcoming up) {
+                                                          int N, int K, int x_stride, int ksplit) {
+    SKINNY_TRACE(0)
     extern __shared__ __align__(16) float red[];          // [warps + 1][RT][NT][32 lanes][4]
     const int warps = blockDim.x >> 5, warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
     const int rank = blockIdx.x % ksplit;                  // the cluster spans x
@@ -72,21 +71,6 @@ __global__ void __launch_bounds__(256) gemm_skinny_kernel(const bf16* __restrict
             asm volatile("prefetch.global.L2 [%0];" ::"l"(p));
         }
     }
-#pragma unroll
-    for (int u = 0; u < 2; ++u) {
-        const long long lines = (up.bytes[u] + 127) / 128;
-        for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < lines; i += (long long)gridDim.x * blockDim.x)
-            asm volatile("prefetch.global.L2 [%0];" ::"l"(up.ptr[u] + i * 128));
-    }
-    pdl_wait();
-    pdl_launch_dependents();
-
-    float acc[RT][NT][4];
-#pragma unroll
-    for (int r = 0; r < RT; ++r)
-#pragma unroll
-        for (int j = 0; j < NT; ++j) acc[r][j][0] = acc[r][j][1] = acc[r][j][2] = acc[r][j][3] = 0.f;
-
     // Row pointers: W rows n0 + 16 r + g and + 8 (clamped; rows beyond N are never stored), x rows 8 j + g.
     const bf16* wrow[RT][2];
 #pragma unroll
@@ -94,19 +78,13 @@ __global__ void __launch_bounds__(256) gemm_skinny_kernel(const bf16* __restrict
         wrow[r][0] = w + (size_t)min(N - 1, n0 + 16 * r + g) * K + 8 * t;
         wrow[r][1] = w + (size_t)min(N - 1, n0 + 16 * r + g + 8) * K + 8 * t;
     }
-    const bf16* xrow[NT];
-    bool xok[NT];
+    // Two register buffers of U k-blocks each.  The weights of both are requested before the wait for the kernel
+    // that makes x (they do not depend on it); after it, the loads of the next U are issued before the products
+    // of the current U, so that a warp's share of K costs one trip to memory plus its streaming.
+    constexpr int U = (RT * NT >= 4) ? 1 : 2;
+    auto load_w = [&](uint4 (&a)[U][RT][2], int kb) {
 #pragma unroll
-    for (int j = 0; j < NT; ++j) {
-        xok[j] = 8 * j + g < M;
-        xrow[j] = x + (size_t)(xok[j] ? 8 * j + g : 0) * x_stride + 8 * t;
-    }
-
-    constexpr int UNROLL = (RT * NT >= 8) ? 2 : 4;
-    for (int kb = kb_begin; kb < kb_end; kb += UNROLL) {
-        uint4 a[UNROLL][RT][2], b[UNROLL][NT];
-#pragma unroll
-        for (int u = 0; u < UNROLL; ++u) {
+        for (int u = 0; u < U; ++u) {
             const bool live = kb + u < kb_end;
             const int k = (live ? kb + u : kb) * 32;
 #pragma unroll
@@ -114,6 +92,34 @@ __global__ void __launch_bounds__(256) gemm_skinny_kernel(const bf16* __restrict
                 a[u][r][0] = live ? ld_stream(wrow[r][0] + k) : make_uint4(0, 0, 0, 0);
                 a[u][r][1] = live ? ld_stream(wrow[r][1] + k) : make_uint4(0, 0, 0, 0);
             }
+        }
+    };
+    uint4 a0[U][RT][2], b0[U][NT], a1[U][RT][2], b1[U][NT];
+    if (kb_begin < kb_end) load_w(a0, kb_begin);
+    if (kb_begin + U < kb_end) load_w(a1, kb_begin + U);
+    SKINNY_TRACE(1)
+    pdl_wait();
+    pdl_launch_dependents();
+    SKINNY_TRACE(2)
+
+    float acc[RT][NT][4];
+#pragma unroll
+    for (int r = 0; r < RT; ++r)
+#pragma unroll
+        for (int j = 0; j < NT; ++j) acc[r][j][0] = acc[r][j][1] = acc[r][j][2] = acc[r][j][3] = 0.f;
+
+    const bf16* xrow[NT];
+    bool xok[NT];
+#pragma unroll
+    for (int j = 0; j < NT; ++j) {
+        xok[j] = 8 * j + g < M;
+        xrow[j] = x + (size_t)(xok[j] ? 8 * j + g : 0) * x_stride + 8 * t;
+    }
+    auto load_x = [&](uint4 (&b)[U][NT], int kb) {
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const bool live = kb + u < kb_end;
+            const int k = (live ? kb + u : kb) * 32;
 #pragma unroll
             for (int j = 0; j < NT; ++j) {
                 if (live && xok[j]) {
@@ -123,8 +129,10 @@ __global__ void __launch_bounds__(256) gemm_skinny_kernel(const bf16* __restrict
                 }
             }
         }
+    };
+    auto multiply = [&](const uint4 (&a)[U][RT][2], const uint4 (&b)[U][NT]) {
 #pragma unroll
-        for (int u = 0; u < UNROLL; ++u)
+        for (int u = 0; u < U; ++u)
 #pragma unroll
             for (int r = 0; r < RT; ++r)
 #pragma unroll
@@ -132,8 +140,21 @@ __global__ void __launch_bounds__(256) gemm_skinny_kernel(const bf16* __restrict
                     mma_bf16(acc[r][j], a[u][r][0].x, a[u][r][1].x, a[u][r][0].y, a[u][r][1].y, b[u][j].x, b[u][j].y);
                     mma_bf16(acc[r][j], a[u][r][0].z, a[u][r][1].z, a[u][r][0].w, a[u][r][1].w, b[u][j].z, b[u][j].w);
                 }
+    };
+    int kb = kb_begin;
+    if (kb < kb_end) load_x(b0, kb);
+    if (kb + U < kb_end) load_x(b1, kb + U);
+    while (kb < kb_end) {
+        multiply(a0, b0);
+        kb += U;
+        if (kb >= kb_end) break;
+        if (kb + U < kb_end) { load_w(a0, kb + U); load_x(b0, kb + U); }
+        multiply(a1, b1);
+        kb += U;
+        if (kb + U < kb_end) { load_w(a1, kb + U); load_x(b1, kb + U); }
     }
 
+    SKINNY_TRACE(3)
     // Partial sums of the warps meet in shared memory and are added in warp order.
     float4* mine = reinterpret_cast<float4*>(red) + ((size_t)warp * RT * NT) * 32 + lane;
 #pragma unroll
@@ -191,19 +212,50 @@ __global__ void __launch_bounds__(256) gemm_skinny_kernel(const bf16* __restrict
             }
         }
     }
+    SKINNY_TRACE(4)
     if (ksplit > 1) cluster_sync_all();                    // no block leaves while another still reads its sums
+    SKINNY_TRACE(5)
+}
+
+// How K is split over a cluster and over a block's warps.  It depends on the weight's shape alone - not on the
+// number of rows of x, nor on how many row tiles a block takes - so that a row's sums are added in the same
+// order whatever the batch.
+struct Split {
+    int ksplit, warps;
+};
+static inline Split choose_split(int N, int kblocks) {
+    const int blocks = (N + 15) / 16;
+    // K over a cluster while that still leaves blocks wanted and every warp of a block something to do.
+    Split s{1, 4};
+    while (s.ksplit < 8 && blocks * s.ksplit * 2 <= BLOCKS_WANTED && kblocks / (s.ksplit * 2) >= 4) s.ksplit *= 2;
+    // Warps split a block's share of K: enough of them to keep loads in flight, not so many that a warp has nothing to do.
+    s.warps = kblocks / s.ksplit >= 32 ? 8 : 4;
+    return s;
+}
+
+// Whether all blocks of this shape are on the SMs at once (no second wave that costs a block's whole latency again).
+template <int RT, int NT, bool ACT, typename TOut>
+bool resident(int N, int K) {
+    const int blocks = (N + 16 * RT - 1) / (16 * RT);
+    const Split s = choose_split(N, K / 32);
+    static int per_sm[2] = {-1, -1}, sm_count = 0;             // per block size: 4 or 8 warps
+    int& cached = per_sm[s.warps == 8];
+    if (cached < 0) {
+        int device = 0;
+        cudaGetDevice(&device);
+        cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, device);
+        const size_t smem = (size_t)(s.warps + 1) * RT * NT * 32 * 4 * sizeof(float);
+        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&cached, gemm_skinny_kernel<RT, NT, ACT, TOut>, s.warps * 32, smem) != cudaSuccess)
+            cached = 1;
+    }
+    return (long long)blocks * s.ksplit <= (long long)cached * sm_count;
 }
 
 template <int RT, int NT, bool ACT, typename TOut>
-int launch(const bf16* x, const bf16* w, const float* bias, TOut* y, int M, int N, int K, int x_stride, const Upcoming& up,
-           cudaStream_t stream) {
-    const int kblocks = K / 32;
+int launch(const bf16* x, const bf16* w, const float* bias, TOut* y, int M, int N, int K, int x_stride, cudaStream_t stream) {
     const int blocks = (N + 16 * RT - 1) / (16 * RT);
-    // K over a cluster while that still leaves blocks wanted and every warp of a block something to do.
-    int ksplit = 1;
-    while (ksplit < 8 && blocks * ksplit * 2 <= BLOCKS_WANTED && kblocks / (ksplit * 2) >= 4) ksplit *= 2;
-    // Warps split a block's share of K: enough of them to keep loads in flight, not so many that a warp has nothing to do.
-    const int warps = kblocks / ksplit >= 32 ? 8 : 4;
+    const Split s = choose_split(N, K / 32);
+    const int ksplit = s.ksplit, warps = s.warps;
     const size_t smem = (size_t)(warps + 1) * RT * NT * 32 * 4 * sizeof(float);
     auto kernel = gemm_skinny_kernel<RT, NT, ACT, TOut>;
     if (smem > 48 * 1024) {
@@ -212,25 +264,30 @@ int launch(const bf16* x, const bf16* w, const float* bias, TOut* y, int M, int 
     }
     if (ksplit > 1)
         kvb_launch_cluster(kernel, dim3(blocks * ksplit), dim3(warps * 32), (unsigned)ksplit, smem, stream, x, w, bias, y, M, N,
-                           K, x_stride, ksplit, up);
+                           K, x_stride, ksplit);
     else
-        kvb_launch(kernel, dim3(blocks), dim3(warps * 32), smem, stream, x, w, bias, y, M, N, K, x_stride, ksplit, up);
+        kvb_launch(kernel, dim3(blocks), dim3(warps * 32), smem, stream, x, w, bias, y, M, N, K, x_stride, ksplit);
     return kvb_launch_status();
 }
 
+// Rows of W per block: the fewest 16-row tiles with which every block is on the SMs at once; a weight too
+// large for that (an output head over the vocabulary) is streamed in waves of two-tile blocks.
+template <int NT, bool ACT, typename TOut>
+int dispatch_rows(const bf16* x, const bf16* w, const float* bias, TOut* y, int M, int N, int K, int x_stride, cudaStream_t stream) {
+    if (resident<1, NT, ACT, TOut>(N, K)) return launch<1, NT, ACT, TOut>(x, w, bias, y, M, N, K, x_stride, stream);
+    if (resident<2, NT, ACT, TOut>(N, K)) return launch<2, NT, ACT, TOut>(x, w, bias, y, M, N, K, x_stride, stream);
+    if constexpr (NT <= 2) {
+        if (resident<4, NT, ACT, TOut>(N, K)) return launch<4, NT, ACT, TOut>(x, w, bias, y, M, N, K, x_stride, stream);
+    }
+    return launch<2, NT, ACT, TOut>(x, w, bias, y, M, N, K, x_stride, stream);
+}
+
 template <bool ACT, typename TOut>
-int dispatch(const bf16* x, const bf16* w, const float* bias, TOut* y, int M, int N, int K, int x_stride, const Upcoming& up,
-             cudaStream_t stream) {
-    // Rows of W per block: two 16-row tiles when there are plenty of blocks anyway.
-    const bool wide = N >= 16 * 2 * 148 * 4;
-    if (M <= 8) return wide ? launch<2, 1, ACT, TOut>(x, w, bias, y, M, N, K, x_stride, up, stream)
-                            : launch<1, 1, ACT, TOut>(x, w, bias, y, M, N, K, x_stride, up, stream);
-    if (M <= 16) return wide ? launch<2, 2, ACT, TOut>(x, w, bias, y, M, N, K, x_stride, up, stream)
-                             : launch<1, 2, ACT, TOut>(x, w, bias, y, M, N, K, x_stride, up, stream);
-    if (M <= 32) return wide ? launch<2, 4, ACT, TOut>(x, w, bias, y, M, N, K, x_stride, up, stream)
-                             : launch<1, 4, ACT, TOut>(x, w, bias, y, M, N, K, x_stride, up, stream);
-    return wide ? launch<2, 8, ACT, TOut>(x, w, bias, y, M, N, K, x_stride, up, stream)
-                : launch<1, 8, ACT, TOut>(x, w, bias, y, M, N, K, x_stride, up, stream);
+int dispatch(const bf16* x, const bf16* w, const float* bias, TOut* y, int M, int N, int K, int x_stride, cudaStream_t stream) {
+    if (M <= 8) return dispatch_rows<1, ACT, TOut>(x, w, bias, y, M, N, K, x_stride, stream);
+    if (M <= 16) return dispatch_rows<2, ACT, TOut>(x, w, bias, y, M, N, K, x_stride, stream);
+    if (M <= 32) return dispatch_rows<4, ACT, TOut>(x, w, bias, y, M, N, K, x_stride, stream);
+    return dispatch_rows<8, ACT, TOut>(x, w, bias, y, M, N, K, x_stride, stream);
 }
 
 }  // namespace skinny
@@ -238,10 +295,8 @@ int dispatch(const bf16* x, const bf16* w, const float* bias, TOut* y, int M, in
 // x: [M, K] bfloat16; w: [N, K] bfloat16; bias: float32 [N] or null; y: [M, N] bfloat16 (out_dtype 1) or float32
 // (out_dtype 0) - or, with swiglu = 1, [M, N / 2] from interleaved gate/up rows (N a multiple of 16, no bias).
 // Refuses M > 64, K not a multiple of 32, misaligned operands.
-// `up0`/`up1` (+ bytes; may be null/0): weights that later products will stream, to be brought into L2 meanwhile.
 KVB_API int kvb_gemm_skinny(int out_dtype, int act, const void* x, const void* w, const float* bias, void* y, int M,
-                            int N, int K, const void* up0, long long up0_bytes, const void* up1, long long up1_bytes,
-                            cudaStream_t stream) {
+                            int N, int K, cudaStream_t stream) {
     if (M <= 0 || N <= 0) return KVB_OK;
     if (M > 64 || K <= 0 || K % 32 != 0) return KVB_ERR_SHAPE;
     if (((uintptr_t)x | (uintptr_t)w) & 15) return KVB_ERR_ALIGN;
@@ -249,14 +304,11 @@ KVB_API int kvb_gemm_skinny(int out_dtype, int act, const void* x, const void* w
     const bf16* wb = (const bf16*)w;
     if (act && (N % 16 != 0 || bias != nullptr)) return KVB_ERR_SHAPE;
     const int x_stride = K;
-    skinny::Upcoming up;
-    up.ptr[0] = (const char*)up0; up.bytes[0] = up0 ? up0_bytes : 0;
-    up.ptr[1] = (const char*)up1; up.bytes[1] = up1 ? up1_bytes : 0;
     if (out_dtype == KVB_BF16)
-        return act ? skinny::dispatch<true, bf16>(xb, wb, bias, (bf16*)y, M, N, K, x_stride, up, stream)
-                   : skinny::dispatch<false, bf16>(xb, wb, bias, (bf16*)y, M, N, K, x_stride, up, stream);
+        return act ? skinny::dispatch<true, bf16>(xb, wb, bias, (bf16*)y, M, N, K, x_stride, stream)
+                   : skinny::dispatch<false, bf16>(xb, wb, bias, (bf16*)y, M, N, K, x_stride, stream);
     if (out_dtype == KVB_F32)
-        return act ? skinny::dispatch<true, float>(xb, wb, bias, (float*)y, M, N, K, x_stride, up, stream)
-                   : skinny::dispatch<false, float>(xb, wb, bias, (float*)y, M, N, K, x_stride, up, stream);
+        return act ? skinny::dispatch<true, float>(xb, wb, bias, (float*)y, M, N, K, x_stride, stream)
+                   : skinny::dispatch<false, float>(xb, wb, bias, (float*)y, M, N, K, x_stride, stream);
     return KVB_ERR_DTYPE;
 }

@@ -70,6 +70,29 @@ __global__ void qkv_rope_append_kernel(const T* __restrict__ qkv, const float* _
 
 // bfloat16, head sizes and rotation halves that are multiples of 8: one thread moves 8 elements
 // (16 bytes) of a head; for a rotated chunk it also reads the partner chunk rot/2 further (or back).
+// What does not depend on the product before this kernel - the row's position and page, and the first
+// chunk's angles and biases - is read before the wait for that product.
+struct ChunkTables {
+    float cs[8], sn[8], b_self[8], b_partner[8];
+};
+
+__device__ __forceinline__ void chunk_tables(ChunkTables& t, int c, int chunks_per_head, int D, int Hq, int Hkv, int rot_half,
+                                             const float* cr, const float* sr, const float* bias) {
+    const int head = c / chunks_per_head, d = (c - head * chunks_per_head) * 8;
+    const int idx = head * D + d;
+    const bool rotated = head < Hq + Hkv && d < 2 * rot_half;
+    const bool low = d < rot_half;
+    const int t0 = low ? d : d - rot_half;
+    const int pidx = low ? idx + rot_half : idx - rot_half;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+        t.b_self[k] = bias ? bias[idx + k] : 0.f;
+        t.b_partner[k] = (bias && rotated) ? bias[pidx + k] : 0.f;
+        t.cs[k] = rotated ? cr[t0 + k] : 1.f;
+        t.sn[k] = rotated ? sr[t0 + k] : 0.f;
+    }
+}
+
 __global__ void qkv_rope_append_vec8_kernel(const bf16* __restrict__ qkv, const float* __restrict__ bias,
                                             const float* __restrict__ cos_t, const float* __restrict__ sin_t,
                                             int rot_half, int table_len, const int* __restrict__ positions,
@@ -77,12 +100,9 @@ __global__ void qkv_rope_append_vec8_kernel(const bf16* __restrict__ qkv, const 
                                             int table_stride, bf16* __restrict__ k_pages, bf16* __restrict__ v_pages,
                                             bf16* __restrict__ q_out, int Hq, int Hkv, int D, int page_size, int write_kv,
                                             int* __restrict__ err) {
-    pdl_wait();
-    pdl_launch_dependents();
     const int r = blockIdx.x;
     const int width = (Hq + 2 * Hkv) * D;
     const int pos = positions[r];
-    const bf16* src = qkv + (size_t)r * width;
     const int rot = 2 * rot_half;
     size_t page_base = 0;
     bool page_ok = true;
@@ -100,7 +120,14 @@ __global__ void qkv_rope_append_vec8_kernel(const bf16* __restrict__ qkv, const 
     const float* cr = cos_t + (size_t)(pos_ok ? pos : 0) * rot_half;
     const float* sr = sin_t + (size_t)(pos_ok ? pos : 0) * rot_half;
     const int chunks_per_head = D >> 3;
-    for (int c = threadIdx.x; c < (width >> 3); c += blockDim.x) {
+    const int chunks = width >> 3;
+    ChunkTables tab;
+    if ((int)threadIdx.x < chunks) chunk_tables(tab, threadIdx.x, chunks_per_head, D, Hq, Hkv, rot_half, cr, sr, bias);
+    pdl_wait();
+    pdl_launch_dependents();
+    const bf16* src = qkv + (size_t)r * width;
+    for (int c = threadIdx.x; c < chunks; c += blockDim.x) {
+        if (c != (int)threadIdx.x) chunk_tables(tab, c, chunks_per_head, D, Hq, Hkv, rot_half, cr, sr, bias);
         const int head = c / chunks_per_head, d = (c - head * chunks_per_head) * 8;
         const int idx = head * D + d;
         float x[8];
@@ -114,13 +141,12 @@ __global__ void qkv_rope_append_vec8_kernel(const bf16* __restrict__ qkv, const 
             }
             if (bias) {
 #pragma unroll
-                for (int k = 0; k < 8; ++k) x[k] += bias[idx + k];
+                for (int k = 0; k < 8; ++k) x[k] += tab.b_self[k];
             }
         }
         const bool is_v = head >= Hq + Hkv;
         if (!is_v && d < rot) {
             const bool low = d < rot_half;
-            const int t0 = low ? d : d - rot_half;
             const int pidx = low ? idx + rot_half : idx - rot_half;
             const uint4 raw = *reinterpret_cast<const uint4*>(src + pidx);
             const uint32_t wv[4] = {raw.x, raw.y, raw.z, raw.w};
@@ -128,8 +154,8 @@ __global__ void qkv_rope_append_vec8_kernel(const bf16* __restrict__ qkv, const 
             for (int k = 0; k < 4; ++k) {
                 const float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&wv[k]));
                 float xp0 = f.x, xp1 = f.y;
-                if (bias) { xp0 += bias[pidx + 2 * k]; xp1 += bias[pidx + 2 * k + 1]; }
-                const float c0 = cr[t0 + 2 * k], s0 = sr[t0 + 2 * k], c1 = cr[t0 + 2 * k + 1], s1 = sr[t0 + 2 * k + 1];
+                if (bias) { xp0 += tab.b_partner[2 * k]; xp1 += tab.b_partner[2 * k + 1]; }
+                const float c0 = tab.cs[2 * k], s0 = tab.sn[2 * k], c1 = tab.cs[2 * k + 1], s1 = tab.sn[2 * k + 1];
                 x[2 * k] = low ? (x[2 * k] * c0 - xp0 * s0) : (x[2 * k] * c0 + xp0 * s0);
                 x[2 * k + 1] = low ? (x[2 * k + 1] * c1 - xp1 * s1) : (x[2 * k + 1] * c1 + xp1 * s1);
             }
@@ -161,7 +187,8 @@ KVB_API int kvb_qkv_rope_append(int dtype, const void* qkv, const float* bias, c
     const int threads = width >= 1024 ? 256 : 128;
     const uintptr_t addresses = (uintptr_t)qkv | (uintptr_t)k_pages | (uintptr_t)v_pages | (uintptr_t)q_out;
     if (dtype == KVB_BF16 && D % 8 == 0 && rot_half % 8 == 0 && (addresses & 15) == 0) {
-        kvb_launch(qkv_rope_append_vec8_kernel, dim3(T), dim3(width >= 2048 ? 256 : 128), 0, stream, 
+        // One 16-byte chunk per thread where the row allows it.
+        kvb_launch(qkv_rope_append_vec8_kernel, dim3(T), dim3(width / 8 >= 1024 ? 1024 : (width / 8 + 31) / 32 * 32), 0, stream,
             (const bf16*)qkv, bias, cos_t, sin_t, rot_half, table_len, positions, row_segment, block_table, table_stride,
             (bf16*)k_pages, (bf16*)v_pages, (bf16*)q_out, Hq, Hkv, D, page_size, write_kv, err);
         return kvb_launch_status();

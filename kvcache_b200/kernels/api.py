@@ -16,7 +16,7 @@ import torch
 from ..parts.base import PagedKVView, StepBatch
 from . import build
 
-_c_int, _c_float, _c_void_p, _c_longlong = ctypes.c_int, ctypes.c_float, ctypes.c_void_p, ctypes.c_longlong
+_c_int, _c_float, _c_void_p = ctypes.c_int, ctypes.c_float, ctypes.c_void_p
 
 DEVICE_ERRORS = {8: "a wait inside a kernel ran out (a pipeline stalled); the step's results are not valid",
                  1: "a token id outside the vocabulary",
@@ -96,8 +96,7 @@ _SIGNATURES = {
         "kvb_gemm_simt": [_c_int, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_void_p],
     },
     "gemm_skinny": {
-        "kvb_gemm_skinny": [_c_int, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_void_p,
-                            _c_longlong, _c_void_p, _c_longlong, _c_void_p],
+        "kvb_gemm_skinny": [_c_int, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_void_p],
     },
     "gemm_tcgen05": {
         "kvb_gemm_tcgen05": [_c_int, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_void_p, _c_void_p],
@@ -219,27 +218,15 @@ class CudaKernels(KernelSet):
         _check(self._elementwise.kvb_silu_mul(_dtype_code(out.dtype), _ptr(gate_up), _ptr(out), T, I,
                                               1 if interleaved else 0, self._stream()), "silu_mul")
 
-    @staticmethod
-    def _upcoming_args(upcoming) -> tuple:
-        """(pointer, bytes) of the first two tensors of `upcoming` for the small-M product's prefetch."""
-        args = []
-        for t in list(upcoming or ())[:2]:
-            args += [_ptr(t), t.numel() * t.element_size()]
-        while len(args) < 4:
-            args += [_ptr(None), 0]
-        return tuple(args)
-
-    def gate_up_act(self, x: torch.Tensor, w_gate_up: torch.Tensor, out: torch.Tensor, workspace, interleaved: bool,
-                    upcoming: Optional[Sequence[torch.Tensor]] = None) -> None:
+    def gate_up_act(self, x: torch.Tensor, w_gate_up: torch.Tensor, out: torch.Tensor, workspace, interleaved: bool) -> None:
         """out[M, I] = silu(x Wg^T) * (x Wu^T); `w_gate_up` [2 I, K] holds gate and up rows one after the
-        other, or interleaved in eights (see csrc/gemm_skinny.cu).  `upcoming`: as in `linear`."""
+        other, or interleaved in eights (see csrc/gemm_skinny.cu)."""
         M, K = x.shape
         I = out.shape[1]
         if interleaved and self._skinny(x.dtype, M, K):
             self.launches += 1
             _check(self._gemm_skinny.kvb_gemm_skinny(_dtype_code(out.dtype), 1, _ptr(x), _ptr(w_gate_up), _ptr(None),
-                                                     _ptr(out), M, 2 * I, K, *self._upcoming_args(upcoming),
-                                                     self._stream()), "gate_up_act (skinny)")
+                                                     _ptr(out), M, 2 * I, K, self._stream()), "gate_up_act (skinny)")
             return
         if interleaved and self._tcgen05(x, w_gate_up, out, fused=True):
             self.launches += 1
@@ -263,10 +250,8 @@ class CudaKernels(KernelSet):
             return fused and -(-x.shape[0] // 256) * -(-w.shape[0] // 256) >= self.sm_count
         return self.bf16_gemm == "tcgen05"
 
-    def linear(self, x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bias: Optional[torch.Tensor] = None,
-               upcoming: Optional[Sequence[torch.Tensor]] = None) -> None:
-        """out = x . w^T + bias.  `upcoming`: weights that products after this one will read (a hint: the
-        small-M kernel asks for the first two to be brought into L2 while it waits for x; others ignore it)."""
+    def linear(self, x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bias: Optional[torch.Tensor] = None) -> None:
+        """out = x . w^T + bias."""
         M = x.shape[0]
         N, K = w.shape
         if x.shape[1] != K or tuple(out.shape) != (M, N):
@@ -274,8 +259,7 @@ class CudaKernels(KernelSet):
         self.launches += 1
         if self._skinny(x.dtype, M, K):
             _check(self._gemm_skinny.kvb_gemm_skinny(_dtype_code(out.dtype), 0, _ptr(x), _ptr(w), _ptr(bias),
-                                                     _ptr(out), M, N, K, *self._upcoming_args(upcoming), self._stream()),
-                   "linear (skinny)")
+                                                     _ptr(out), M, N, K, self._stream()), "linear (skinny)")
             return
         if self._tcgen05(x, w, out):
             _check(self._gemm_tc.kvb_gemm_tcgen05(_dtype_code(out.dtype), 0, _ptr(x), _ptr(w), _ptr(bias), _ptr(out), M, N, K,
