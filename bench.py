@@ -161,7 +161,7 @@ def time_prefill(folder, tokens, layers_total, repeats=3):
     from kvcache_b200.engine.core import EngineCore
     from kvcache_b200.engine.runner import StepEntry
     options = EngineOptions(dtype="bfloat16", page_size=16, max_cached_tokens=tokens + 16, max_running=1,
-                            max_tokens_per_step=tokens, max_model_len=tokens + 16, use_graphs=False)
+                            max_tokens_per_step=tokens, max_model_len=tokens + 16, use_graphs=True)
     core = EngineCore(folder, options)
     ids = torch.randint(0, core.model.vocab_size, (tokens,), generator=torch.Generator().manual_seed(3)).tolist()
     times = []

@@ -27,7 +27,7 @@ class EngineOptions:
     chunk_size: int = 512                  # largest portion of one prompt in a step
     max_model_len: Optional[int] = None    # None: the configuration's max_position_embeddings
     admission: str = "reserve"             # "reserve" (worst case held back) or "optimistic" (preempts)
-    use_graphs: bool = True                # CUDA graphs for pure-decode steps
+    use_graphs: bool = True                # CUDA graphs for steps of decoded tokens and of one portion of one prompt
     seed: int = 0
     device: str = "cuda:0"
 

@@ -15,7 +15,11 @@
 //   O_t = P V   tcgen05.mma, M 128 x N head size x K 64 keys; P is the A operand (K-major), the value tile as
 //               TMA left it - rows of keys, head size contiguous - is the B operand in MN-major form.
 //               The thread adds its row of O_t (tcgen05.ld) into float32 registers, o = o * 2^(m_old - m_new) + O_t.
-// Warp 4 holds the control thread: it issues the TMA loads (two key/value stages) and both MMAs.
+// S, P and O_t exist twice: while the threads run the softmax of tile i + 1, the tensor core multiplies P V of
+// tile i and Q K^T of tile i + 2, and a thread adds O_t of tile i only after it has handed over P of tile i + 1 -
+// so the softmax threads never wait for an MMA they have just asked for.
+// Warp 4's first thread issues both MMAs; warp 5 runs ahead of it with the TMA loads (a ring of three key
+// stages and one of three value stages, each refilled as soon as the MMA that read it has finished).
 // Every mbarrier wait is bounded; on a timeout the error word is set and the block winds down.
 #include "tc_common.cuh"
 
@@ -33,10 +37,10 @@ constexpr int HALVES = D / 64;                       // 64-wide (128-byte) colum
 constexpr int SUB_BYTES = BQ * 128;                  // a [128 rows x 64 columns] bfloat16 sub-tile (Q, P), swizzled
 constexpr int KV_SUB_BYTES = BKEYS * 128;            // a [64 keys x 64 columns] sub-tile (K, V)
 constexpr int Q_BYTES = HALVES * SUB_BYTES, KV_BYTES = HALVES * KV_SUB_BYTES, P_BYTES = SUB_BYTES;
-constexpr int STAGES = 2;
-constexpr int SMEM_BYTES = Q_BYTES + P_BYTES + 2 * STAGES * KV_BYTES + 1024;
-constexpr int TMEM_COLS = D == 64 ? 128 : 256;       // S: 64 columns, O_t: D columns
-constexpr int THREADS = 160;
+constexpr int STAGES = 3;                            // of keys, and of values: two rings, each filled on its own
+constexpr int SMEM_BYTES = Q_BYTES + 2 * P_BYTES + 2 * STAGES * KV_BYTES + 1024;
+constexpr int TMEM_COLS = D == 64 ? 256 : 512;       // S: 2 x 64 columns, O_t: 2 x D columns
+constexpr int THREADS = 192;                         // warps 0-3: softmax rows; warp 4: MMA issue; warp 5: TMA loads
 constexpr float NEG_INF = -INFINITY;
 
 // Shared-memory descriptor of an MN-major operand with 128-byte swizzle: rows of 64 elements (128 bytes) along
@@ -61,7 +65,10 @@ __device__ __forceinline__ float ex2(float x) {
 struct Params {
     bf16* out;                 // [T, Hq * D]
     const int* block_table;    // [segments, table_stride]
-    const int* tiles;          // [n_tiles, 2]: segment, first row of the tile within the segment
+    const int* units;          // [n_units, 8]: segment, first row of the tile, unit, units of the tile, tile id, first unit of the tile
+    float* part_o;             // [units, Hq, D / 4, 128, 4]  unnormalised outputs of units that share a tile
+    float* part_ml;            // [units, Hq, 128, 2]  their running maximum and sum
+    int* tickets;              // [tiles, Hq], zero between launches
     const int* seg_q_start;
     const int* seg_q_len;
     const int* seg_kv_len;
@@ -71,38 +78,47 @@ struct Params {
 };
 
 struct Shared {
-    uint64_t q_full, kv_full[STAGES], kv_empty[STAGES], s_full, p_ready, o_full;
+    uint64_t q_full, k_full[STAGES], k_empty[STAGES], v_full[STAGES], v_empty[STAGES], s_full[2], p_ready[2], o_full[2];
     uint32_t tmem_base;
     int failed;
 };
 
-__global__ void __launch_bounds__(THREADS, D == 64 ? 3 : 1)
+__global__ void __launch_bounds__(THREADS, D == 64 ? 2 : 1)
 attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                     const __grid_constant__ CUtensorMap map_v, const __grid_constant__ Params p) {
     extern __shared__ unsigned char smem_raw[];
     unsigned char* base = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     unsigned char* q_s = base;
     unsigned char* p_s = q_s + Q_BYTES;
-    unsigned char* kv_s = p_s + P_BYTES;                      // stage s: K at kv_s + 2 s KV_BYTES, V right after it
+    unsigned char* k_s = p_s + 2 * P_BYTES;                   // key stage s at k_s + s KV_BYTES
+    unsigned char* v_s = k_s + STAGES * KV_BYTES;             // value stage s at v_s + s KV_BYTES
     __shared__ Shared sh;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int tile = blockIdx.x, h = blockIdx.y;
-    const int seg = p.tiles[2 * tile], row0 = p.tiles[2 * tile + 1];
+    __shared__ int ticket_s;
+    const int h = blockIdx.x, unit = blockIdx.y;              // all heads of a unit start together
+    const int* u = p.units + 8 * unit;
+    const int seg = u[0], row0 = u[1], split = u[2], nsplit = u[3], tile_id = u[4], unit0 = u[5];
     const int hk = h / (p.Hq / p.Hkv);
     const int q_start = p.seg_q_start[seg], q_len = p.seg_q_len[seg], kv_len = p.seg_kv_len[seg];
     const int first_pos = kv_len - q_len;
     const int tile_rows = min(BQ, q_len - row0);
     const int pos_first = first_pos + row0, pos_last = pos_first + tile_rows - 1;
     const int key_lo = (p.window > 0 && pos_first - p.window + 1 > 0) ? pos_first - p.window + 1 : 0;
-    const int kt_begin = key_lo / BKEYS, kt_end = pos_last / BKEYS + 1;
+    // The tile's key tiles are shared out among its units; a window may leave some units without any.
+    const int tile_begin = key_lo / BKEYS, tile_end = pos_last / BKEYS + 1;
+    const int per_split = (tile_end - tile_begin + nsplit - 1) / nsplit;
+    const int n_valid = (tile_end - tile_begin + per_split - 1) / per_split;
+    if (split >= n_valid) return;
+    const int kt_begin = tile_begin + split * per_split, kt_end = min(tile_end, kt_begin + per_split);
     const int n = kt_end - kt_begin;
 
     if (tid == 0) {
         mbar_init(&sh.q_full, 1);
-        for (int s = 0; s < STAGES; ++s) { mbar_init(&sh.kv_full[s], 1); mbar_init(&sh.kv_empty[s], 1); }
-        mbar_init(&sh.s_full, 1);
-        mbar_init(&sh.p_ready, 128);
-        mbar_init(&sh.o_full, 1);
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(&sh.k_full[s], 1); mbar_init(&sh.k_empty[s], 1);
+            mbar_init(&sh.v_full[s], 1); mbar_init(&sh.v_empty[s], 1);
+        }
+        for (int b = 0; b < 2; ++b) { mbar_init(&sh.s_full[b], 1); mbar_init(&sh.p_ready[b], 128); mbar_init(&sh.o_full[b], 1); }
         sh.failed = 0;
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
@@ -114,24 +130,41 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-    const uint32_t tmem_s = sh.tmem_base, tmem_o = sh.tmem_base + BKEYS;
+    const uint32_t tmem_s = sh.tmem_base, tmem_o = sh.tmem_base + 2 * BKEYS;   // S of tile i at + (i % 2) * 64, O_t at + (i % 2) * D
 
-    if (warp == 4) {
-        // ---- control warp: TMA loads and MMA issue by lane 0; all lanes zero-fill page slots that no TMA fills ----
+    if (warp == 5) {
+        // ---- loader warp: lane 0 issues the TMA copies; all lanes look pages up and zero-fill slots that no copy fills ----
         const int* table = p.block_table + (size_t)seg * p.table_stride;
         const int pages_per_tile = BKEYS >> p.page_shift;
         bool ok = true;
-
-        auto load_kv = [&](int i) {                            // key/value tile kt_begin + i into stage i % STAGES
-            const int s = i % STAGES;
-            unsigned char* k_dst = kv_s + (size_t)(2 * s) * KV_BYTES;
-            unsigned char* v_dst = k_dst + KV_BYTES;
-            const int key0 = (kt_begin + i) * BKEYS;
-            // Lane pg looks up the tile's page pg (one coalesced read of the block table for the whole tile).
-            int my_page = -1;
+        // Key (or value) tile kt_begin + i into stage i % STAGES of its ring, once the MMA that read the stage's
+        // last tenant has finished.
+        // Lane pg looks up page pg of tile kt_begin + i (one coalesced read of the block table for the whole tile);
+        // -1 where the tile has no page that the rows can see.
+#ifdef KVB_TRACE
+        long long l_wk = 0, l_wv = 0, l_start = clock64();
+#endif
+        auto lookup = [&](int i) -> int {
+            int page = -1;
             if (lane < pages_per_tile) {
-                const int first_key = key0 + lane * p.page_size;
-                if (first_key <= pos_last && first_key + p.page_size > key_lo) my_page = table[first_key >> p.page_shift];
+                const int first_key = (kt_begin + i) * BKEYS + lane * p.page_size;
+                if (first_key <= pos_last && first_key + p.page_size > key_lo) page = table[first_key >> p.page_shift];
+            }
+            return page;
+        };
+        auto load_tile = [&](int i, int my_page, const CUtensorMap* map, unsigned char* ring, uint64_t* full, uint64_t* empty) {
+            const int s = i % STAGES;
+            unsigned char* dst = ring + (size_t)s * KV_BYTES;
+            if (i >= STAGES) {
+#ifdef KVB_TRACE
+                const long long w0 = clock64();
+#endif
+                if (lane == 0) ok = mbar_wait(&empty[s], ((i - STAGES) / STAGES) & 1);
+#ifdef KVB_TRACE
+                if (empty == sh.k_empty) l_wk += clock64() - w0; else l_wv += clock64() - w0;
+#endif
+                ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+                if (!ok) return;
             }
             const unsigned held = __ballot_sync(0xffffffffu, my_page >= 0);
             const int present = __popc(held);
@@ -142,27 +175,22 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
                 for (int pg = 0; pg < pages_per_tile; ++pg) {
                     if ((held >> pg) & 1u) continue;
                     for (int hb = 0; hb < HALVES; ++hb)
-                        for (int off = lane * 16; off < bytes; off += 32 * 16) {
-                            *reinterpret_cast<uint4*>(k_dst + hb * KV_SUB_BYTES + pg * bytes + off) = make_uint4(0, 0, 0, 0);
-                            *reinterpret_cast<uint4*>(v_dst + hb * KV_SUB_BYTES + pg * bytes + off) = make_uint4(0, 0, 0, 0);
-                        }
+                        for (int off = lane * 16; off < bytes; off += 32 * 16)
+                            *reinterpret_cast<uint4*>(dst + hb * KV_SUB_BYTES + pg * bytes + off) = make_uint4(0, 0, 0, 0);
                 }
                 asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
                 __syncwarp();
             }
-            if (lane == 0) mbar_expect_tx(&sh.kv_full[s], (uint32_t)present * 2 * HALVES * p.page_size * 128);
-            for (int pg = 0; pg < pages_per_tile; ++pg) {
-                const int page = __shfl_sync(0xffffffffu, my_page, pg);
-                if (page < 0 || lane != 0) continue;
-                const int row = (page * p.Hkv + hk) * p.page_size;     // row of the pool seen as [pages * heads * page, D]
-                for (int hb = 0; hb < HALVES; ++hb) {
-                    tma_load_2d(k_dst + hb * KV_SUB_BYTES + pg * p.page_size * 128, &map_k, hb * 64, row, &sh.kv_full[s]);
-                    tma_load_2d(v_dst + hb * KV_SUB_BYTES + pg * p.page_size * 128, &map_v, hb * 64, row, &sh.kv_full[s]);
-                }
+            if (lane == 0) mbar_expect_tx(&full[s], (uint32_t)present * HALVES * p.page_size * 128);
+            __syncwarp();
+            if (my_page >= 0) {                                         // lane pg copies page pg: the copies go out side by side
+                const int row = (my_page * p.Hkv + hk) * p.page_size;   // row of the pool seen as [pages * heads * page, D]
+#pragma unroll
+                for (int hb = 0; hb < HALVES; ++hb)
+                    tma_load_2d(dst + hb * KV_SUB_BYTES + lane * p.page_size * 128, map, hb * 64, row, &full[s]);
             }
             __syncwarp();
         };
-
         if (lane == 0) {
             asm volatile("prefetch.tensormap [%0];\n" ::"l"(&map_q) : "memory");
             asm volatile("prefetch.tensormap [%0];\n" ::"l"(&map_k) : "memory");
@@ -170,53 +198,90 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
             mbar_expect_tx(&sh.q_full, Q_BYTES);
             for (int hb = 0; hb < HALVES; ++hb) tma_load_2d(q_s + hb * SUB_BYTES, &map_q, h * D + hb * 64, q_start + row0, &sh.q_full);
         }
-        load_kv(0);
-        constexpr uint32_t idesc_s = instr_desc(BQ, BKEYS);
-        constexpr uint32_t idesc_o = instr_desc(BQ, D) | (1u << 16);            // B (values) is MN-major
-        for (int i = 0; i < n && ok; ++i) {
-            const int s = i % STAGES;
-            if (lane == 0) {
-                if (i == 0) ok = mbar_wait(&sh.q_full, 0);
-                ok = ok && mbar_wait(&sh.kv_full[s], (i / STAGES) & 1);
-                if (ok) {
-                    asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-                    const uint32_t k_addr = smem_u32(kv_s + (size_t)(2 * s) * KV_BYTES);
-#pragma unroll
-                    for (int k = 0; k < D / 16; ++k) {             // 16 of the head size a step; 64 a sub-tile
-                        umma(tmem_s, smem_desc(smem_u32(q_s) + (k / 4) * SUB_BYTES) + 2 * (k % 4),
-                             smem_desc(k_addr + (k / 4) * KV_SUB_BYTES) + 2 * (k % 4), idesc_s, k != 0 ? 1u : 0u);
-                    }
-                    umma_commit(&sh.s_full);
-                }
-            }
-            ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
-            if (!ok) break;
-            // The next tile's loads overlap this tile's softmax; its stage is free once the second MMA of the tile
-            // before this one has finished.
-            if (i + 1 < n) {
-                if (i + 1 >= STAGES) {
-                    if (lane == 0) ok = mbar_wait(&sh.kv_empty[(i + 1) % STAGES], (((i + 1) / STAGES) - 1) & 1);
-                    ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
-                    if (!ok) break;
-                }
-                load_kv(i + 1);
-            }
-            if (lane == 0) {
-                ok = mbar_wait(&sh.p_ready, i & 1);
-                if (ok) {
-                    asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-                    const uint32_t v_addr = smem_u32(kv_s + (size_t)(2 * s + 1) * KV_BYTES);
-#pragma unroll
-                    for (int k = 0; k < BKEYS / 16; ++k)           // 16 keys a step: 32 bytes along P's rows, 2048 bytes down V
-                        umma(tmem_o, smem_desc(smem_u32(p_s)) + 2 * k, smem_desc_mn(v_addr + k * 2048, KV_SUB_BYTES), idesc_o,
-                             k != 0 ? 1u : 0u);
-                    umma_commit(&sh.kv_empty[s]);
-                    umma_commit(&sh.o_full);
-                }
-            }
-            ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+        // Keys are wanted two tiles before the values of the same tile: K_j goes before V_{j-1}.  The pages of a
+        // tile are looked up one tile ahead, so that the table's latency is not in the way of the copies.
+        int pages_next = lookup(0), pages_prev = -1;
+        for (int j = 0; j <= n && ok; ++j) {
+            const int pages_cur = pages_next;
+            if (j + 1 < n) pages_next = lookup(j + 1);
+            if (j < n) load_tile(j, pages_cur, &map_k, k_s, sh.k_full, sh.k_empty);
+            if (ok && j >= 1) load_tile(j - 1, pages_prev, &map_v, v_s, sh.v_full, sh.v_empty);
+            pages_prev = pages_cur;
         }
         if (!ok && lane == 0) { atomicOr(p.err, KVB_DEV_TIMEOUT); sh.failed = 1; }
+#ifdef KVB_TRACE
+        if (lane == 0) {
+            const int cta = blockIdx.y * gridDim.x + blockIdx.x;
+            if (cta < 4096) {
+                long long* t = kvb_trace_buf + (4096 + cta) * 8;
+                t[4] = l_wk; t[5] = l_wv; t[6] = clock64() - l_start;
+            }
+        }
+#endif
+    } else if (warp == 4) {
+        // ---- MMA warp: its first thread issues every MMA ----
+        bool ok = true;
+        constexpr uint32_t idesc_s = instr_desc(BQ, BKEYS);
+        constexpr uint32_t idesc_o = instr_desc(BQ, D) | (1u << 16);            // B (values) is MN-major
+        if (lane == 0) {
+#ifdef KVB_TRACE
+            long long m_wp = 0, m_wv = 0, m_wk = 0, m_t, m_start = clock64();
+#define MCLK(acc) { const long long now_ = clock64(); acc += now_ - m_t; m_t = now_; }
+#define MCLK0() m_t = clock64();
+#else
+#define MCLK(acc)
+#define MCLK0()
+#endif
+            // S_{i % 2} = Q K_i^T
+            auto mma_scores = [&](int i) -> bool {
+                const int s = i % STAGES;
+                if (i == 0 && !mbar_wait(&sh.q_full, 0)) return false;
+                MCLK0()
+                if (!mbar_wait(&sh.k_full[s], (i / STAGES) & 1)) return false;
+                MCLK(m_wk)
+                asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+                const uint32_t k_addr = smem_u32(k_s + (size_t)s * KV_BYTES);
+#pragma unroll
+                for (int k = 0; k < D / 16; ++k)                   // 16 of the head size a step; 64 a sub-tile
+                    umma(tmem_s + (i & 1) * BKEYS, smem_desc(smem_u32(q_s) + (k / 4) * SUB_BYTES) + 2 * (k % 4),
+                         smem_desc(k_addr + (k / 4) * KV_SUB_BYTES) + 2 * (k % 4), idesc_s, k != 0 ? 1u : 0u);
+                umma_commit(&sh.k_empty[s]);
+                umma_commit(&sh.s_full[i & 1]);
+                return true;
+            };
+            ok = mma_scores(0);
+            if (ok && n > 1) ok = mma_scores(1);
+            for (int i = 0; i < n && ok; ++i) {
+                const int s = i % STAGES;
+                MCLK0()
+                ok = mbar_wait(&sh.p_ready[i & 1], (i >> 1) & 1);  // P_i is in shared memory; S_{i % 2} and O_{i % 2} are free
+                MCLK(m_wp)
+                ok = ok && mbar_wait(&sh.v_full[s], (i / STAGES) & 1);
+                MCLK(m_wv)
+                if (!ok) break;
+                asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+                const uint32_t v_addr = smem_u32(v_s + (size_t)s * KV_BYTES);
+                const uint32_t p_addr = smem_u32(p_s + (i & 1) * P_BYTES);
+#pragma unroll
+                for (int k = 0; k < BKEYS / 16; ++k)               // 16 keys a step: 32 bytes along P's rows, 2048 bytes down V
+                    umma(tmem_o + (i & 1) * D, smem_desc(p_addr) + 2 * k, smem_desc_mn(v_addr + k * 2048, KV_SUB_BYTES), idesc_o,
+                         k != 0 ? 1u : 0u);
+                umma_commit(&sh.v_empty[s]);
+                umma_commit(&sh.o_full[i & 1]);
+                if (i + 2 < n) ok = mma_scores(i + 2);
+            }
+            if (!ok) { atomicOr(p.err, KVB_DEV_TIMEOUT); sh.failed = 1; }
+#ifdef KVB_TRACE
+            {
+                const int cta = blockIdx.y * gridDim.x + blockIdx.x;
+                if (cta < 4096) {
+                    long long* t = kvb_trace_buf + (4096 + cta) * 8;
+                    t[0] = m_wp; t[1] = m_wv; t[2] = m_wk; t[3] = clock64() - m_start;
+                }
+            }
+#endif
+        }
+        __syncwarp();
     } else {
         // ---- softmax warps: thread = row ----
         const int row = tid;                                    // 0..127 within the tile
@@ -227,29 +292,70 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
         for (int d = 0; d < D; ++d) o[d] = 0.f;
         float m = NEG_INF, l = 0.f;
         bool ok = true;
+        auto store_row = [&](const float* vals, float factor) {
+            bf16* orow = p.out + ((size_t)(q_start + row0 + row) * p.Hq + h) * D;
+#pragma unroll
+            for (int d = 0; d < D; d += 8) {
+                uint32_t w4[4];
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    __nv_bfloat162 v = __floats2bfloat162_rn(vals[d + 2 * e] * factor, vals[d + 2 * e + 1] * factor);
+                    w4[e] = *reinterpret_cast<uint32_t*>(&v);
+                }
+                *reinterpret_cast<uint4*>(orow + d) = make_uint4(w4[0], w4[1], w4[2], w4[3]);
+            }
+        };
+        float corr_prev = 1.f;                                  // the rescaling that belongs to the O_t not yet added
+#ifdef KVB_TRACE
+        long long c_wait_s = 0, c_soft = 0, c_wait_o = 0, c_add = 0, c_t, c_start = clock64();
+#define TCLK(acc) { const long long now_ = clock64(); acc += now_ - c_t; c_t = now_; }
+#define TCLK0() c_t = clock64();
+#else
+#define TCLK(acc)
+#define TCLK0()
+#endif
+        // o = o * corr + O_t of tile i (from tensor memory).
+        auto add_output = [&](int i, float corr) -> bool {
+            TCLK0()
+            if (!mbar_wait(&sh.o_full[i & 1], (i >> 1) & 1)) return false;
+            TCLK(c_wait_o)
+            asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+#pragma unroll
+            for (int c = 0; c < D / 32; ++c) {
+                uint32_t r[32];
+                tmem_ld32(tmem_o + (i & 1) * D + lane_base + c * 32, r);
+#pragma unroll
+                for (int e = 0; e < 32; ++e) o[c * 32 + e] = fmaf(o[c * 32 + e], corr, __uint_as_float(r[e]));
+            }
+            asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+            TCLK(c_add)
+            return true;
+        };
         for (int i = 0; i < n; ++i) {
-            ok = mbar_wait(&sh.s_full, i & 1);
+            TCLK0()
+            ok = mbar_wait(&sh.s_full[i & 1], (i >> 1) & 1);
             if (!ok) break;
+            TCLK(c_wait_s)
             asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
             const int key0 = (kt_begin + i) * BKEYS;
             // Whether every row of this warp sees every key of the tile (then no element needs its mask).
             const bool open = pos >= 0 && key0 + BKEYS - 1 <= pos && (p.window <= 0 || key0 > pos - p.window);
             const bool warp_open = __all_sync(0xffffffffu, open);
-            // First pass over the row of S: its maximum.
+            // The row of S, read once.
+            uint32_t sv[BKEYS];
+            tmem_ld32(tmem_s + (i & 1) * BKEYS + lane_base, sv);
+            tmem_ld32(tmem_s + (i & 1) * BKEYS + lane_base + 32, sv + 32);
             float mx = NEG_INF;
+            if (warp_open) {
 #pragma unroll
-            for (int c = 0; c < BKEYS / 32; ++c) {
-                uint32_t r[32];
-                tmem_ld32(tmem_s + lane_base + c * 32, r);
-                if (warp_open) {
+                for (int e = 0; e < BKEYS; ++e) mx = fmaxf(mx, __uint_as_float(sv[e]));
+            } else {
 #pragma unroll
-                    for (int e = 0; e < 32; ++e) mx = fmaxf(mx, __uint_as_float(r[e]));
-                } else {
-#pragma unroll
-                    for (int e = 0; e < 32; ++e) {
-                        const int j = key0 + c * 32 + e;
-                        if (j <= pos && (p.window <= 0 || j > pos - p.window)) mx = fmaxf(mx, __uint_as_float(r[e]));
-                    }
+                for (int e = 0; e < BKEYS; ++e) {
+                    const int j = key0 + e;
+                    const bool seen = j <= pos && (p.window <= 0 || j > pos - p.window);
+                    if (!seen) sv[e] = __float_as_uint(NEG_INF);
+                    mx = fmaxf(mx, __uint_as_float(sv[e]));
                 }
             }
             const float m_new = fmaxf(m, mx * p.scale_log2);
@@ -257,71 +363,93 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
             const float corr = ex2(m - base_m);
             m = m_new;
             l *= corr;
-            // Second pass: P = 2^(s * scale - m) as bfloat16 into shared memory, row `row`, 16-byte chunk c' of the
-            // row at chunk position c' ^ (row % 8).
+            // P = 2^(s * scale - m) as bfloat16 into shared memory, row `row`, 16-byte chunk c of the row at chunk
+            // position c ^ (row % 8).  A masked score is -inf and gives 0.
+            unsigned char* dst = p_s + (i & 1) * P_BYTES + row * 128;
 #pragma unroll
-            for (int c = 0; c < BKEYS / 32; ++c) {
-                uint32_t r[32];
-                tmem_ld32(tmem_s + lane_base + c * 32, r);
-                uint32_t packed[16];
-                if (warp_open) {
+            for (int c = 0; c < BKEYS / 8; ++c) {
+                uint32_t packed[4];
 #pragma unroll
-                    for (int e = 0; e < 32; e += 2) {
-                        const float p0 = ex2(fmaf(__uint_as_float(r[e]), p.scale_log2, -base_m));
-                        const float p1 = ex2(fmaf(__uint_as_float(r[e + 1]), p.scale_log2, -base_m));
-                        l += p0 + p1;
-                        __nv_bfloat162 v = __floats2bfloat162_rn(p0, p1);
-                        packed[e / 2] = *reinterpret_cast<uint32_t*>(&v);
-                    }
-                } else {
-#pragma unroll
-                    for (int e = 0; e < 32; e += 2) {
-                        const int j = key0 + c * 32 + e;
-                        const bool seen0 = j <= pos && (p.window <= 0 || j > pos - p.window);
-                        const bool seen1 = j + 1 <= pos && (p.window <= 0 || j + 1 > pos - p.window);
-                        const float p0 = seen0 ? ex2(fmaf(__uint_as_float(r[e]), p.scale_log2, -base_m)) : 0.f;
-                        const float p1 = seen1 ? ex2(fmaf(__uint_as_float(r[e + 1]), p.scale_log2, -base_m)) : 0.f;
-                        l += p0 + p1;
-                        __nv_bfloat162 v = __floats2bfloat162_rn(p0, p1);
-                        packed[e / 2] = *reinterpret_cast<uint32_t*>(&v);
-                    }
+                for (int e = 0; e < 4; ++e) {
+                    const float p0 = ex2(fmaf(__uint_as_float(sv[8 * c + 2 * e]), p.scale_log2, -base_m));
+                    const float p1 = ex2(fmaf(__uint_as_float(sv[8 * c + 2 * e + 1]), p.scale_log2, -base_m));
+                    l += p0 + p1;
+                    __nv_bfloat162 v = __floats2bfloat162_rn(p0, p1);
+                    packed[e] = *reinterpret_cast<uint32_t*>(&v);
                 }
-                unsigned char* dst = p_s + row * 128;
-#pragma unroll
-                for (int q4 = 0; q4 < 4; ++q4) {
-                    const int chunk = c * 4 + q4;               // 16-byte chunk within the row of 64 keys
-                    *reinterpret_cast<uint4*>(dst + ((chunk ^ (row & 7)) << 4)) =
-                        make_uint4(packed[4 * q4], packed[4 * q4 + 1], packed[4 * q4 + 2], packed[4 * q4 + 3]);
-                }
+                *reinterpret_cast<uint4*>(dst + ((c ^ (row & 7)) << 4)) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
             }
             asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
             asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");    // P was written by ordinary stores; the MMA reads it
-            mbar_arrive(&sh.p_ready);
-            ok = mbar_wait(&sh.o_full, i & 1);
-            if (!ok) break;
-            asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-#pragma unroll
-            for (int c = 0; c < D / 32; ++c) {
-                uint32_t r[32];
-                tmem_ld32(tmem_o + lane_base + c * 32, r);
-#pragma unroll
-                for (int e = 0; e < 32; ++e) o[c * 32 + e] = fmaf(o[c * 32 + e], corr, __uint_as_float(r[e]));
+            mbar_arrive(&sh.p_ready[i & 1]);
+            TCLK(c_soft)
+            // While the tensor core multiplies P_i V_i, add the O_t of the tile before.
+            if (i >= 1) {
+                ok = add_output(i - 1, corr_prev);
+                if (!ok) break;
             }
-            asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+            corr_prev = corr;
         }
+        if (ok) ok = add_output(n - 1, corr_prev);
+#ifdef KVB_TRACE
+        if (tid == 0) {
+            const int cta = blockIdx.y * gridDim.x + blockIdx.x;
+            if (cta < 8192) {
+                long long* t = kvb_trace_buf + cta * 8;
+                t[0] = n; t[1] = c_wait_s; t[2] = c_soft; t[3] = c_wait_o; t[4] = c_add; t[5] = clock64() - c_start;
+                unsigned smid; asm volatile("mov.u32 %0, %%smid;" : "=r"(smid)); t[6] = smid;
+                t[7] = trace_now();
+            }
+        }
+#endif
         if (!ok && lane == 0) { atomicOr(p.err, KVB_DEV_TIMEOUT); sh.failed = 1; }
-        if (ok && row < tile_rows) {
-            const float inv = l > 0.f ? 1.f / l : 0.f;
-            bf16* orow = p.out + ((size_t)(q_start + row0 + row) * p.Hq + h) * D;
+        if (ok && n_valid == 1 && row < tile_rows) store_row(o, l > 0.f ? 1.f / l : 0.f);
+        if (ok && n_valid > 1) {
+            // Leave this unit's (m, l, o) for the block that merges the tile.
+            // Layout [D / 4][128 rows] of float4, so that a warp's rows make one contiguous store.
+            float4* po = reinterpret_cast<float4*>(p.part_o + ((size_t)(unit0 + split) * p.Hq + h) * BQ * D) + row;
 #pragma unroll
-            for (int d = 0; d < D; d += 8) {
-                uint32_t w4[4];
+            for (int d = 0; d < D; d += 4) po[(d / 4) * BQ] = make_float4(o[d], o[d + 1], o[d + 2], o[d + 3]);
+            *reinterpret_cast<float2*>(p.part_ml + (((size_t)(unit0 + split) * p.Hq + h) * BQ + row) * 2) = make_float2(m, l);
+            __threadfence();
+        }
+        if (n_valid > 1) {
+            asm volatile("bar.sync 1, 128;\n" ::: "memory");            // the four softmax warps
+            if (tid == 0) ticket_s = atomicAdd(p.tickets + tile_id * p.Hq + h, 1);
+            asm volatile("bar.sync 1, 128;\n" ::: "memory");
+            if (ticket_s == n_valid - 1) {
+                // The last unit of the tile to finish merges all of them, in unit order:
+                // weight_s = 2^(m_s - M) / sum_s 2^(m_s - M) l_s, out = sum_s weight_s o_s.
+                __threadfence();
+                if (tid == 0) p.tickets[tile_id * p.Hq + h] = 0;
+                if (ok && row < tile_rows) {
+                    // Every unit, this one too, is read back from scratch: one order of additions whichever unit is last.
+                    const float* ml0 = p.part_ml + (((size_t)unit0 * p.Hq + h) * BQ + row) * 2;
+                    const float4* po0 = reinterpret_cast<const float4*>(p.part_o + ((size_t)unit0 * p.Hq + h) * BQ * D) + row;
+                    const size_t ml_step = (size_t)p.Hq * BQ * 2, po_step = (size_t)p.Hq * BQ * D / 4;
+                    float M = NEG_INF;
+                    for (int s2 = 0; s2 < n_valid; ++s2) M = fmaxf(M, __ldcg(ml0 + s2 * ml_step));
+                    const float base_m = M == NEG_INF ? 0.f : M;
+                    float L = 0.f;
+                    for (int s2 = 0; s2 < n_valid; ++s2) {
+                        const float2 ml = __ldcg(reinterpret_cast<const float2*>(ml0 + s2 * ml_step));
+                        L += ex2(ml.x - base_m) * ml.y;
+                    }
+                    const float inv = L > 0.f ? 1.f / L : 0.f;
+                    float acc[D];
 #pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    __nv_bfloat162 v = __floats2bfloat162_rn(o[d + 2 * e] * inv, o[d + 2 * e + 1] * inv);
-                    w4[e] = *reinterpret_cast<uint32_t*>(&v);
+                    for (int d = 0; d < D; ++d) acc[d] = 0.f;
+                    for (int s2 = 0; s2 < n_valid; ++s2) {
+                        const float ws = ex2(__ldcg(ml0 + s2 * ml_step) - base_m) * inv;
+                        const float4* po = po0 + s2 * po_step;
+#pragma unroll
+                        for (int d = 0; d < D; d += 4) {
+                            const float4 v = __ldcg(po + (d / 4) * BQ);
+                            acc[d] += ws * v.x; acc[d + 1] += ws * v.y; acc[d + 2] += ws * v.z; acc[d + 3] += ws * v.w;
+                        }
+                    }
+                    store_row(acc, 1.f);
                 }
-                *reinterpret_cast<uint4*>(orow + d) = make_uint4(w4[0], w4[1], w4[2], w4[3]);
             }
         }
     }
@@ -330,7 +458,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     __syncthreads();
     if (sh.failed && tid == 0) {      // give copies that may still be in flight a bounded chance to land
         mbar_wait(&sh.q_full, 0);
-        for (int s = 0; s < STAGES; ++s) mbar_wait(&sh.kv_full[s], 0);
+        for (int s = 0; s < STAGES; ++s) { mbar_wait(&sh.k_full[s], 0); mbar_wait(&sh.v_full[s], 0); }
     }
     __syncthreads();
     if (warp == 4) {
@@ -357,14 +485,21 @@ static int make_map(CUtensorMap* map, const void* base, long long rows, int cols
 
 KVB_API int kvb_attention_tc_head_dim() { return atc::D; }
 
-// q, out: [T, Hq * D] bfloat16; k_pages, v_pages: [num_pages, Hkv, page_size, D]; tiles: int32 [n_tiles, 2]
-// (segment, first row of a tile of 128 rows).  page_size a power of two, 8..64.
+KVB_API long long kvb_attention_tc_scratch_floats(int n_units, int Hq) {
+    return (long long)n_units * Hq * atc::BQ * (atc::D + 2);
+}
+
+// q, out: [T, Hq * D] bfloat16; k_pages, v_pages: [num_pages, Hkv, page_size, D]; units: int32 [n_units, 8]
+// (segment, first row of a tile of 128 rows, unit, units of the tile, tile id, first unit of the tile, 0, 0);
+// scratch: kvb_attention_tc_scratch_floats floats; tickets: one int per (tile, head), zero before the first
+// launch (the kernel leaves them zero).  page_size a power of two, 8..64.
 KVB_API int kvb_attention_tc(const void* q, void* out, const void* k_pages, const void* v_pages, int num_pages,
-                             const int* block_table, int table_stride, const int* tiles, int n_tiles,
-                             const int* seg_q_start, const int* seg_q_len, const int* seg_kv_len, int T, int Hq, int Hkv,
-                             int page_size, int window, float scale, int* err, cudaStream_t stream) {
+                             const int* block_table, int table_stride, const int* units, int n_units, float* scratch,
+                             int* tickets, const int* seg_q_start, const int* seg_q_len, const int* seg_kv_len, int T,
+                             int Hq, int Hkv, int page_size, int window, float scale, int* err, cudaStream_t stream) {
     using namespace atc;
-    if (n_tiles <= 0) return KVB_OK;
+    const int n_tiles = n_units;
+    if (n_units <= 0) return KVB_OK;
     if (Hkv < 1 || Hq % Hkv != 0 || Hq > 65535) return KVB_ERR_SHAPE;
     if (page_size < 8 || page_size > atc::BKEYS || (page_size & (page_size - 1)) != 0) return KVB_ERR_SHAPE;
     if (((uintptr_t)q | (uintptr_t)out | (uintptr_t)k_pages | (uintptr_t)v_pages) & 15) return KVB_ERR_ALIGN;
@@ -377,7 +512,8 @@ KVB_API int kvb_attention_tc(const void* q, void* out, const void* k_pages, cons
     rc = make_map(&mv, v_pages, pool_rows, D, D, page_size);
     if (rc != KVB_OK) return rc;
     Params p;
-    p.out = (bf16*)out; p.block_table = block_table; p.tiles = tiles; p.seg_q_start = seg_q_start; p.seg_q_len = seg_q_len;
+    p.out = (bf16*)out; p.block_table = block_table; p.units = units; p.seg_q_start = seg_q_start; p.seg_q_len = seg_q_len;
+    p.part_o = scratch; p.part_ml = scratch + (size_t)n_units * Hq * BQ * D; p.tickets = tickets;
     p.seg_kv_len = seg_kv_len; p.table_stride = table_stride; p.Hq = Hq; p.Hkv = Hkv; p.page_size = page_size;
     p.page_shift = 0;
     while ((1 << p.page_shift) < page_size) ++p.page_shift;
@@ -390,7 +526,7 @@ KVB_API int kvb_attention_tc(const void* q, void* out, const void* k_pages, cons
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
-    dim3 grid(n_tiles, Hq);
+    dim3 grid(Hq, n_tiles);
     attention_tc_kernel<<<grid, THREADS, SMEM_BYTES, stream>>>(mq, mk, mv, p);
     return kvb_launch_status();
 }

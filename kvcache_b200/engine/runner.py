@@ -50,20 +50,26 @@ PREFILL_MAX_UNITS = 16          # most units one tile may be cut into (csrc/atte
 PREFILL_UNITS_WANTED = 256      # about this many units beyond one per tile, however long the prompts
 
 
-def plan_prefill_units(segments):
+TC_TILE_ROWS = 128              # query rows of a tile of the tensor-memory attention kernel
+TC_MIN_KEY_TILES = 16           # a unit of that kernel has at least this many key tiles, unless its tile has fewer
+
+
+def plan_prefill_units(segments, tile_rows: int = PREFILL_TILE_ROWS, min_key_tiles: int = 4):
     """The work list of prefill attention.  `segments`: (segment index, tokens cached before the step, tokens
-    it brings) for every segment of more than one token.  A tile is 64 consecutive rows of a segment; a tile
-    whose rows see many keys is cut into units of about equal numbers of key tiles, so that the blocks of the
-    grid - one per (unit, head) - all have about the same work although causal tiles do not.
+    it brings) for every segment of more than one token.  A tile is `tile_rows` consecutive rows of a segment;
+    a tile whose rows see many keys is cut into units of about equal numbers of key tiles, so that the blocks
+    of the grid - one per (unit, head) - all have about the same work although causal tiles do not.  Tiles
+    with the most keys come first.
     Returns (int32 array [units, 8]: segment, first row, unit, units of the tile, tile id, first unit of the
     tile, 0, 0; number of tiles)."""
     tiles = []
     for seg, start, count in segments:
-        for row0 in range(0, count, PREFILL_TILE_ROWS):
-            rows = min(PREFILL_TILE_ROWS, count - row0)
+        for row0 in range(0, count, tile_rows):
+            rows = min(tile_rows, count - row0)
             tiles.append((seg, row0, (start + row0 + rows - 1) // PREFILL_KEY_TILE + 1))
+    tiles.sort(key=lambda t: -t[2])
     total = sum(k for _, _, k in tiles)
-    per_unit = max(4, -(-total // PREFILL_UNITS_WANTED))
+    per_unit = max(min_key_tiles, -(-total // PREFILL_UNITS_WANTED))
     units = []
     for tile_id, (seg, row0, key_tiles) in enumerate(tiles):
         nsplit = max(1, min(PREFILL_MAX_UNITS, -(-key_tiles // per_unit)))
@@ -79,13 +85,13 @@ class StepLayout:
     SECTIONS = (("token_ids", "T", 1), ("positions", "T", 1), ("row_segment", "T", 1), ("seg_q_start", "S", 1),
                 ("seg_q_len", "S", 1), ("seg_kv_len", "S", 1), ("seg_slot", "S", 1), ("wanted_rows", "R", 1),
                 ("sample_temperature", "R", 1), ("sample_counter", "R", 1), ("sample_seed", "R", 2),
-                ("decode_items", "S", 1), ("prefill_tiles", "UNITS", 8), ("token_src", "T", 1), ("tc_tiles", "TILES128", 2))
+                ("decode_items", "S", 1), ("prefill_tiles", "UNITS", 8), ("token_src", "T", 1), ("tc_units", "TC_UNITS", 8))
 
     def __init__(self, T: int, S: int, R: int, table_width: int, num_groups: int):
         self.T, self.S, self.R = T, S, R
         self.table_width, self.num_groups = table_width, num_groups
         sizes = {"T": T, "S": S, "R": R, "UNITS": 2 * (T // PREFILL_TILE_ROWS + S) + PREFILL_UNITS_WANTED,
-                 "TILES128": T // 128 + S}
+                 "TC_UNITS": 2 * (T // TC_TILE_ROWS + S) + PREFILL_UNITS_WANTED}
         offset = 0
         self.offsets = {}
         for name, dim, words in self.SECTIONS:
@@ -215,7 +221,7 @@ class ModelRunner:
         for g in range(len(self.cache.groups)):
             layout.table(host, g)[:] = self.cache.table_rows(g, slots)
         if T == S:
-            n_items, n_units, n_tiles, n_tc = S, 0, 0, 0
+            n_items, n_units, n_tiles, n_tc, n_tc_tiles = S, 0, 0, 0, 0
             layout.view(host, "decode_items")[:] = row_segment
         else:
             single = counts_np == 1
@@ -226,12 +232,12 @@ class ModelRunner:
             n_units = len(units)
             if n_units:
                 layout.view(host, "prefill_tiles")[:8 * n_units] = units.reshape(-1)
-            # The same segments as tiles of 128 rows, longest first, for the tensor-memory kernel.
-            tc = [(int(i), r) for i in np.nonzero(~single)[0] for r in range(0, counts[i], 128)]
-            tc.sort(key=lambda t: -(starts[t[0]] + t[1]))
+            # The same segments as tiles of 128 rows for the tensor-memory kernel.
+            tc, n_tc_tiles = plan_prefill_units([(int(i), starts[i], counts[i]) for i in np.nonzero(~single)[0]],
+                                                TC_TILE_ROWS, TC_MIN_KEY_TILES)
             n_tc = len(tc)
             if n_tc:
-                layout.view(host, "tc_tiles")[:2 * n_tc] = np.asarray(tc, dtype=np.int32).reshape(-1)
+                layout.view(host, "tc_units")[:8 * n_tc] = tc.reshape(-1)
 
         dev = self._meta_device
         dev[:layout.total].copy_(staging[:layout.total], non_blocking=True)
@@ -249,7 +255,7 @@ class ModelRunner:
             token_src=layout.view(dev, "token_src"), last_tokens=self.last_tokens,
             decode_items=layout.view(dev, "decode_items")[:n_items], num_decode_items=n_items,
             prefill_tiles=layout.view(dev, "prefill_tiles")[:8 * n_units].view(-1, 8), num_prefill_units=n_units,
-            num_prefill_tiles=n_tiles, tc_tiles=layout.view(dev, "tc_tiles")[:2 * n_tc].view(-1, 2), num_tc_tiles=n_tc,
+            num_prefill_tiles=n_tiles, tc_units=layout.view(dev, "tc_units")[:8 * n_tc].view(-1, 8), num_tc_units=n_tc, num_tc_tiles=n_tc_tiles,
             max_q_len=int(counts_np.max()), max_kv_len=int((starts_np + counts_np).max()),
             host={"counts": counts_np, "starts": starts_np, "q_start": q_start, "slots": slots})
         view = self.cache.step_view([layout.table(dev, g) for g in range(len(self.cache.groups))])
@@ -275,17 +281,35 @@ class ModelRunner:
         tokens = self._sample(logits, layout, workspace) if sample and batch.num_wanted else None
         return logits, tokens
 
-    def _decode_graph(self, batch, view, layout) -> _DecodeGraph:
-        B = batch.num_tokens
-        found = self._graphs.get(B)
+    MAX_GRAPHS = 32
+
+    def _graph_key(self, batch, sample: bool):
+        """The key under which a step's launches can be replayed, or None.  Two kinds of steps have launches
+        that depend on nothing but a few counts: steps of single decoded tokens (the batch size), and steps
+        that bring one portion of one prompt (its length and the lengths of the attention work lists, which
+        grow with what the prompt has cached).  Everything else - the ids, positions, block tables, the work
+        lists themselves - is read from the step's metadata buffer, whose layout these counts fix."""
+        if not self.use_graphs:
+            return None
+        if sample and batch.num_tokens == batch.num_segments == batch.num_wanted:
+            return ("decode", batch.num_tokens)
+        if batch.num_segments == 1 and batch.num_tokens > 1:
+            return ("portion", batch.num_tokens, batch.num_wanted, sample, batch.num_prefill_units, batch.num_prefill_tiles,
+                    batch.num_tc_units, batch.num_tc_tiles)
+        return None
+
+    def _graph(self, key, batch, view, layout, sample: bool) -> _DecodeGraph:
+        found = self._graphs.get(key)
         if found is not None:
             return found
+        if len(self._graphs) >= self.MAX_GRAPHS:
+            self._graphs.pop(next(iter(self._graphs)))        # the oldest
         ws = self.graph_workspace
         moved = ws.moved
         # A first run outside the graph sizes the buffers.  It writes what the replay writes again - except that
         # sampling overwrites `last_tokens`, which this very step may read its ids from: put them back.
         saved = self.last_tokens.clone()
-        self._forward(batch, view, layout, ws, True)
+        self._forward(batch, view, layout, ws, sample)
         self.last_tokens.copy_(saved)
         if ws.moved != moved:
             self._graphs.clear()                              # a buffer moved: graphs that hold its old address go
@@ -295,11 +319,11 @@ class ModelRunner:
         ws.frozen = True
         try:
             with torch.cuda.graph(graph):
-                logits, tokens = self._forward(batch, view, layout, ws, True)
+                logits, tokens = self._forward(batch, view, layout, ws, sample)
         finally:
             ws.frozen = False
         found = _DecodeGraph(graph, logits, tokens, self.kernels.launches - before)
-        self._graphs[B] = found
+        self._graphs[key] = found
         return found
 
     def read_tokens_async(self, count: int):
@@ -325,9 +349,9 @@ class ModelRunner:
         (logits, int32 tokens sampled at those places, on the device: `last_tokens`).  The
         tensors are views of buffers the next step overwrites."""
         batch, view, layout = self.prepare(entries)
-        decode_only = sample and self.use_graphs and batch.num_tokens == batch.num_segments == batch.num_wanted
-        if decode_only:
-            found = self._decode_graph(batch, view, layout)
+        key = self._graph_key(batch, sample)
+        if key is not None:
+            found = self._graph(key, batch, view, layout, sample)
             found.graph.replay()
             self.kernels.launches += found.launches
             self.graph_replays += 1

@@ -115,7 +115,8 @@ _SIGNATURES = {
     "attention_tc": {
         "kvb_attention_tc_head_dim": [],
         "kvb_attention_tc": [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_int, _c_void_p, _c_int, _c_void_p,
-                             _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_void_p, _c_void_p],
+                             _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float,
+                             _c_void_p, _c_void_p],
     },
     "sampling": {
         "kvb_sample_parts": [_c_int],
@@ -306,17 +307,20 @@ class CudaKernels(KernelSet):
         if (self.flash_attention and q.dtype == torch.bfloat16 and D % 16 == 0 and D <= 128 and num_heads // Hkv <= 16
                 and workspace is not None and batch.decode_items is not None):
             lib = self._flash_library(D)
-            if (batch.num_tc_tiles and self.tc_attention_min_rows is not None and D in (64, 128)
+            if (batch.num_tc_units and self.tc_attention_min_rows is not None and D in (64, 128)
                     and 8 <= kv.page_size <= 64 and batch.max_q_len >= self.tc_attention_min_rows):
                 tc = self._attn_tc.get(D)
                 if tc is None:
                     tc = self._attn_tc[D] = _Library("attention_tc", f"d{D}", [f"-DKVB_HEAD_DIM={D}"])
+                units = batch.num_tc_units
+                scratch = workspace.buffer("attn.tc_scratch", (units * num_heads * 128 * (D + 2),), torch.float32)
+                tickets = workspace.zeros("attn.tc_tickets", (max(batch.num_tc_tiles, 1) * num_heads,), torch.int32)
                 self.launches += 1
                 _check(tc.kvb_attention_tc(
                     _ptr(q), _ptr(out), _ptr(kv.k_pages), _ptr(kv.v_pages), kv.k_pages.shape[0], _ptr(kv.block_table),
-                    kv.block_table.shape[1], _ptr(batch.tc_tiles), batch.num_tc_tiles, _ptr(batch.seg_q_start),
-                    _ptr(batch.seg_q_len), _ptr(batch.seg_kv_len), T, num_heads, Hkv, kv.page_size, spec.window or 0,
-                    float(scale), _ptr(self.error_word), self._stream()), "attention_tc")
+                    kv.block_table.shape[1], _ptr(batch.tc_units), units, _ptr(scratch), _ptr(tickets),
+                    _ptr(batch.seg_q_start), _ptr(batch.seg_q_len), _ptr(batch.seg_kv_len), T, num_heads, Hkv, kv.page_size,
+                    spec.window or 0, float(scale), _ptr(self.error_word), self._stream()), "attention_tc")
             elif batch.num_prefill_units:
                 units = batch.num_prefill_units
                 scratch = workspace.buffer("attn.prefill_scratch", (units * num_heads * 64 * (D + 2),), torch.float32)

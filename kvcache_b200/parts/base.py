@@ -82,7 +82,8 @@ class StepBatch:
     num_decode_items: int = 0
     num_prefill_units: int = 0
     num_prefill_tiles: int = 0
-    tc_tiles: Optional[torch.Tensor] = None        # int32 [num_tc_tiles, 2]: the same segments as 128-row tiles
+    tc_units: Optional[torch.Tensor] = None        # int32 [num_tc_units, 8]: the same segments as units of 128-row tiles
+    num_tc_units: int = 0
     num_tc_tiles: int = 0
     max_q_len: int = 1               # host copies, for launch shapes
     max_kv_len: int = 1

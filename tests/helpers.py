@@ -24,7 +24,8 @@ def random_tokens(vocab: int, n: int, seed: int) -> List[int]:
 
 
 def paged_scenario(segments, *, num_kv_heads: int, head_dim: int, page_size: int, dtype, device,
-                   window=None, seed: int = 0, extra_pages: int = 3, fill_history: bool = True):
+                   window=None, seed: int = 0, extra_pages: int = 3, fill_history: bool = True,
+                   tc_min_key_tiles: int = 16):
     """A step's metadata and a paged cache with shuffled pages, made by hand for kernel tests.
 
     `segments`: list of (tokens already cached, new tokens).  Returns (StepBatch, PagedKVView);
@@ -55,9 +56,9 @@ def paged_scenario(segments, *, num_kv_heads: int, head_dim: int, page_size: int
     items = [i for i, (_, n) in enumerate(segments) if n == 1]
     from kvcache_b200.engine.runner import plan_prefill_units
     units, n_tiles = plan_prefill_units([(i, s, n) for i, (s, n) in enumerate(segments) if n > 1])
-    tc = [(i, r) for i, (s, n) in enumerate(segments) if n > 1 for r in range(0, n, 128)]
+    tc, n_tc_tiles = plan_prefill_units([(i, s, n) for i, (s, n) in enumerate(segments) if n > 1], 128, tc_min_key_tiles)
     batch = StepBatch(
-        tc_tiles=dev(np.asarray(tc, dtype=np.int32).reshape(-1, 2)), num_tc_tiles=len(tc),
+        tc_units=dev(tc), num_tc_units=len(tc), num_tc_tiles=n_tc_tiles,
         decode_items=dev(items), num_decode_items=len(items),
         prefill_tiles=dev(units), num_prefill_units=len(units), num_prefill_tiles=n_tiles,
         num_tokens=T, num_segments=S, num_wanted=0, token_ids=dev(np.zeros(T)), positions=dev(pos),

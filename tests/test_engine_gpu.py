@@ -65,6 +65,28 @@ def test_portions(tmp_path, kernels, name, dtype):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
+def test_portions_replayed_from_graphs_equal_eager_launches(tmp_path, kernels, dtype):
+    """A step that brings one portion of one prompt is captured once per (length, lengths of the work lists)
+    and replayed; the logits are those of eager launches, bit for bit, also when the same graph serves
+    another request at other pages."""
+    runner, config, weights = _runner(tmp_path, kernels, "B", dtype)
+    tokens = random_tokens(config["vocab_size"], 101, 16)
+    sizes = [20, 20, 20, 20, 21]
+    eager = replay_modes.portions(runner, tokens, sizes)
+    runner.use_graphs = True
+    first = replay_modes.portions(runner, tokens, sizes)
+    other = random_tokens(config["vocab_size"], 101, 17)
+    runner.use_graphs = False
+    eager_other = replay_modes.portions(runner, other, sizes)
+    runner.use_graphs = True
+    again = replay_modes.portions(runner, other, sizes)
+    assert 1 <= len(runner._graphs) <= 2 and runner.graph_replays == 2 * len(sizes)
+    assert torch.equal(first, eager) and torch.equal(again, eager_other)
+    assert_close(first, logits_of(config, weights, tokens), REL[dtype])
+    kernels.check_errors()
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("name", NAMES)
 def test_mixed_with_page_reuse(tmp_path, kernels, name, dtype):
     page = PAGE_SIZE[name]

@@ -326,14 +326,17 @@ def test_paged_attention_flash(kernels, request, scenario):
 
 
 TC_SCENARIOS = [
-    # (segments (cached, new), Hq, Hkv, D, page, window)
-    ([(0, 128)], 2, 1, 64, 16, None),
-    ([(0, 300)], 4, 2, 64, 16, None),
-    ([(0, 700), (100, 70), (515, 2)], 14, 2, 64, 16, None),
-    ([(1000, 130), (0, 64)], 4, 4, 128, 16, None),
-    ([(0, 520)], 3, 1, 128, 64, None),
-    ([(300, 400)], 6, 2, 64, 8, 150),                       # window: pages behind it are not held
-    ([(0, 257)], 2, 2, 64, 64, 64),
+    # (segments (cached, new), Hq, Hkv, D, page, window, least key tiles of a unit)
+    ([(0, 128)], 2, 1, 64, 16, None, 8),
+    ([(0, 300)], 4, 2, 64, 16, None, 8),
+    ([(0, 700), (100, 70), (515, 2)], 14, 2, 64, 16, None, 8),
+    ([(1000, 130), (0, 64)], 4, 4, 128, 16, None, 8),
+    ([(0, 520)], 3, 1, 128, 64, None, 8),
+    ([(300, 400)], 6, 2, 64, 8, 150, 8),                    # window: pages behind it are not held
+    ([(0, 257)], 2, 2, 64, 64, 64, 8),
+    ([(0, 1100), (2000, 300)], 4, 2, 64, 16, None, 16),     # tiles cut into units over the keys and merged
+    ([(0, 700), (100, 70)], 6, 2, 64, 32, None, 1),         # units of a single key tile
+    ([(900, 700)], 4, 1, 128, 32, 300, 2),                  # units of a windowed layer: some hold no keys
 ]
 
 
@@ -342,10 +345,10 @@ def test_paged_attention_tc(kernels, request, scenario):
     """The tensor-memory prefill attention against float64 on the same bfloat16 inputs.  Pages behind a window
     are dropped from the block table, as the cache manager does, so the kernel must not touch them."""
     from kvcache_b200.engine.workspace import Workspace
-    segments, Hq, Hkv, D, page, window = scenario
+    segments, Hq, Hkv, D, page, window, min_key_tiles = scenario
     dtype = torch.bfloat16
     batch, kv = paged_scenario(segments, num_kv_heads=Hkv, head_dim=D, page_size=page, dtype=dtype, device="cpu",
-                               window=window, seed=22)
+                               window=window, seed=22, tc_min_key_tiles=min_key_tiles)
     T = batch.num_tokens
     q = torch.randn(T, Hq * D, generator=torch.Generator().manual_seed(23)).to(dtype)
     ref = torch.empty(T, Hq * D, dtype=dtype)
@@ -357,11 +360,15 @@ def test_paged_attention_tc(kernels, request, scenario):
     saved = kernels.tc_attention_min_rows
     kernels.tc_attention_min_rows = 2
     request.addfinalizer(lambda: setattr(kernels, "tc_attention_min_rows", saved))
-    out = torch.full((T, Hq * D), float("nan"), dtype=dtype, device=DEV)
-    kernels.paged_attention(q.to(DEV), batch_to(batch, DEV), clone_kv(kv, DEV), out, Hq, D ** -0.5, Workspace(DEV))
-    kernels.check_errors()
+    ws = Workspace(DEV)
     rows = torch.cat([torch.arange(n) + sum(m for _, m in segments[:i]) for i, (_, n) in enumerate(segments) if n > 1])
-    assert_close(out[rows], ref[rows], REL[dtype])
+    for _ in range(2):                                        # twice: the tickets of the first call must be zero again
+        out = torch.full((T, Hq * D), float("nan"), dtype=dtype, device=DEV)
+        kernels.paged_attention(q.to(DEV), batch_to(batch, DEV), clone_kv(kv, DEV), out, Hq, D ** -0.5, ws)
+        kernels.check_errors()
+        assert_close(out[rows], ref[rows], REL[dtype])
+    if "attn.tc_tickets" in ws._buffers:
+        assert int(ws._buffers["attn.tc_tickets"].sum()) == 0
 
 
 def test_flash_attention_sees_one_far_key_and_the_window_edge(kernels):

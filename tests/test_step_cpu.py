@@ -67,7 +67,12 @@ def test_prefill_work_list():
         nsplit = rows[0][3]
         assert [r[2] for r in rows] == list(range(nsplit)) and len({r[4] for r in rows}) == 1
         assert 1 <= nsplit <= 16
-    assert by_tile[0][0][3] == 1 and by_tile[31][0][3] == 8 and by_tile[32][0][:2] == (3, 0)   # 32 key tiles in units of 4
+    # Tiles with the most keys come first: tile 0 is the prompt's last 64 rows, 32 key tiles in units of 4.
+    assert by_tile[0][0][:2] == (0, 2048 - 64) and by_tile[0][0][3] == 8
+    assert by_tile[32][0][:2] == (0, 0) and by_tile[32][0][3] == 1 and (3, 0) in {r[0][:2] for r in by_tile.values()}
+    # The same prompt in tiles of 128 rows with units of at least 16 key tiles.
+    units128, n128 = plan_prefill_units([(0, 0, 2048)], 128, 16)
+    assert n128 == 16 and len(units128) == 24 and units128[0].tolist()[:4] == [0, 2048 - 128, 0, 2]
     # However long the prompt, the list stays bounded.
     units, n_tiles = plan_prefill_units([(0, 0, 32768)])
     assert n_tiles == 512 and len(units) <= 2 * 512 + 256
