@@ -192,14 +192,18 @@ def time_e2e(folder, batch, context, steps, warmup):
     go from pinned host memory to the device, and the sampled ids come back to the host."""
     import torch
     from kvcache_b200 import LLM, EngineOptions, SamplingParams
-    options = EngineOptions(dtype="bfloat16", page_size=16, max_cached_tokens=batch * (context + 16), max_running=batch,
-                            max_tokens_per_step=2048, chunk_size=2048, max_model_len=context + 16, use_graphs=True)
+    options = EngineOptions(dtype="bfloat16", page_size=16, max_cached_tokens=batch * (context + 64), max_running=batch,
+                            max_tokens_per_step=2048, chunk_size=2048, max_model_len=context + 64, use_graphs=True)
     llm = LLM(folder, options)
-    prompt_len = context - steps - warmup
+    # The prompts are prefilled one after the other under the token budget, so the requests start to decode a
+    # few steps apart; none may finish inside the timed region (the batch would shrink), and the longest ends
+    # at `context` tokens.
+    lead = 4 * batch
+    prompt_len = context - steps - warmup - lead
     g = torch.Generator().manual_seed(4)
     prompts = [torch.randint(0, llm.core.model.vocab_size, (prompt_len,), generator=g).tolist() for _ in range(batch)]
     for p in prompts:
-        llm.scheduler.add_request(p, SamplingParams(max_new_tokens=steps + warmup + 1, ignore_eos=True))
+        llm.scheduler.add_request(p, SamplingParams(max_new_tokens=steps + warmup + 2 * lead, ignore_eos=True))
     while any(r.num_computed < len(r.prompt) for r in llm.scheduler.running) or llm.scheduler.waiting:
         llm.step()                                   # prefill, untimed
     for _ in range(warmup):
@@ -213,6 +217,8 @@ def time_e2e(folder, batch, context, steps, warmup):
     end.record()
     torch.cuda.synchronize()
     wall = time.perf_counter() - wall
+    if len(llm.scheduler.running) != batch or llm.scheduler.stats.finished:
+        raise RuntimeError("a request finished inside the timed region: the steps did not all decode the whole batch")
     ms = max(begin.elapsed_time(end), wall * 1e3)
     h2d = llm.core.runner.last_h2d_bytes
     d2h = batch * 4
