@@ -7,6 +7,9 @@
 // over the keys with a tree reduction per key), with the split over the keys and its merge
 // taken from the toy flash-decode kernel (src/flash_decode.cu:18-101).
 #include "flash_core.cuh"
+#if KVB_HEAD_DIM % 64 == 0
+#include "tc_common.cuh"
+#endif
 
 using namespace flash;
 
@@ -264,10 +267,13 @@ KVB_API int kvb_flash_decode(const void* q, void* out, const void* k_pages, cons
 // ---------------------------------------------------------------------------------------------
 // Stages of keys/values in shared memory: two blocks share an SM.  (A block that takes most of an SM's shared
 // memory to request its whole split at once was measured slower: clusters of such blocks wait long for a place.)
-#define CLUSTER_STAGES (KVB_HEAD_DIM <= 64 ? 5 : 3)
+// For head sizes up to 64 a stage holds two 64-key tiles and a warp takes 32 keys of it: half as many barriers
+// per key, and four independent chains of MMAs instead of two.
+#define CLUSTER_STAGES 3
+#define CLUSTER_KW (KVB_HEAD_DIM <= 64 ? 2 : 1)      // key tiles per stage
 constexpr int MAX_CLUSTER = 8;      // the portable limit; clusters of 16 were measured slower (they wait long for a place)
 
-template <int STAGES>
+template <int STAGES, int KW>
 __global__ void __launch_bounds__(128) flash_decode_cluster_kernel(const __grid_constant__ DecodeParams p) {
     TRACE(0)
 #ifdef KVB_TRACE
@@ -286,18 +292,26 @@ __global__ void __launch_bounds__(128) flash_decode_cluster_kernel(const __grid_
     const int key_lo = (p.window > 0 && first_pos - p.window + 1 > 0) ? first_pos - p.window + 1 : 0;
     const int tile_begin = key_lo / KT, tile_end = (kv_len + KT - 1) / KT;
     const int num_tiles = tile_end - tile_begin;
-    const int per_split = (num_tiles + p.nsplit - 1) / p.nsplit;
+    // A stage holds KW key tiles, of which each warp takes 16 * KW keys; a split is a whole number of stages.
+    const int per_split = ((num_tiles + p.nsplit - 1) / p.nsplit + KW - 1) / KW * KW;
     const int my_begin = tile_begin + split * per_split;
     const int my_end = min(tile_end, my_begin + per_split);
-    const int n = max(0, my_end - my_begin);                                // a split may be empty; it still joins the barriers
+    const int n = max(0, (my_end - my_begin + KW - 1) / KW);                // stages to scan; a split may be empty and still joins the barriers
+    constexpr int NK = 16 * KW, STAGE_ELEMS = 2 * KW * TILE_ELEMS;
 
     KVSource src{p.k_pages, p.v_pages, p.block_table + (size_t)seg * p.table_stride, hk, p.Hkv, p.page_size, p.page_shift};
-    // The tiles of the prologue are old if all their keys lie before this step's first position.
-    const bool early = (my_begin + min(n, STAGES - 1)) * KT <= first_pos;
+    auto load_stage = [&](int i) {                                          // key tiles my_begin + i KW .. + KW - 1; beyond kv_len: zeros
+        bf16* ks = smem + (i % STAGES) * STAGE_ELEMS;
+#pragma unroll
+        for (int h = 0; h < KW; ++h)
+            load_tile(ks + h * TILE_ELEMS, ks + (KW + h) * TILE_ELEMS, src, (my_begin + i * KW + h) * KT, key_lo, kv_len);
+    };
+    // The stages of the prologue are old if all their keys lie before this step's first position.
+    const bool early = (my_begin + min(n, STAGES - 1) * KW) * KT <= first_pos;
     if (early) {
 #pragma unroll
         for (int s = 0; s < STAGES - 1; ++s) {
-            if (s < n) load_tile(smem + (2 * s) * TILE_ELEMS, smem + (2 * s + 1) * TILE_ELEMS, src, (my_begin + s) * KT, key_lo, kv_len);
+            if (s < n) load_stage(s);
             cp_async_commit();
         }
     }
@@ -307,7 +321,7 @@ __global__ void __launch_bounds__(128) flash_decode_cluster_kernel(const __grid_
     if (!early) {
 #pragma unroll
         for (int s = 0; s < STAGES - 1; ++s) {
-            if (s < n) load_tile(smem + (2 * s) * TILE_ELEMS, smem + (2 * s + 1) * TILE_ELEMS, src, (my_begin + s) * KT, key_lo, kv_len);
+            if (s < n) load_stage(s);
             cp_async_commit();
         }
     }
@@ -321,21 +335,16 @@ __global__ void __launch_bounds__(128) flash_decode_cluster_kernel(const __grid_
     w.pos[1] = g + 8 < rows ? first_pos + (g + 8) / G : -1;
 
     for (int i = 0; i < n; ++i) {
-        const int ahead = i + STAGES - 1;
-        if (ahead < n) {
-            const int s = ahead % STAGES;
-            load_tile(smem + (2 * s) * TILE_ELEMS, smem + (2 * s + 1) * TILE_ELEMS, src, (my_begin + ahead) * KT, key_lo, kv_len);
-        }
+        if (i + STAGES - 1 < n) load_stage(i + STAGES - 1);
         cp_async_commit();
         cp_async_wait<STAGES - 1>();
         __syncthreads();
         if (i == 0) { TRACE(2) }
-        const int s = i % STAGES;
-        const int key0 = (my_begin + i) * KT + warp * 16;
+        const bf16* ks = smem + (i % STAGES) * STAGE_ELEMS;
+        const int key0 = (my_begin + i * KW) * KT + warp * NK;
         if (key0 < kv_len)
-            rows_tile_auto<16>(w, smem + (2 * s) * TILE_ELEMS + warp * 16 * STRIDE,
-                               smem + (2 * s + 1) * TILE_ELEMS + warp * 16 * STRIDE, key0, p.window, p.scale_log2,
-                               first_pos, kv_len - 1, true);
+            rows_tile_auto<NK>(w, ks + warp * NK * STRIDE, ks + KW * TILE_ELEMS + warp * NK * STRIDE, key0, p.window,
+                               p.scale_log2, first_pos, kv_len - 1, true);
         __syncthreads();
     }
     cp_async_wait<0>();
@@ -442,8 +451,8 @@ KVB_API int kvb_flash_decode_cluster(const void* q, void* out, const void* k_pag
     while ((1 << p.page_shift) < page_size) ++p.page_shift;
     p.window = window; p.nsplit = nsplit;
     p.scale_log2 = scale * 1.4426950408889634f;
-    auto kernel = flash_decode_cluster_kernel<CLUSTER_STAGES>;
-    size_t smem = (size_t)CLUSTER_STAGES * 2 * TILE_ELEMS * sizeof(bf16);
+    auto kernel = flash_decode_cluster_kernel<CLUSTER_STAGES, CLUSTER_KW>;
+    size_t smem = (size_t)CLUSTER_STAGES * 2 * CLUSTER_KW * TILE_ELEMS * sizeof(bf16);
     const size_t merge = (size_t)(5 * 16 * D + 5 * 16 * 2) * sizeof(float);
     if (merge > smem) smem = merge;
     static bool configured = false;
@@ -458,6 +467,271 @@ KVB_API int kvb_flash_decode_cluster(const void* q, void* out, const void* k_pag
     kvb_launch_cluster(kernel, dim3(grid), dim3(128), (unsigned)nsplit, smem, stream, p);
     return kvb_launch_status();
 }
+
+#if KVB_HEAD_DIM % 64 == 0
+// ---------------------------------------------------------------------------------------------
+// The cluster kernel with keys and values brought by TMA (head sizes 64 and 128, pages of 8..64 tokens): a fifth
+// warp looks pages up and issues one tiled copy per page and 64 columns - a few large requests instead of
+// thousands of 16-byte ones - into 128-byte-swizzled stages; a stage is handed to the four scanning warps
+// through a "full" mbarrier and handed back through an "empty" one.  Everything else - the split into a
+// cluster, the merge, what is fetched before the wait - is as above.  Waits are bounded: on a timeout the
+// error word is set and the block winds down (it still joins the cluster's barriers).
+// ---------------------------------------------------------------------------------------------
+namespace dtma {
+using namespace tc;
+constexpr int HALVES = D / 64;
+constexpr int KW = D == 64 ? 2 : 1;                       // 64-key tiles per stage
+constexpr int STAGES = 3;
+constexpr int NKEYS = 64 * KW;
+constexpr int HALF_BYTES = NKEYS * 128;                   // a [NKEYS x 64 columns] swizzled sub-tile
+constexpr int KV_BYTES = HALVES * HALF_BYTES;             // keys of a stage; values follow
+constexpr int STAGE_BYTES = 2 * KV_BYTES;
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024;
+
+struct Shared {
+    uint64_t full[STAGES], empty[STAGES];
+    int failed;
+};
+
+__global__ void __launch_bounds__(160) flash_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k,
+                                                               const __grid_constant__ CUtensorMap map_v,
+                                                               const __grid_constant__ DecodeParams p, int* err) {
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char* stages = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    __shared__ Shared sh;
+    const int split = blockIdx.x, hk = blockIdx.y, item = blockIdx.z;       // the cluster spans x: split is the rank
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
+    const int G = p.Hq / p.Hkv;
+    // Written by the host's copy at the start of the step: safe to read before the wait.
+    const int seg = p.items ? p.items[item] : item;
+    const int q_start = p.seg_q_start[seg], q_len = p.seg_q_len[seg], kv_len = p.seg_kv_len[seg];
+    const int rows = q_len * G;
+    const int first_pos = kv_len - q_len;
+    const int key_lo = (p.window > 0 && first_pos - p.window + 1 > 0) ? first_pos - p.window + 1 : 0;
+    const int tile_begin = key_lo / KT, tile_end = (kv_len + KT - 1) / KT;
+    const int num_tiles = tile_end - tile_begin;
+    const int per_split = ((num_tiles + p.nsplit - 1) / p.nsplit + KW - 1) / KW * KW;
+    const int my_begin = tile_begin + split * per_split;
+    const int my_end = min(tile_end, my_begin + per_split);
+    const int n = max(0, (my_end - my_begin + KW - 1) / KW);                // stages to scan
+
+    if (tid == 0) {
+        for (int s = 0; s < STAGES; ++s) { mbar_init(&sh.full[s], 1); mbar_init(&sh.empty[s], 4); }
+        sh.failed = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+    }
+    __syncthreads();
+
+    WarpRows w;
+    rows_init(w);
+    if (warp == 4) {
+        // ---- loader warp ----
+        const int* table = p.block_table + (size_t)seg * p.table_stride;
+        const int pages_per_stage = NKEYS >> p.page_shift;
+        bool ok = true;
+        if (lane == 0) {
+            asm volatile("prefetch.tensormap [%0];\n" ::"l"(&map_k) : "memory");
+            asm volatile("prefetch.tensormap [%0];\n" ::"l"(&map_v) : "memory");
+        }
+        // Stage i holds keys [(my_begin + i KW) * 64, + NKEYS).  Lane pg takes page pg of it.
+        auto load_stage = [&](int i) {
+            const int s = i % STAGES;
+            unsigned char* dst = stages + (size_t)s * STAGE_BYTES;
+            const int key0 = (my_begin + i * KW) * KT;
+            int my_page = -1;
+            if (lane < pages_per_stage) {
+                const int first_key = key0 + lane * p.page_size;
+                if (first_key < kv_len && first_key + p.page_size > key_lo) my_page = table[first_key >> p.page_shift];
+            }
+            if (i >= STAGES) {
+                if (lane == 0) ok = mbar_wait(&sh.empty[s], ((i - STAGES) / STAGES) & 1);
+                ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+                if (!ok) return;
+            }
+            const unsigned held = __ballot_sync(0xffffffffu, my_page >= 0);
+            const int present = __popc(held);
+            if (present < pages_per_stage) {
+                // No page there (beyond the last key, or given back behind a window): the slot must still hold
+                // finite numbers, because 0 * NaN would poison the sums.
+                const int bytes = p.page_size * 128;
+                for (int pg = 0; pg < pages_per_stage; ++pg) {
+                    if ((held >> pg) & 1u) continue;
+                    for (int x = 0; x < 2 * HALVES; ++x)
+                        for (int off = lane * 16; off < bytes; off += 32 * 16)
+                            *reinterpret_cast<uint4*>(dst + x * HALF_BYTES + pg * bytes + off) = make_uint4(0, 0, 0, 0);
+                }
+                asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+                __syncwarp();
+            }
+            if (lane == 0) mbar_expect_tx(&sh.full[s], (uint32_t)present * 2 * HALVES * p.page_size * 128);
+            __syncwarp();
+            if (my_page >= 0) {
+                const int row = (my_page * p.Hkv + hk) * p.page_size;   // row of the pool seen as [pages * heads * page, D]
+#pragma unroll
+                for (int hb = 0; hb < HALVES; ++hb) {
+                    tma_load_2d(dst + hb * HALF_BYTES + lane * p.page_size * 128, &map_k, hb * 64, row, &sh.full[s]);
+                    tma_load_2d(dst + KV_BYTES + hb * HALF_BYTES + lane * p.page_size * 128, &map_v, hb * 64, row, &sh.full[s]);
+                }
+            }
+        };
+        // The first stages are old if all their keys lie before this step's first position: fetched before the wait.
+        const int first = min(n, STAGES);
+        const bool early = (my_begin + first * KW) * KT <= first_pos;
+        if (early)
+            for (int i = 0; i < first && ok; ++i) load_stage(i);
+        pdl_wait();
+        pdl_launch_dependents();
+        for (int i = early ? first : 0; i < n && ok; ++i) load_stage(i);
+        if (!ok && lane == 0) { atomicOr(err, KVB_DEV_TIMEOUT); sh.failed = 1; }
+    } else {
+        // ---- scanning warps ----
+        pdl_wait();
+        pdl_launch_dependents();
+        auto q_row = [&](int r) -> const bf16* {
+            return r < rows ? p.q + ((size_t)(q_start + r / G) * p.Hq + hk * G + r % G) * D : nullptr;
+        };
+        rows_load_q(w, q_row);
+        w.pos[0] = g < rows ? first_pos + g / G : -1;
+        w.pos[1] = g + 8 < rows ? first_pos + (g + 8) / G : -1;
+        constexpr int NK = 16 * KW;
+        for (int i = 0; i < n; ++i) {
+            const int s = i % STAGES;
+            if (!mbar_wait(&sh.full[s], (i / STAGES) & 1)) {
+                if (lane == 0) { atomicOr(err, KVB_DEV_TIMEOUT); sh.failed = 1; }
+                break;
+            }
+            const unsigned char* base = stages + (size_t)s * STAGE_BYTES + warp * NK * 128;   // this warp's keys: rows warp NK ..
+            const int key0 = (my_begin + i * KW) * KT + warp * NK;
+            if (key0 < kv_len)
+                rows_tile_auto_in<NK>(w, SwizzledTile{base, HALF_BYTES}, SwizzledTile{base + KV_BYTES, HALF_BYTES}, key0,
+                                      p.window, p.scale_log2, first_pos, kv_len - 1, true);
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&sh.empty[s]);
+        }
+        rows_finish_sum(w);
+    }
+    __syncthreads();                                           // every stage has been read: the merge may reuse them
+
+    float* wo = reinterpret_cast<float*>(stages);              // [4][16][D]
+    float* wml = wo + 4 * 16 * D;                              // [4][16][2]
+    float* res_o = wml + 4 * 16 * 2;                           // [16][D]   this block's acc
+    float* res_ml = res_o + 16 * D;                            // [16][2]   this block's (m, l)
+    if (warp < 4) {
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+            const int row = g + 8 * r;
+#pragma unroll
+            for (int i = 0; i < NT_O; ++i)
+                *reinterpret_cast<float2*>(wo + (warp * 16 + row) * D + i * 8 + 2 * t) = make_float2(w.o[i][2 * r], w.o[i][2 * r + 1]);
+            if (t == 0) { wml[(warp * 16 + row) * 2] = w.m[r]; wml[(warp * 16 + row) * 2 + 1] = w.l[r]; }
+        }
+    }
+    __syncthreads();
+    for (int idx = tid; idx < rows * D; idx += 160) {
+        const int row = idx / D, d = idx - row * D;
+        float M = NEG_INF;
+#pragma unroll
+        for (int x = 0; x < 4; ++x) M = fmaxf(M, wml[(x * 16 + row) * 2]);
+        const float base = M == NEG_INF ? 0.f : M;
+        float L = 0.f, acc = 0.f;
+#pragma unroll
+        for (int x = 0; x < 4; ++x) {
+            const float e = exp2f(wml[(x * 16 + row) * 2] - base);
+            L += e * wml[(x * 16 + row) * 2 + 1];
+            acc += e * wo[(x * 16 + row) * D + d];
+        }
+        if (p.nsplit == 1) {
+            p.out[((size_t)(q_start + row / G) * p.Hq + hk * G + row % G) * D + d] = __float2bfloat16_rn(L > 0.f ? acc / L : 0.f);
+        } else {
+            res_o[row * D + d] = acc;
+            if (d == 0) { res_ml[row * 2] = M; res_ml[row * 2 + 1] = L; }
+        }
+    }
+    if (p.nsplit == 1) return;
+
+    cluster_sync_all();                                        // every block's result is in its shared memory
+    const int my_rows = rows > split ? (rows - split + p.nsplit - 1) / p.nsplit : 0;
+    for (int idx = tid; idx < my_rows * (D / 4); idx += 160) {
+        const int row = split + (idx / (D / 4)) * p.nsplit, d = (idx % (D / 4)) * 4;
+        float2 ml[MAX_CLUSTER];
+        float4 v[MAX_CLUSTER];
+#pragma unroll
+        for (int s = 0; s < MAX_CLUSTER; ++s) {
+            if (s < p.nsplit) {
+                ml[s] = peer_ld2(peer_smem(res_ml + row * 2, s));
+                v[s] = peer_ld4(peer_smem(res_o + row * D + d, s));
+            } else {
+                ml[s] = make_float2(NEG_INF, 0.f);
+                v[s] = make_float4(0.f, 0.f, 0.f, 0.f);
+            }
+        }
+        float M = NEG_INF;
+#pragma unroll
+        for (int s = 0; s < MAX_CLUSTER; ++s) M = fmaxf(M, ml[s].x);
+        const float base = M == NEG_INF ? 0.f : M;
+        float L = 0.f;
+        float e[MAX_CLUSTER];
+#pragma unroll
+        for (int s = 0; s < MAX_CLUSTER; ++s) {
+            e[s] = exp2f(ml[s].x - base);
+            L += e[s] * ml[s].y;
+        }
+        const float inv = L > 0.f ? 1.f / L : 0.f;
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+        for (int s = 0; s < MAX_CLUSTER; ++s) {
+            const float ws = e[s] * inv;
+            acc.x += ws * v[s].x; acc.y += ws * v[s].y; acc.z += ws * v[s].z; acc.w += ws * v[s].w;
+        }
+        bf16* o = p.out + ((size_t)(q_start + row / G) * p.Hq + hk * G + row % G) * D + d;
+        *reinterpret_cast<uint2*>(o) = make_uint2(pack_bf16(acc.x, acc.y), pack_bf16(acc.z, acc.w));
+    }
+    cluster_sync_all();                                        // no block leaves while another still reads its result
+}
+}  // namespace dtma
+
+// The splits as a cluster, keys and values by TMA: nsplit 1..8, page_size a power of two 8..64, num_pages the pool's
+// page count, err the device error word.
+KVB_API int kvb_flash_decode_tma(const void* q, void* out, const void* k_pages, const void* v_pages, int num_pages,
+                                 const int* block_table, int table_stride, const int* items, int n_items,
+                                 const int* seg_q_start, const int* seg_q_len, const int* seg_kv_len, int Hq, int Hkv,
+                                 int page_size, int window, int nsplit, float scale, int* err, cudaStream_t stream) {
+    using namespace dtma;
+    if (n_items <= 0) return KVB_OK;
+    if (Hkv < 1 || Hq % Hkv != 0 || Hq / Hkv > 16) return KVB_ERR_SHAPE;
+    if (page_size < 8 || page_size > 64 || (page_size & (page_size - 1)) != 0) return KVB_ERR_SHAPE;
+    if (nsplit < 1 || nsplit > MAX_CLUSTER || n_items > 65535 || Hkv > 65535) return KVB_ERR_LIMIT;
+    if (((uintptr_t)k_pages | (uintptr_t)v_pages) & 15) return KVB_ERR_ALIGN;
+    CUtensorMap mk, mv;
+    const long long pool_rows = (long long)num_pages * Hkv * page_size;
+    int rc = make_bf16_map(&mk, k_pages, pool_rows, D, D, page_size);
+    if (rc != KVB_OK) return rc;
+    rc = make_bf16_map(&mv, v_pages, pool_rows, D, D, page_size);
+    if (rc != KVB_OK) return rc;
+    DecodeParams p;
+    p.q = (const bf16*)q; p.out = (bf16*)out; p.k_pages = (const bf16*)k_pages; p.v_pages = (const bf16*)v_pages;
+    p.block_table = block_table; p.items = items; p.seg_q_start = seg_q_start; p.seg_q_len = seg_q_len;
+    p.seg_kv_len = seg_kv_len;
+    p.part_o = nullptr; p.part_ml = nullptr; p.tickets = nullptr;
+    p.table_stride = table_stride; p.Hq = Hq; p.Hkv = Hkv; p.page_size = page_size;
+    p.page_shift = 0;
+    while ((1 << p.page_shift) < page_size) ++p.page_shift;
+    p.window = window; p.nsplit = nsplit;
+    p.scale_log2 = scale * 1.4426950408889634f;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(flash_decode_tma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+        if (e != cudaSuccess) return (int)e;
+        e = cudaFuncSetAttribute(flash_decode_tma_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+        if (e != cudaSuccess) return (int)e;
+        configured = true;
+    }
+    dim3 grid(nsplit, Hkv, n_items);
+    kvb_launch_cluster(flash_decode_tma_kernel, dim3(grid), dim3(160), (unsigned)nsplit, (size_t)SMEM_BYTES, stream, mk, mv, p, err);
+    return kvb_launch_status();
+}
+#endif
 
 // ---------------------------------------------------------------------------------------------
 // Prefill: one block of four warps per (unit, query head).  A tile is 64 consecutive query positions of one

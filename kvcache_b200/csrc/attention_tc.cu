@@ -467,20 +467,6 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     }
 }
 
-// A bfloat16 matrix [rows, cols] with `row_stride` elements between rows; tiles of [box_rows, 64], 128-byte swizzle.
-static int make_map(CUtensorMap* map, const void* base, long long rows, int cols, long long row_stride, int box_rows) {
-    EncodeTiled fn = encode_fn();
-    if (!fn) return KVB_ERR_LIMIT;
-    cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
-    cuuint64_t strides[1] = {(cuuint64_t)row_stride * 2};
-    cuuint32_t box[2] = {64u, (cuuint32_t)box_rows};
-    cuuint32_t estr[2] = {1, 1};
-    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
-                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    return r == CUDA_SUCCESS ? KVB_OK : KVB_ERR_SHAPE;
-}
-
 }  // namespace atc
 
 KVB_API int kvb_attention_tc_head_dim() { return atc::D; }
@@ -504,12 +490,12 @@ KVB_API int kvb_attention_tc(const void* q, void* out, const void* k_pages, cons
     if (page_size < 8 || page_size > atc::BKEYS || (page_size & (page_size - 1)) != 0) return KVB_ERR_SHAPE;
     if (((uintptr_t)q | (uintptr_t)out | (uintptr_t)k_pages | (uintptr_t)v_pages) & 15) return KVB_ERR_ALIGN;
     CUtensorMap mq, mk, mv;
-    int rc = make_map(&mq, q, T, Hq * D, (long long)Hq * D, BQ);
+    int rc = make_bf16_map(&mq, q, T, Hq * D, (long long)Hq * D, BQ);
     if (rc != KVB_OK) return rc;
     const long long pool_rows = (long long)num_pages * Hkv * page_size;
-    rc = make_map(&mk, k_pages, pool_rows, D, D, page_size);
+    rc = make_bf16_map(&mk, k_pages, pool_rows, D, D, page_size);
     if (rc != KVB_OK) return rc;
-    rc = make_map(&mv, v_pages, pool_rows, D, D, page_size);
+    rc = make_bf16_map(&mv, v_pages, pool_rows, D, D, page_size);
     if (rc != KVB_OK) return rc;
     Params p;
     p.out = (bf16*)out; p.block_table = block_table; p.units = units; p.seg_q_start = seg_q_start; p.seg_q_len = seg_q_len;

@@ -122,12 +122,26 @@ __device__ __forceinline__ void rows_load_q(WarpRows& w, RowPtr row_ptr) {
     }
 }
 
-// NK keys [key0, key0 + NK) whose rows start at `ks` / `vs` in a stage: scores, masking, running
+// Where element (row, col) of a key or value tile lies in shared memory; col is a multiple of 8 (ldmatrix
+// takes 16 bytes of a row per lane).
+struct PaddedTile {            // rows STRIDE elements apart (cp.async fills it)
+    const bf16* base;
+    __device__ __forceinline__ const bf16* at(int row, int col) const { return base + row * STRIDE + col; }
+};
+struct SwizzledTile {          // as TMA leaves it with the 128-byte swizzle: rows of 64 elements (128 bytes), whose 16-byte
+    const unsigned char* base; // chunk c sits at chunk position c ^ (row % 8); the next 64 columns lie `half_bytes` further.
+    int half_bytes;            // `base` is 1024-byte aligned.
+    __device__ __forceinline__ const bf16* at(int row, int col) const {
+        return reinterpret_cast<const bf16*>(base + (col >> 6) * half_bytes + row * 128 + ((((col & 63) >> 3) ^ (row & 7)) << 4));
+    }
+};
+
+// NK keys [key0, key0 + NK) whose rows start at row 0 of `kt` / `vt`: scores, masking, running
 // softmax, weighted sum.  NK is a multiple of 16 (a whole tile, or a part of one).
 // A key j is seen by a row at position p iff key_lo(p) <= j <= p, key_lo(p) = max(0, p - window + 1).
 // MASKED = false: the caller knows that every row sees every key of the range.
-template <int NK, bool MASKED>
-__device__ __forceinline__ void rows_tile(WarpRows& w, const bf16* ks, const bf16* vs, int key0, int window,
+template <int NK, bool MASKED, class Tile>
+__device__ __forceinline__ void rows_tile(WarpRows& w, const Tile& kt, const Tile& vt, int key0, int window,
                                           float scale_log2) {
     const int lane = threadIdx.x & 31, t = lane & 3;
     float s[NK / 8][4];
@@ -140,7 +154,7 @@ __device__ __forceinline__ void rows_tile(WarpRows& w, const bf16* ks, const bf1
 #pragma unroll
             for (int n2 = 0; n2 < NK / 16; ++n2) {
                 uint32_t b0, b1, b2, b3;
-                ldmatrix_x4(b0, b1, b2, b3, ks + (n2 * 16 + key_off) * STRIDE + k * 16 + d_off);
+                ldmatrix_x4(b0, b1, b2, b3, kt.at(n2 * 16 + key_off, k * 16 + d_off));
                 mma_bf16(s[2 * n2], w.q[k], b0, b1);
                 mma_bf16(s[2 * n2 + 1], w.q[k], b2, b3);
             }
@@ -200,7 +214,7 @@ __device__ __forceinline__ void rows_tile(WarpRows& w, const bf16* ks, const bf1
 #pragma unroll
             for (int n2 = 0; n2 < NT_O / 2; ++n2) {
                 uint32_t b0, b1, b2, b3;
-                ldmatrix_x4_trans(b0, b1, b2, b3, vs + (kk * 16 + key_off) * STRIDE + n2 * 16 + d_off);
+                ldmatrix_x4_trans(b0, b1, b2, b3, vt.at(kk * 16 + key_off, n2 * 16 + d_off));
                 mma_bf16(w.o[2 * n2], pa, b0, b1);
                 mma_bf16(w.o[2 * n2 + 1], pa, b2, b3);
             }
@@ -210,12 +224,17 @@ __device__ __forceinline__ void rows_tile(WarpRows& w, const bf16* ks, const bf1
 
 // NK keys from key0 on: masked only if a row may miss one of them.  `pos_min` / `pos_max`: smallest and
 // largest position among the warp's existing rows.
+template <int NK, class Tile>
+__device__ __forceinline__ void rows_tile_auto_in(WarpRows& w, const Tile& kt, const Tile& vt, int key0, int window,
+                                               float scale_log2, int pos_min, int pos_max, bool all_rows_exist) {
+    const bool open = all_rows_exist && key0 + NK - 1 <= pos_min && (window <= 0 || key0 > pos_max - window);
+    if (open) rows_tile<NK, false>(w, kt, vt, key0, window, scale_log2);
+    else rows_tile<NK, true>(w, kt, vt, key0, window, scale_log2);
+}
 template <int NK>
 __device__ __forceinline__ void rows_tile_auto(WarpRows& w, const bf16* ks, const bf16* vs, int key0, int window,
                                                float scale_log2, int pos_min, int pos_max, bool all_rows_exist) {
-    const bool open = all_rows_exist && key0 + NK - 1 <= pos_min && (window <= 0 || key0 > pos_max - window);
-    if (open) rows_tile<NK, false>(w, ks, vs, key0, window, scale_log2);
-    else rows_tile<NK, true>(w, ks, vs, key0, window, scale_log2);
+    rows_tile_auto_in<NK>(w, PaddedTile{ks}, PaddedTile{vs}, key0, window, scale_log2, pos_min, pos_max, all_rows_exist);
 }
 
 // Sums each row's l over the four threads that share it.

@@ -102,4 +102,19 @@ static EncodeTiled encode_fn() {
     return fn;
 }
 
+// A bfloat16 matrix [rows, cols] with `row_stride` elements between rows, read in tiles of [box_rows, 64] with the
+// 128-byte swizzle.
+static int make_bf16_map(CUtensorMap* map, const void* base, long long rows, int cols, long long row_stride, int box_rows) {
+    EncodeTiled fn = encode_fn();
+    if (!fn) return KVB_ERR_LIMIT;
+    cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)row_stride * 2};
+    cuuint32_t box[2] = {64u, (cuuint32_t)box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? KVB_OK : KVB_ERR_SHAPE;
+}
+
 }  // namespace tc

@@ -109,6 +109,9 @@ _SIGNATURES = {
         "kvb_flash_decode_cluster": [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_int,
                                      _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float,
                                      _c_void_p],
+        "kvb_flash_decode_tma": [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_int, _c_void_p, _c_int,
+                                 _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float,
+                                 _c_void_p, _c_void_p],
         "kvb_flash_prefill": [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_int, _c_void_p,
                               _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_float, _c_void_p],
     },
@@ -125,6 +128,9 @@ _SIGNATURES = {
 }
 
 
+_OPTIONAL = {"kvb_flash_decode_tma"}      # only in attention_flash variants for head sizes 64 and 128
+
+
 class _Library:
     """A lazily built and loaded kernel module with typed entry points."""
 
@@ -136,7 +142,12 @@ class _Library:
         if self._lib is None:
             lib = build.load_module(self.module, self.variant, self.flags)
             for fname, argtypes in _SIGNATURES[self.module].items():
-                fn = getattr(lib, fname)
+                try:
+                    fn = getattr(lib, fname)
+                except AttributeError:
+                    if fname in _OPTIONAL:
+                        continue              # a variant compiled for a size that has no such entry point
+                    raise
                 fn.argtypes = argtypes
                 fn.restype = _c_int
             self._lib = lib
@@ -175,9 +186,10 @@ class CudaKernels(KernelSet):
         self.tc_attention_min_rows: Optional[int] = 64
         self.flash_attention = True          # bfloat16, head sizes 16..128: tensor-core kernels
         # Decode attention splits the keys of a request over blocks.  "cluster": the splits (at most 8) are a
-        # thread-block cluster and merge through distributed shared memory; "ticket": up to 32 splits leave
-        # partial results in scratch and the last one to finish merges them.
-        self.decode_merge = "cluster"
+        # thread-block cluster and merge through distributed shared memory; "tma": the same with keys and values
+        # brought by TMA (head sizes 64 and 128, pages of 8..64 tokens; otherwise it falls back to "cluster");
+        # "ticket": up to 32 splits leave partial results in scratch and the last one to finish merges them.
+        self.decode_merge = "tma"
         self.decode_cluster_max = 8          # the kernel's limit
         self.decode_ctas_wanted = 148 * 2    # the split over the keys aims at this many blocks in flight
         self.decode_min_tiles = 4            # ... but gives a split at least this many 64-key tiles
@@ -336,10 +348,18 @@ class CudaKernels(KernelSet):
                 # Sized by the longest request the block table allows, not by this step's lengths, so that the
                 # split (and with it the rounding) is the same in every step and under a CUDA graph.
                 tiles = -(-(kv.block_table.shape[1] * kv.page_size) // 64)
-                if self.decode_merge == "cluster":
+                if self.decode_merge in ("cluster", "tma"):
                     nsplit = max(1, min(self.decode_cluster_max, self.decode_ctas_wanted // (n * Hkv),
                                         tiles // self.decode_min_tiles))
                     self.launches += 1
+                    if self.decode_merge == "tma" and D % 64 == 0 and 8 <= kv.page_size <= 64:
+                        _check(lib.kvb_flash_decode_tma(
+                            _ptr(q), _ptr(out), _ptr(kv.k_pages), _ptr(kv.v_pages), kv.k_pages.shape[0],
+                            _ptr(kv.block_table), kv.block_table.shape[1], _ptr(batch.decode_items), n,
+                            _ptr(batch.seg_q_start), _ptr(batch.seg_q_len), _ptr(batch.seg_kv_len), num_heads, Hkv,
+                            kv.page_size, spec.window or 0, nsplit, float(scale), _ptr(self.error_word), self._stream()),
+                            "flash_decode_tma")
+                        return
                     _check(lib.kvb_flash_decode_cluster(
                         _ptr(q), _ptr(out), _ptr(kv.k_pages), _ptr(kv.v_pages), _ptr(kv.block_table),
                         kv.block_table.shape[1], _ptr(batch.decode_items), n, _ptr(batch.seg_q_start),

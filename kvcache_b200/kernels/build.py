@@ -34,7 +34,7 @@ MODULES: Dict[str, dict] = {
     "gemm_skinny": {"src": "gemm_skinny.cu", "deps": ["common.cuh"]},
     "gemm_tcgen05": {"src": "gemm_tcgen05.cu", "deps": ["common.cuh", "tc_common.cuh"]},
     # Compiled per head size: variant "d<head_dim>" with -DKVB_HEAD_DIM=<head_dim>.
-    "attention_flash": {"src": "attention_flash.cu", "deps": ["common.cuh", "flash_core.cuh", "no_alloc.h"]},
+    "attention_flash": {"src": "attention_flash.cu", "deps": ["common.cuh", "flash_core.cuh", "no_alloc.h", "tc_common.cuh"]},
     "attention_tc": {"src": "attention_tc.cu", "deps": ["common.cuh", "tc_common.cuh"]},
 }
 # Variants that `build_all` makes for modules compiled per size.

@@ -311,7 +311,7 @@ def test_paged_attention_flash(kernels, request, scenario):
     saved = (kernels.decode_merge, kernels.decode_ctas_wanted, kernels.decode_min_tiles)
     request.addfinalizer(lambda: [setattr(kernels, n, v) for n, v in
                                   zip(("decode_merge", "decode_ctas_wanted", "decode_min_tiles"), saved)])
-    for merge in ("cluster", "ticket"):                  # the splits of a request as a cluster, or through scratch
+    for merge in ("tma", "cluster", "ticket"):           # the splits as a cluster (keys by TMA, or by cp.async), or through scratch
         kernels.decode_merge = merge
         # default; one split; as many as allowed; a number of splits that does not divide the rows
         for wanted, min_tiles in ((saved[1], saved[2]), (3, 4), (100000, 1), (5 * len(segments) * Hkv, 1)):
