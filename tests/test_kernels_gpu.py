@@ -290,6 +290,9 @@ FLASH_SCENARIOS = SCENARIOS[:6] + [
     ([(50, 3), (64, 2)], 2, 1, 112, 16, None),
     ([(0, 1500), (3000, 70)], 6, 2, 64, 16, None),                              # long tiles cut into units and merged
     ([(900, 700)], 4, 1, 64, 32, 300),                                          # units of a windowed layer: some hold no keys
+    ([(1000, 1), (70, 2), (5, 1), (2047, 1)], 8, 2, 64, 8, 200),                # decode by TMA: small pages, a window that gave pages back
+    ([(777, 1), (3000, 1), (15, 1)], 8, 4, 128, 32, None),                      # decode by TMA: head size 128, splits without keys
+    ([(130, 1), (64, 2)], 3, 3, 64, 64, 100),                                   # decode by TMA: a page is a whole key tile
 ]
 
 
@@ -304,6 +307,9 @@ def test_paged_attention_flash(kernels, request, scenario):
     q = torch.randn(T, Hq * D, generator=torch.Generator().manual_seed(13)).to(dtype)
     ref = torch.empty(T, Hq * D, dtype=dtype)
     REF.paged_attention(q, batch, kv, ref, Hq, D ** -0.5)
+    if window:                                           # as the cache manager does: pages behind the window are not held
+        for i, (cached, new) in enumerate(segments):
+            kv.block_table[i, :max(0, cached - window + 1) // page] = -1
     ws = Workspace(DEV)
     saved_tc = kernels.tc_attention_min_rows
     kernels.tc_attention_min_rows = None                 # this test is about the mma.sync kernels
