@@ -44,7 +44,8 @@ def test_embed_flags_bad_token(kernels):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("T,H,eps", [(1, 64, 1e-6), (5, 896, 1e-6), (19, 120, 1e-5), (3, 3584, 1e-6), (4, 50, 1e-3)])
+@pytest.mark.parametrize("T,H,eps", [(1, 64, 1e-6), (5, 896, 1e-6), (19, 120, 1e-5), (3, 3584, 1e-6), (4, 50, 1e-3),
+                                     (300, 896, 1e-6), (257, 5000, 1e-5), (261, 120, 1e-6)])   # many rows, rows longer than the registers keep
 def test_add_rmsnorm(kernels, dtype, T, H, eps):
     g = torch.Generator().manual_seed(1)
     h = torch.randn(T, H, generator=g) * 3
@@ -64,6 +65,14 @@ def test_add_rmsnorm(kernels, dtype, T, H, eps):
     kernels.add_rmsnorm(h_dev, delta.to(DEV), w.to(DEV), eps, out, rows.to(DEV))
     assert torch.equal(h_dev.cpu(), h), "with rows the residual stream is left alone"
     assert_close(out, out_ref, REL[dtype], "gathered rows")
+    if T >= 256:                                             # a long gather
+        rows = torch.arange(T - 1, -1, -1, dtype=torch.int32)
+        out_ref = torch.empty(T, H, dtype=dtype)
+        REF.add_rmsnorm(h.clone(), delta, w, eps, out_ref, rows)
+        h_dev, out = h.clone().to(DEV), torch.empty(T, H, dtype=dtype, device=DEV)
+        kernels.add_rmsnorm(h_dev, delta.to(DEV), w.to(DEV), eps, out, rows.to(DEV))
+        assert torch.equal(h_dev.cpu(), h)
+        assert_close(out, out_ref, REL[dtype], "many gathered rows")
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
@@ -238,10 +247,12 @@ SCENARIOS = [
     ([(515, 2), (127, 1)], 5, 1, 128, 32, 128),
     ([(0, 9)], 2, 2, 256, 4, None),
 ]
+# Steps of many rows take the kernel that handles four rows per block (a count of rows that four does not divide).
+ROPE_SCENARIOS = SCENARIOS + [([(40, 301), (3, 1), (0, 61)], 6, 2, 64, 16, None), ([(0, 258)], 3, 1, 48, 8, 100)]
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("scenario", SCENARIOS)
+@pytest.mark.parametrize("scenario", ROPE_SCENARIOS)
 def test_qkv_rope_append(kernels, dtype, scenario):
     segments, Hq, Hkv, D, page, window = scenario
     batch, kv = paged_scenario(segments, num_kv_heads=Hkv, head_dim=D, page_size=page, dtype=dtype, device="cpu",
