@@ -486,7 +486,8 @@ constexpr int NKEYS = 64 * KW;
 constexpr int HALF_BYTES = NKEYS * 128;                   // a [NKEYS x 64 columns] swizzled sub-tile
 constexpr int KV_BYTES = HALVES * HALF_BYTES;             // keys of a stage; values follow
 constexpr int STAGE_BYTES = 2 * KV_BYTES;
-constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024;
+constexpr int RECV_BYTES = 24 * (D + 2) * 4;               // nsplit * ceil(16 / nsplit) <= 24 row slots of (m, l, acc)
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + RECV_BYTES + 1024;
 
 struct Shared {
     uint64_t full[STAGES], empty[STAGES];
@@ -496,6 +497,8 @@ struct Shared {
 __global__ void __launch_bounds__(160) flash_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k,
                                                                const __grid_constant__ CUtensorMap map_v,
                                                                const __grid_constant__ DecodeParams p, int* err) {
+    TRACE(0)
+    if (p.nsplit > 1) cluster_arrive_started();
     extern __shared__ unsigned char smem_raw[];
     unsigned char* stages = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     __shared__ Shared sh;
@@ -588,6 +591,7 @@ __global__ void __launch_bounds__(160) flash_decode_tma_kernel(const __grid_cons
         // ---- scanning warps ----
         pdl_wait();
         pdl_launch_dependents();
+        TRACE(1)
         auto q_row = [&](int r) -> const bf16* {
             return r < rows ? p.q + ((size_t)(q_start + r / G) * p.Hq + hk * G + r % G) * D : nullptr;
         };
@@ -601,6 +605,7 @@ __global__ void __launch_bounds__(160) flash_decode_tma_kernel(const __grid_cons
                 if (lane == 0) { atomicOr(err, KVB_DEV_TIMEOUT); sh.failed = 1; }
                 break;
             }
+            if (i == 0) { TRACE(2) }
             const unsigned char* base = stages + (size_t)s * STAGE_BYTES + warp * NK * 128;   // this warp's keys: rows warp NK ..
             const int key0 = (my_begin + i * KW) * KT + warp * NK;
             if (key0 < kv_len)
@@ -610,13 +615,18 @@ __global__ void __launch_bounds__(160) flash_decode_tma_kernel(const __grid_cons
             if (lane == 0) mbar_arrive(&sh.empty[s]);
         }
         rows_finish_sum(w);
+        TRACE(3)
     }
     __syncthreads();                                           // every stage has been read: the merge may reuse them
 
     float* wo = reinterpret_cast<float*>(stages);              // [4][16][D]
     float* wml = wo + 4 * 16 * D;                              // [4][16][2]
-    float* res_o = wml + 4 * 16 * 2;                           // [16][D]   this block's acc
-    float* res_ml = res_o + 16 * D;                            // [16][2]   this block's (m, l)
+    // What the other blocks of the cluster send: slot s holds block s's (m, l, acc) of the rows this block finishes
+    // (rows split, split + nsplit, ...: at most `rpo` of them).  It lies behind the stages, which a block may
+    // still be filling while others already send.
+    const int rpo = (16 + p.nsplit - 1) / p.nsplit;
+    float* recv_o = reinterpret_cast<float*>(stages + STAGES * STAGE_BYTES);   // [nsplit][rpo][D]
+    float* recv_ml = recv_o + p.nsplit * rpo * D;                                // [nsplit][rpo][2]
     if (warp < 4) {
 #pragma unroll
         for (int r = 0; r < 2; ++r) {
@@ -628,39 +638,49 @@ __global__ void __launch_bounds__(160) flash_decode_tma_kernel(const __grid_cons
         }
     }
     __syncthreads();
-    for (int idx = tid; idx < rows * D; idx += 160) {
-        const int row = idx / D, d = idx - row * D;
+    if (p.nsplit > 1) cluster_wait_started();                  // every block of the cluster is running: its memory may be written
+    // The four warps' results become the block's: four columns of one row per thread and step.
+    for (int idx = tid; idx < rows * (D / 4); idx += 160) {
+        const int row = idx / (D / 4), d = (idx - row * (D / 4)) * 4;
         float M = NEG_INF;
 #pragma unroll
         for (int x = 0; x < 4; ++x) M = fmaxf(M, wml[(x * 16 + row) * 2]);
         const float base = M == NEG_INF ? 0.f : M;
-        float L = 0.f, acc = 0.f;
+        float L = 0.f;
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
         for (int x = 0; x < 4; ++x) {
             const float e = exp2f(wml[(x * 16 + row) * 2] - base);
+            const float4 v = *reinterpret_cast<const float4*>(wo + (x * 16 + row) * D + d);
             L += e * wml[(x * 16 + row) * 2 + 1];
-            acc += e * wo[(x * 16 + row) * D + d];
+            acc.x += e * v.x; acc.y += e * v.y; acc.z += e * v.z; acc.w += e * v.w;
         }
         if (p.nsplit == 1) {
-            p.out[((size_t)(q_start + row / G) * p.Hq + hk * G + row % G) * D + d] = __float2bfloat16_rn(L > 0.f ? acc / L : 0.f);
+            const float inv = L > 0.f ? 1.f / L : 0.f;
+            bf16* o = p.out + ((size_t)(q_start + row / G) * p.Hq + hk * G + row % G) * D + d;
+            *reinterpret_cast<uint2*>(o) = make_uint2(pack_bf16(acc.x * inv, acc.y * inv), pack_bf16(acc.z * inv, acc.w * inv));
         } else {
-            res_o[row * D + d] = acc;
-            if (d == 0) { res_ml[row * 2] = M; res_ml[row * 2 + 1] = L; }
+            // To the block that finishes this row, into the slot of this split.
+            const int owner = row % p.nsplit, k = row / p.nsplit;
+            peer_st4(peer_smem(recv_o + ((size_t)split * rpo + k) * D + d, owner), acc);
+            if (d == 0) peer_st2(peer_smem(recv_ml + ((size_t)split * rpo + k) * 2, owner), make_float2(M, L));
         }
     }
     if (p.nsplit == 1) return;
 
-    cluster_sync_all();                                        // every block's result is in its shared memory
+    cluster_sync_all();                                        // what was sent has arrived; nobody reads another block's memory after this
+    TRACE(4)
+    // weight_s = 2^(m_s - M) / sum_s 2^(m_s - M) l_s; out = sum_s weight_s acc_s, added in split order.
     const int my_rows = rows > split ? (rows - split + p.nsplit - 1) / p.nsplit : 0;
     for (int idx = tid; idx < my_rows * (D / 4); idx += 160) {
-        const int row = split + (idx / (D / 4)) * p.nsplit, d = (idx % (D / 4)) * 4;
+        const int k = idx / (D / 4), row = split + k * p.nsplit, d = (idx % (D / 4)) * 4;
         float2 ml[MAX_CLUSTER];
         float4 v[MAX_CLUSTER];
 #pragma unroll
         for (int s = 0; s < MAX_CLUSTER; ++s) {
             if (s < p.nsplit) {
-                ml[s] = peer_ld2(peer_smem(res_ml + row * 2, s));
-                v[s] = peer_ld4(peer_smem(res_o + row * D + d, s));
+                ml[s] = *reinterpret_cast<const float2*>(recv_ml + ((size_t)s * rpo + k) * 2);
+                v[s] = *reinterpret_cast<const float4*>(recv_o + ((size_t)s * rpo + k) * D + d);
             } else {
                 ml[s] = make_float2(NEG_INF, 0.f);
                 v[s] = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -687,7 +707,7 @@ __global__ void __launch_bounds__(160) flash_decode_tma_kernel(const __grid_cons
         bf16* o = p.out + ((size_t)(q_start + row / G) * p.Hq + hk * G + row % G) * D + d;
         *reinterpret_cast<uint2*>(o) = make_uint2(pack_bf16(acc.x, acc.y), pack_bf16(acc.z, acc.w));
     }
-    cluster_sync_all();                                        // no block leaves while another still reads its result
+    TRACE(5)
 }
 }  // namespace dtma
 

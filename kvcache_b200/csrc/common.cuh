@@ -93,6 +93,10 @@ __device__ __forceinline__ void cluster_sync_all() {
     asm volatile("barrier.cluster.arrive.release.aligned;\n" ::: "memory");
     asm volatile("barrier.cluster.wait.acquire.aligned;\n" ::: "memory");
 }
+// Split form: every block arrives when it starts and waits just before it first touches another block's shared
+// memory - by then the others have long arrived, and all are known to be running.
+__device__ __forceinline__ void cluster_arrive_started() { asm volatile("barrier.cluster.arrive.relaxed.aligned;\n" ::: "memory"); }
+__device__ __forceinline__ void cluster_wait_started() { asm volatile("barrier.cluster.wait.aligned;\n" ::: "memory"); }
 __device__ __forceinline__ uint32_t peer_smem(const void* mine, uint32_t rank) {
     uint32_t out;
     asm volatile("mapa.shared::cluster.u32 %0, %1, %2;\n" : "=r"(out) : "r"((uint32_t)__cvta_generic_to_shared(mine)), "r"(rank));
@@ -102,6 +106,12 @@ __device__ __forceinline__ float2 peer_ld2(uint32_t addr) {
     float2 v;
     asm volatile("ld.shared::cluster.v2.f32 {%0,%1}, [%2];\n" : "=f"(v.x), "=f"(v.y) : "r"(addr));
     return v;
+}
+__device__ __forceinline__ void peer_st4(uint32_t addr, const float4& v) {
+    asm volatile("st.shared::cluster.v4.f32 [%0], {%1,%2,%3,%4};\n" ::"r"(addr), "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w) : "memory");
+}
+__device__ __forceinline__ void peer_st2(uint32_t addr, const float2& v) {
+    asm volatile("st.shared::cluster.v2.f32 [%0], {%1,%2};\n" ::"r"(addr), "f"(v.x), "f"(v.y) : "memory");
 }
 __device__ __forceinline__ float4 peer_ld4(uint32_t addr) {
     float4 v;

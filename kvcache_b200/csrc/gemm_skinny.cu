@@ -50,7 +50,8 @@ __global__ void __launch_bounds__(256) gemm_skinny_kernel(const bf16* __restrict
                                                           const float* __restrict__ bias, TOut* __restrict__ y, int M,
                                                           int N, int K, int x_stride, int ksplit) {
     SKINNY_TRACE(0)
-    extern __shared__ __align__(16) float red[];          // [warps + 1][RT][NT][32 lanes][4]
+    if (ksplit > 1) cluster_arrive_started();
+    extern __shared__ __align__(16) float red[];          // [warps + ksplit][RT][NT][32 lanes][4]
     const int warps = blockDim.x >> 5, warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
     const int rank = blockIdx.x % ksplit;                  // the cluster spans x
     const int n0 = (blockIdx.x / ksplit) * 16 * RT;
@@ -162,31 +163,35 @@ __global__ void __launch_bounds__(256) gemm_skinny_kernel(const bf16* __restrict
 #pragma unroll
         for (int j = 0; j < NT; ++j) mine[(r * NT + j) * 32] = make_float4(acc[r][j][0], acc[r][j][1], acc[r][j][2], acc[r][j][3]);
     __syncthreads();
-    float4* total = reinterpret_cast<float4*>(red) + (size_t)warps * RT * NT * 32;     // this block's sums
+    // With a cluster, block `rank` finishes the fragments idx = rank, rank + ksplit, ...: every block sends its own
+    // sums of those fragments into the finishing block's shared memory (slot `rank` of `recv`), one cluster barrier
+    // makes them visible, and nobody reads another block's memory after it - so a block may leave at once.
+    constexpr int F = RT * NT * 32;
+    float4* recv = reinterpret_cast<float4*>(red) + (size_t)warps * F;                 // [ksplit][F]
     if (ksplit > 1) {
-        for (int idx = threadIdx.x; idx < RT * NT * 32; idx += blockDim.x) {
+        cluster_wait_started();
+        for (int idx = threadIdx.x; idx < F; idx += blockDim.x) {
             float4 s = reinterpret_cast<const float4*>(red)[idx];
             for (int wi = 1; wi < warps; ++wi) {
-                const float4 v = reinterpret_cast<const float4*>(red)[(size_t)wi * RT * NT * 32 + idx];
+                const float4 v = reinterpret_cast<const float4*>(red)[(size_t)wi * F + idx];
                 s.x += v.x; s.y += v.y; s.z += v.z; s.w += v.w;
             }
-            total[idx] = s;
+            peer_st4(peer_smem(recv + (size_t)rank * F + idx, idx % ksplit), s);
         }
         cluster_sync_all();
     }
-    // With a cluster, block `rank` finishes the fragments idx = rank, rank + ksplit, ...
-    for (int idx = threadIdx.x * ksplit + rank; idx < RT * NT * 32; idx += blockDim.x * ksplit) {
+    for (int idx = threadIdx.x * ksplit + rank; idx < F; idx += blockDim.x * ksplit) {
         float4 s;
         if (ksplit > 1) {
-            s = peer_ld4(peer_smem(total + idx, 0));
+            s = recv[idx];
             for (int r = 1; r < ksplit; ++r) {
-                const float4 v = peer_ld4(peer_smem(total + idx, r));
+                const float4 v = recv[(size_t)r * F + idx];
                 s.x += v.x; s.y += v.y; s.z += v.z; s.w += v.w;
             }
         } else {
             s = reinterpret_cast<const float4*>(red)[idx];
             for (int wi = 1; wi < warps; ++wi) {
-                const float4 v = reinterpret_cast<const float4*>(red)[(size_t)wi * RT * NT * 32 + idx];
+                const float4 v = reinterpret_cast<const float4*>(red)[(size_t)wi * F + idx];
                 s.x += v.x; s.y += v.y; s.z += v.z; s.w += v.w;
             }
         }
@@ -213,8 +218,6 @@ __global__ void __launch_bounds__(256) gemm_skinny_kernel(const bf16* __restrict
         }
     }
     SKINNY_TRACE(4)
-    if (ksplit > 1) cluster_sync_all();                    // no block leaves while another still reads its sums
-    SKINNY_TRACE(5)
 }
 
 // How K is split over a cluster and over a block's warps.  It depends on the weight's shape alone - not on the
@@ -244,7 +247,7 @@ bool resident(int N, int K) {
         int device = 0;
         cudaGetDevice(&device);
         cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, device);
-        const size_t smem = (size_t)(s.warps + 1) * RT * NT * 32 * 4 * sizeof(float);
+        const size_t smem = (size_t)(s.warps + s.ksplit) * RT * NT * 32 * 4 * sizeof(float);
         if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&cached, gemm_skinny_kernel<RT, NT, ACT, TOut>, s.warps * 32, smem) != cudaSuccess)
             cached = 1;
     }
@@ -256,7 +259,7 @@ int launch(const bf16* x, const bf16* w, const float* bias, TOut* y, int M, int 
     const int blocks = (N + 16 * RT - 1) / (16 * RT);
     const Split s = choose_split(N, K / 32);
     const int ksplit = s.ksplit, warps = s.warps;
-    const size_t smem = (size_t)(warps + 1) * RT * NT * 32 * 4 * sizeof(float);
+    const size_t smem = (size_t)(warps + ksplit) * RT * NT * 32 * 4 * sizeof(float);
     auto kernel = gemm_skinny_kernel<RT, NT, ACT, TOut>;
     if (smem > 48 * 1024) {
         cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
