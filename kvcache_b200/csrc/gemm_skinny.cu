@@ -61,17 +61,6 @@ __global__ void __launch_bounds__(256) gemm_skinny_kernel(const bf16* __restrict
     const int per_warp = (block_end - block_begin + warps - 1) / warps;
     const int kb_begin = min(block_end, block_begin + warp * per_warp), kb_end = min(block_end, kb_begin + per_warp);
 
-    // Before waiting for the kernel that makes x: pull this warp's slice of the weights (which no kernel
-    // writes) towards L2, so that the predecessor's tail and this kernel's memory latency overlap.
-    {
-        const int slice_bytes = (kb_end - kb_begin) * 64;
-        const int lines = (slice_bytes + 127) / 128;
-        for (int i = lane; i < 16 * RT * lines; i += 32) {
-            const int row = min(N - 1, n0 + i / lines);
-            const char* p = reinterpret_cast<const char*>(w + (size_t)row * K + kb_begin * 32) + (i % lines) * 128;
-            asm volatile("prefetch.global.L2 [%0];" ::"l"(p));
-        }
-    }
     // Row pointers: W rows n0 + 16 r + g and + 8 (clamped; rows beyond N are never stored), x rows 8 j + g.
     const bf16* wrow[RT][2];
 #pragma unroll
@@ -79,10 +68,12 @@ __global__ void __launch_bounds__(256) gemm_skinny_kernel(const bf16* __restrict
         wrow[r][0] = w + (size_t)min(N - 1, n0 + 16 * r + g) * K + 8 * t;
         wrow[r][1] = w + (size_t)min(N - 1, n0 + 16 * r + g + 8) * K + 8 * t;
     }
-    // Two register buffers of U k-blocks each.  The weights of both are requested before the wait for the kernel
-    // that makes x (they do not depend on it); after it, the loads of the next U are issued before the products
-    // of the current U, so that a warp's share of K costs one trip to memory plus its streaming.
+    // NBUF register buffers of U k-blocks each.  The weights of all of them are requested before the wait for the
+    // kernel that makes x (they do not depend on it); after it, a buffer is refilled as soon as its products are
+    // issued, so that a warp's share of K costs one trip to memory plus its streaming.  (An L2 prefetch of the rest
+    // of the share was measured slower than none.)
     constexpr int U = (RT * NT >= 4) ? 1 : 2;
+    constexpr int NBUF = (RT * NT == 1) ? 3 : 2;        // measured: three beat two and four for the narrowest tiles
     auto load_w = [&](uint4 (&a)[U][RT][2], int kb) {
 #pragma unroll
         for (int u = 0; u < U; ++u) {
@@ -95,9 +86,10 @@ __global__ void __launch_bounds__(256) gemm_skinny_kernel(const bf16* __restrict
             }
         }
     };
-    uint4 a0[U][RT][2], b0[U][NT], a1[U][RT][2], b1[U][NT];
-    if (kb_begin < kb_end) load_w(a0, kb_begin);
-    if (kb_begin + U < kb_end) load_w(a1, kb_begin + U);
+    uint4 a[NBUF][U][RT][2], bx[NBUF][U][NT];
+#pragma unroll
+    for (int nb = 0; nb < NBUF; ++nb)
+        if (kb_begin + nb * U < kb_end) load_w(a[nb], kb_begin + nb * U);
     SKINNY_TRACE(1)
     pdl_wait();
     pdl_launch_dependents();
@@ -142,17 +134,18 @@ __global__ void __launch_bounds__(256) gemm_skinny_kernel(const bf16* __restrict
                     mma_bf16(acc[r][j], a[u][r][0].z, a[u][r][1].z, a[u][r][0].w, a[u][r][1].w, b[u][j].z, b[u][j].w);
                 }
     };
-    int kb = kb_begin;
-    if (kb < kb_end) load_x(b0, kb);
-    if (kb + U < kb_end) load_x(b1, kb + U);
-    while (kb < kb_end) {
-        multiply(a0, b0);
-        kb += U;
-        if (kb >= kb_end) break;
-        if (kb + U < kb_end) { load_w(a0, kb + U); load_x(b0, kb + U); }
-        multiply(a1, b1);
-        kb += U;
-        if (kb + U < kb_end) { load_w(a1, kb + U); load_x(b1, kb + U); }
+#pragma unroll
+    for (int nb = 0; nb < NBUF; ++nb)
+        if (kb_begin + nb * U < kb_end) load_x(bx[nb], kb_begin + nb * U);
+    for (int base = kb_begin; base < kb_end; base += NBUF * U) {
+#pragma unroll
+        for (int nb = 0; nb < NBUF; ++nb) {
+            const int kb = base + nb * U;
+            if (kb < kb_end) {
+                multiply(a[nb], bx[nb]);
+                if (kb + NBUF * U < kb_end) { load_w(a[nb], kb + NBUF * U); load_x(bx[nb], kb + NBUF * U); }
+            }
+        }
     }
 
     SKINNY_TRACE(3)
