@@ -40,13 +40,13 @@ __global__ void sample_stage1_kernel(const float* __restrict__ logits, int V, co
                                      float* __restrict__ part_val, int* __restrict__ part_idx, int parts) {
     pdl_wait();
     pdl_launch_dependents();
-    __shared__ float sv[256];
-    __shared__ int si[256];
+    __shared__ float sv[32];
+    __shared__ int si[32];
     const int row = blockIdx.y, part = blockIdx.x;
     const float temp = temperature[row];
     const float* lr = logits + (size_t)row * V;
-    const int per = (V + parts - 1) / parts;
-    const int begin = part * per, end = min(V, begin + per);
+    const int per = ((V + parts - 1) / parts + 3) & ~3;          // a multiple of four: parts start on 16-byte boundaries
+    const int begin = min(V, part * per), end = min(V, begin + per);
     float bv = -FLT_MAX; int bi = 0x7fffffff;
     if (temp > 0.f) {
         const unsigned long long seed = seeds[row];
@@ -58,19 +58,52 @@ __global__ void sample_stage1_kernel(const float* __restrict__ logits, int V, co
             philox4x32_10((uint32_t)i, ctr, 0u, 0u, k0, k1, rnd);
             better(bv, bi, lr[i] * inv_t + gumbel_from_bits(rnd[0]), i);
         }
+    } else if ((((uintptr_t)lr | (uintptr_t)begin * 4) & 15) == 0) {
+        // Greedy: four logits a load, four loads in flight; `better` is a total order (value, then lowest index), so
+        // the order in which candidates meet does not matter.
+        const int vec_end = begin + ((end - begin) & ~3);
+        for (int i0 = begin + threadIdx.x * 4; i0 < vec_end; i0 += blockDim.x * 16) {
+            float4 v[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const int i = i0 + u * blockDim.x * 4;
+                v[u] = i < vec_end ? *reinterpret_cast<const float4*>(lr + i) : make_float4(-FLT_MAX, -FLT_MAX, -FLT_MAX, -FLT_MAX);
+            }
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const int i = i0 + u * blockDim.x * 4;
+                if (i < vec_end) {
+                    better(bv, bi, v[u].x, i); better(bv, bi, v[u].y, i + 1);
+                    better(bv, bi, v[u].z, i + 2); better(bv, bi, v[u].w, i + 3);
+                }
+            }
+        }
+        for (int i = vec_end + threadIdx.x; i < end; i += blockDim.x) better(bv, bi, lr[i], i);
     } else {
         for (int i = begin + threadIdx.x; i < end; i += blockDim.x) better(bv, bi, lr[i], i);
     }
-    sv[threadIdx.x] = bv; si[threadIdx.x] = bi;
-    __syncthreads();
-    for (int s = blockDim.x >> 1; s > 0; s >>= 1) {
-        if (threadIdx.x < s) {
-            float v = sv[threadIdx.x]; int i = si[threadIdx.x];
-            better(v, i, sv[threadIdx.x + s], si[threadIdx.x + s]);
-            sv[threadIdx.x] = v; si[threadIdx.x] = i;
-        }
-        __syncthreads();
+    // The block's best: within each warp by shuffles, then over the warps.
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+        better(bv, bi, ov, oi);
     }
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
+    if (lane == 0) { sv[warp] = bv; si[warp] = bi; }
+    __syncthreads();
+    if (warp == 0) {
+        bv = lane < nwarps ? sv[lane] : -FLT_MAX;
+        bi = lane < nwarps ? si[lane] : 0x7fffffff;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+            const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+            better(bv, bi, ov, oi);
+        }
+        if (lane == 0) { sv[0] = bv; si[0] = bi; }
+    }
+    __syncthreads();
     if (threadIdx.x == 0) { part_val[row * parts + part] = sv[0]; part_idx[row * parts + part] = si[0]; }
 }
 

@@ -355,7 +355,8 @@ class CudaKernels(KernelSet):
                     if self.decode_merge == "tma" and D % 64 == 0 and 8 <= kv.page_size <= 64:
                         _check(lib.kvb_flash_decode_tma(
                             _ptr(q), _ptr(out), _ptr(kv.k_pages), _ptr(kv.v_pages), kv.k_pages.shape[0],
-                            _ptr(kv.block_table), kv.block_table.shape[1], _ptr(batch.decode_items), n,
+                            _ptr(kv.block_table), kv.block_table.shape[1],
+                            _ptr(None if n == batch.num_segments else batch.decode_items), n,   # every segment, in order: no list
                             _ptr(batch.seg_q_start), _ptr(batch.seg_q_len), _ptr(batch.seg_kv_len), num_heads, Hkv,
                             kv.page_size, spec.window or 0, nsplit, float(scale), _ptr(self.error_word), self._stream()),
                             "flash_decode_tma")
