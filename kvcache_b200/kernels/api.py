@@ -182,8 +182,10 @@ class CudaKernels(KernelSet):
         self._flash: Dict[int, _Library] = {}
         self._attn_tc: Dict[int, _Library] = {}
         # Portions of prompts with at least this many rows go through the tensor-memory attention kernel
-        # (bfloat16, head size 64 or 128, pages of 8..64 tokens); None turns it off.
-        self.tc_attention_min_rows: Optional[int] = 64
+        # (bfloat16, head size 64 or 128, pages of 8..64 tokens); None turns it off.  Measured on 24 layers of the
+        # 0.5B shape: the mma.sync kernel is ahead at 128 and 256 rows (1.09 / 1.24 ms a step against 1.14 / 1.28),
+        # the tensor-memory kernel from 512 rows on (1.56 against 1.69 ms).
+        self.tc_attention_min_rows: Optional[int] = 384
         self.flash_attention = True          # bfloat16, head sizes 16..128: tensor-core kernels
         # Decode attention splits the keys of a request over blocks.  "cluster": the splits (at most 8) are a
         # thread-block cluster and merge through distributed shared memory; "tma": the same with keys and values

@@ -87,6 +87,25 @@ def test_portions_replayed_from_graphs_equal_eager_launches(tmp_path, kernels, d
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
+def test_head_size_64_long_prompt_and_decoding(tmp_path, kernels, dtype):
+    """Configuration D has the head size of the benchmarked model (64; seven query heads on one kv head; its second
+    layer windowed), so in bfloat16 a prompt of 700 tokens goes through the tensor-memory prefill kernel and
+    decoding through the TMA decode kernel - whole, in portions of which the first is long, and with the last
+    32 tokens one by one - against the plain implementation."""
+    runner, config, weights = _runner(tmp_path, kernels, "D", dtype, num_pages=96, max_tokens_per_step=1024,
+                                      max_tokens_per_request=1024)
+    tokens = random_tokens(config["vocab_size"], 700, 21)
+    want = logits_of(config, weights, tokens)
+    assert_close(replay_modes.whole(runner, tokens), want, REL[dtype], "whole")
+    assert_close(replay_modes.portions(runner, tokens, [450, 2, 130, 118]), want, REL[dtype], "portions")
+    assert_close(replay_modes.last_32_one_by_one(runner, tokens), want[-33:], REL[dtype], "last 32 one by one")
+    kernels.check_errors()
+    if dtype == "bfloat16":                                  # the kernels this test is about were the ones that ran
+        assert kernels._attn_tc[64]._lib is not None and kernels._flash[64]._lib is not None
+        assert kernels.decode_merge == "tma" and kernels.tc_attention_min_rows <= 450
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("name", NAMES)
 def test_mixed_with_page_reuse(tmp_path, kernels, name, dtype):
     page = PAGE_SIZE[name]

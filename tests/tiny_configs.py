@@ -26,8 +26,15 @@ TINY_C = {  # sizes that are no power of two anywhere; windowed upper layers; he
     "tie_word_embeddings": False, "max_position_embeddings": 768, "hidden_act": "silu",
     "use_sliding_window": True, "sliding_window": 40, "max_window_layers": 1, "initializer_range": 0.05,
 }
-PAGE_SIZE = {"A": 16, "B": 8, "C": 16}
-CONFIGS = {"A": TINY_A, "B": TINY_B, "C": TINY_C}
+TINY_D = {  # head size 64, the size of the benchmarked model: the TMA decode and tensor-memory prefill kernels; group of 7
+    "architectures": ["Qwen2ForCausalLM"], "model_type": "qwen2",
+    "hidden_size": 112, "num_hidden_layers": 2, "num_attention_heads": 7, "num_key_value_heads": 1,
+    "head_dim": 64, "intermediate_size": 136, "vocab_size": 270, "rms_norm_eps": 1e-6, "rope_theta": 1000000.0,
+    "tie_word_embeddings": True, "max_position_embeddings": 2048, "hidden_act": "silu",
+    "use_sliding_window": True, "sliding_window": 300, "max_window_layers": 1,
+}
+PAGE_SIZE = {"A": 16, "B": 8, "C": 16, "D": 32}
+CONFIGS = {"A": TINY_A, "B": TINY_B, "C": TINY_C, "D": TINY_D}
 
 
 def make_model_folder(tmp_path, name: str, seed: int = 0, dtype=torch.float32) -> str:
