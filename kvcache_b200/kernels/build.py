@@ -36,6 +36,7 @@ MODULES: Dict[str, dict] = {
     # Compiled per head size: variant "d<head_dim>" with -DKVB_HEAD_DIM=<head_dim>.
     "attention_flash": {"src": "attention_flash.cu", "deps": ["common.cuh", "flash_core.cuh", "no_alloc.h", "tc_common.cuh"]},
     "attention_tc": {"src": "attention_tc.cu", "deps": ["common.cuh", "tc_common.cuh"]},
+    "gemm_wstream": {"src": "gemm_wstream.cu", "deps": ["common.cuh", "tc_common.cuh"]},
 }
 # Variants that `build_all` makes for modules compiled per size.
 DEFAULT_VARIANTS = {"attention_flash": [("d64", ["-DKVB_HEAD_DIM=64"]), ("d128", ["-DKVB_HEAD_DIM=128"])],

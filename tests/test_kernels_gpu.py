@@ -174,6 +174,56 @@ TC_SHAPES = [(128, 128, 64), (128, 128, 128), (2048, 1152, 896), (300, 896, 4864
              (2048, 9728, 896), (2100, 9800, 904), (4096, 5000, 136)]        # enough 256 x 256 tiles for two SMs per tile
 
 
+@pytest.mark.parametrize("M,N,K", [(17, 1152, 896), (64, 896, 4864), (100, 896, 896), (128, 1000, 320), (33, 331, 120),
+                                   (40, 136, 72), (128, 200, 64), (31, 9728, 896), (65, 2560, 128)])
+def test_gemm_wstream(kernels, request, M, N, K):
+    """The weight-streaming tensor-memory product (17..128 rows) against float64 on the same bfloat16 inputs: K over
+    a cluster of 1, 2, 4, 8 blocks, ragged N and K, every padded row count."""
+    g = torch.Generator().manual_seed(31)
+    x = torch.randn(M, K, generator=g).to(torch.bfloat16)
+    w = torch.randn(N, K, generator=g).to(torch.bfloat16)
+    bias = torch.randn(N, generator=g)
+    saved = kernels.WSTREAM_MAX_ROWS
+    kernels.WSTREAM_MAX_ROWS = 128                        # the kernel takes up to 128 rows; the engine gives it fewer
+    request.addfinalizer(lambda: setattr(kernels, "WSTREAM_MAX_ROWS", saved))
+    assert kernels._wstream(torch.bfloat16, M, K) and not kernels._skinny(torch.bfloat16, M, K)
+    xd, wd = x.to(DEV), w.to(DEV)
+    for out_dtype in (torch.bfloat16, torch.float32):
+        for b in (None, bias):
+            out = torch.full((M, N), float("nan"), dtype=out_dtype, device=DEV)
+            kernels.linear(xd, wd, out, b.to(DEV) if b is not None else None)
+            kernels.check_errors()
+            want = x.double() @ w.double().t() + (b.double() if b is not None else 0)
+            assert_close(out, want, REL[out_dtype])
+    # Rows do not depend on how many rows there are beside them.
+    full = torch.empty(M, N, dtype=torch.bfloat16, device=DEV)
+    kernels.linear(xd, wd, full)
+    part = torch.empty(17, N, dtype=torch.bfloat16, device=DEV)
+    kernels.linear(xd[:17].contiguous(), wd, part)
+    assert torch.equal(part, full[:17])
+
+
+@pytest.mark.parametrize("M,I,K", [(17, 64, 64), (64, 4864, 896), (128, 200, 120), (50, 4872, 200)])
+def test_gemm_wstream_gated(kernels, request, M, I, K):
+    from kvcache_b200.engine.workspace import Workspace
+    from kvcache_b200.parts.feedforward import GatedMLP
+    saved = kernels.WSTREAM_MAX_ROWS
+    kernels.WSTREAM_MAX_ROWS = 128
+    request.addfinalizer(lambda: setattr(kernels, "WSTREAM_MAX_ROWS", saved))
+    g = torch.Generator().manual_seed(32)
+    x = torch.randn(M, K, generator=g).to(torch.bfloat16)
+    wg, wu = (torch.randn(I, K, generator=g) * 0.2).to(torch.bfloat16), (torch.randn(I, K, generator=g) * 0.2).to(torch.bfloat16)
+    gate, up = x.double() @ wg.double().t(), x.double() @ wu.double().t()
+    want = gate / (1 + torch.exp(-gate)) * up
+    ffn = GatedMLP(K, I, activation="silu", prefix="m.", dtype="bfloat16")
+    ffn.bind({"m.gate_proj.weight": wg, "m.up_proj.weight": wu, "m.down_proj.weight": torch.zeros(K, I)}, torch.device(DEV))
+    assert ffn.interleaved and kernels._wstream(torch.bfloat16, M, K)
+    out = torch.full((M, I), float("nan"), dtype=torch.bfloat16, device=DEV)
+    kernels.gate_up_act(x.to(DEV), ffn.w_gate_up, out, Workspace(DEV), ffn.interleaved)
+    kernels.check_errors()
+    assert_close(out, want, 1e-2)
+
+
 @pytest.mark.parametrize("M,N,K", TC_SHAPES)
 def test_gemm_tcgen05(M, N, K):
     """The tensor-memory kernel against float64 on the same bfloat16 inputs: whole tiles, ragged edges in M, N
