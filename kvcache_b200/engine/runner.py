@@ -16,6 +16,8 @@ lies in the metadata buffer at fixed addresses.
 """
 from __future__ import annotations
 
+import contextlib
+
 from dataclasses import dataclass
 from typing import Dict, List, Optional, Sequence, Tuple
 
@@ -277,8 +279,10 @@ class ModelRunner:
         return tokens
 
     def _forward(self, batch, view, layout, workspace, sample: bool):
-        logits = self.model.forward(batch, self.kernels, workspace, view)
-        tokens = self._sample(logits, layout, workspace) if sample and batch.num_wanted else None
+        scope = getattr(self.kernels, "on_current_stream", None)
+        with (scope() if scope is not None else contextlib.nullcontext()):
+            logits = self.model.forward(batch, self.kernels, workspace, view)
+            tokens = self._sample(logits, layout, workspace) if sample and batch.num_wanted else None
         return logits, tokens
 
     MAX_GRAPHS = 32

@@ -16,10 +16,15 @@ class Workspace:
         self.device = torch.device(device)
         self.row_capacity = row_capacity
         self._buffers: Dict[str, torch.Tensor] = {}
+        self._views: Dict[tuple, torch.Tensor] = {}      # (name, shape, dtype) -> the view handed out last time
         self.moved = 0        # how many times an existing buffer was replaced by a larger one
         self.frozen = False   # set while a CUDA graph is captured or replayed: growing is an error
 
     def buffer(self, name: str, shape: Tuple[int, ...], dtype: torch.dtype) -> torch.Tensor:
+        key = (name, tuple(shape), dtype)
+        view = self._views.get(key)
+        if view is not None:
+            return view                                  # the same request as before: nothing to compute or to slice
         count = 1
         for s in shape:
             count *= int(s)
@@ -37,7 +42,11 @@ class Workspace:
                 self.moved += 1
             buf = torch.empty(capacity, dtype=dtype, device=self.device)
             self._buffers[name] = buf
-        return buf[:count].view(shape)
+            for old in [k for k in self._views if k[0] == name]:
+                del self._views[old]                     # views of the buffer that was replaced
+        view = buf[:count].view(shape)
+        self._views[key] = view
+        return view
 
     def zeros(self, name: str, shape: Tuple[int, ...], dtype: torch.dtype) -> torch.Tensor:
         """Like `buffer`, but zero when first made (or remade); its users leave it zero."""

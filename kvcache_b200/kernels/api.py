@@ -8,6 +8,7 @@ package; `CudaKernels` raises if the device or the compiler is missing.
 """
 from __future__ import annotations
 
+import contextlib
 import ctypes
 from typing import Dict, Optional, Sequence
 
@@ -203,10 +204,23 @@ class CudaKernels(KernelSet):
         self.sm_count = torch.cuda.get_device_properties(self.device).multi_processor_count
         self.error_word = torch.zeros(1, dtype=torch.int32, device=self.device)
         self.launches = 0
+        self._pinned_stream: Optional[_c_void_p] = None
 
     # ---- helpers -----------------------------------------------------------
     def _stream(self) -> _c_void_p:
+        if self._pinned_stream is not None:
+            return self._pinned_stream
         return _c_void_p(torch.cuda.current_stream(self.device).cuda_stream)
+
+    @contextlib.contextmanager
+    def on_current_stream(self):
+        """Within the block every launch goes to the stream that is current now (asked for once, not per launch)."""
+        saved = self._pinned_stream
+        self._pinned_stream = _c_void_p(torch.cuda.current_stream(self.device).cuda_stream)
+        try:
+            yield
+        finally:
+            self._pinned_stream = saved
 
     def check_errors(self) -> None:
         word = int(self.error_word.item())
