@@ -199,6 +199,7 @@ class CudaKernels(KernelSet):
         # "ticket": up to 32 splits leave partial results in scratch and the last one to finish merges them.
         self.decode_merge = "tma"
         self.decode_cluster_max = 8          # the kernel's limit
+        self.decode_pow2_splits = True
         self.decode_ctas_wanted = 148 * 2    # the split over the keys aims at this many blocks in flight
         self.decode_min_tiles = 4            # ... but gives a split at least this many 64-key tiles
         self.sm_count = torch.cuda.get_device_properties(self.device).multi_processor_count
@@ -386,6 +387,8 @@ class CudaKernels(KernelSet):
                 if self.decode_merge in ("cluster", "tma"):
                     nsplit = max(1, min(self.decode_cluster_max, self.decode_ctas_wanted // (n * Hkv),
                                         tiles // self.decode_min_tiles))
+                    if self.decode_pow2_splits:
+                        nsplit = 1 << (nsplit.bit_length() - 1)     # clusters of 3, 5, 6, 7 blocks place badly
                     self.launches += 1
                     if self.decode_merge == "tma" and D % 64 == 0 and 8 <= kv.page_size <= 64:
                         _check(lib.kvb_flash_decode_tma(
