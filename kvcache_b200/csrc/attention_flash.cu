@@ -711,6 +711,28 @@ __global__ void __launch_bounds__(160) flash_decode_tma_kernel(const __grid_cons
 }
 }  // namespace dtma
 
+// How many clusters of `nsplit` blocks of the TMA decode kernel the GPU holds at once (0 on an error): a grid with more
+// clusters than that runs in waves, which costs a whole kernel's latency again.
+KVB_API int kvb_flash_decode_tma_max_clusters(int nsplit) {
+    using namespace dtma;
+    if (nsplit < 1 || nsplit > MAX_CLUSTER) return 0;
+    if (cudaFuncSetAttribute(flash_decode_tma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES) != cudaSuccess) return 0;
+    cudaLaunchConfig_t config = {};
+    config.gridDim = dim3(nsplit * 64);
+    config.blockDim = dim3(160);
+    config.dynamicSmemBytes = SMEM_BYTES;
+    cudaLaunchAttribute attribute[1];
+    attribute[0].id = cudaLaunchAttributeClusterDimension;
+    attribute[0].val.clusterDim.x = nsplit;
+    attribute[0].val.clusterDim.y = 1;
+    attribute[0].val.clusterDim.z = 1;
+    config.attrs = attribute;
+    config.numAttrs = 1;
+    int clusters = 0;
+    if (cudaOccupancyMaxActiveClusters(&clusters, flash_decode_tma_kernel, &config) != cudaSuccess) return 0;
+    return clusters;
+}
+
 // The splits as a cluster, keys and values by TMA: nsplit 1..8, page_size a power of two 8..64, num_pages the pool's
 // page count, err the device error word.
 KVB_API int kvb_flash_decode_tma(const void* q, void* out, const void* k_pages, const void* v_pages, int num_pages,

@@ -65,12 +65,19 @@ gemm_wstream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
     const int my_kblocks = rank < kblocks ? (kblocks - rank + ksplit - 1) / ksplit : 0;   // K blocks rank, rank + ksplit, ...
     if (ksplit > 1) cluster_arrive_started();
 
+    // The first thread makes the barriers and at once sends for the first stages' W tiles - they depend neither on
+    // the kernel before this one nor on the tensor memory that warp 1 allocates meanwhile.
+    const int early = my_kblocks < STAGES ? my_kblocks : STAGES;
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) { mbar_init(&sh.full[s], 1); mbar_init(&sh.empty[s], 1); }
         mbar_init(&sh.accum_full, 1);
         sh.failed = 0;
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+        for (int i = 0; i < early; ++i) {
+            mbar_expect_tx(&sh.full[i], STAGE_BYTES);                          // W and x tile of the stage
+            tma_load_2d(tiles + i * STAGE_BYTES, &map_w, (rank + i * ksplit) * BK, n0, &sh.full[i]);
+        }
     }
     if (warp == 1) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_u32(&sh.tmem_base)), "r"(MB) : "memory");
@@ -83,15 +90,6 @@ gemm_wstream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
 
     if (warp == 0) {
         if (lane == 0) {
-            asm volatile("prefetch.tensormap [%0];\n" ::"l"(&map_w) : "memory");
-            asm volatile("prefetch.tensormap [%0];\n" ::"l"(&map_x) : "memory");
-            // The weights do not depend on the kernel before this one: the first stages' W tiles go out before the
-            // wait, the x tiles after it.  Both count towards the same "full" barrier of their stage.
-            const int early = my_kblocks < STAGES ? my_kblocks : STAGES;
-            for (int i = 0; i < early; ++i) {
-                mbar_expect_tx(&sh.full[i], STAGE_BYTES);
-                tma_load_2d(tiles + i * STAGE_BYTES, &map_w, (rank + i * ksplit) * BK, n0, &sh.full[i]);
-            }
             pdl_wait();
             for (int i = 0; i < early; ++i)
                 tma_load_2d(tiles + i * STAGE_BYTES + W_BYTES, &map_x, (rank + i * ksplit) * BK, 0, &sh.full[i]);

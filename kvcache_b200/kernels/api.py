@@ -113,6 +113,7 @@ _SIGNATURES = {
         "kvb_flash_decode_cluster": [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_int,
                                      _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float,
                                      _c_void_p],
+        "kvb_flash_decode_tma_max_clusters": [_c_int],
         "kvb_flash_decode_tma": [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_int, _c_void_p, _c_int,
                                  _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float,
                                  _c_void_p, _c_void_p],
@@ -132,7 +133,7 @@ _SIGNATURES = {
 }
 
 
-_OPTIONAL = {"kvb_flash_decode_tma"}      # only in attention_flash variants for head sizes 64 and 128
+_OPTIONAL = {"kvb_flash_decode_tma", "kvb_flash_decode_tma_max_clusters"}      # only in attention_flash variants for head sizes 64 and 128
 
 
 class _Library:
@@ -206,6 +207,7 @@ class CudaKernels(KernelSet):
         self.error_word = torch.zeros(1, dtype=torch.int32, device=self.device)
         self.launches = 0
         self._pinned_stream: Optional[_c_void_p] = None
+        self._tma_cluster_capacity: Dict[tuple, int] = {}
 
     # ---- helpers -----------------------------------------------------------
     def _stream(self) -> _c_void_p:
@@ -340,6 +342,14 @@ class CudaKernels(KernelSet):
             _ptr(kv.k_pages), _ptr(kv.v_pages), _ptr(q_out), T, num_heads, spec.num_kv_heads, spec.head_dim,
             kv.page_size, 1 if kv.writes else 0, _ptr(self.error_word), self._stream()), "qkv_rope_append")
 
+    def _tma_clusters(self, lib, head_dim: int, nsplit: int) -> int:
+        key = (head_dim, nsplit)
+        found = self._tma_cluster_capacity.get(key)
+        if found is None:
+            found = int(lib.kvb_flash_decode_tma_max_clusters(nsplit)) or 1 << 30     # unknown: no limit
+            self._tma_cluster_capacity[key] = found
+        return found
+
     def _flash_library(self, head_dim: int) -> _Library:
         lib = self._flash.get(head_dim)
         if lib is None:
@@ -391,6 +401,9 @@ class CudaKernels(KernelSet):
                         nsplit = 1 << (nsplit.bit_length() - 1)     # clusters of 3, 5, 6, 7 blocks place badly
                     self.launches += 1
                     if self.decode_merge == "tma" and D % 64 == 0 and 8 <= kv.page_size <= 64:
+                        # All clusters at once: a grid with more clusters than the GPU holds runs in waves.
+                        while nsplit > 1 and n * Hkv > self._tma_clusters(lib, D, nsplit):
+                            nsplit //= 2
                         _check(lib.kvb_flash_decode_tma(
                             _ptr(q), _ptr(out), _ptr(kv.k_pages), _ptr(kv.v_pages), kv.k_pages.shape[0],
                             _ptr(kv.block_table), kv.block_table.shape[1],
