@@ -100,6 +100,9 @@ __global__ void qkv_rope_append_vec8_kernel(const bf16* __restrict__ qkv, const 
                                             int table_stride, bf16* __restrict__ k_pages, bf16* __restrict__ v_pages,
                                             bf16* __restrict__ q_out, int Hq, int Hkv, int D, int page_size, int write_kv,
                                             int* __restrict__ err) {
+    // This kernel is a few small blocks: it lets its successor (attention, which fetches block tables and old keys
+    // before its own wait) onto the SMs at once, while the product before this kernel may still be running.
+    pdl_launch_dependents();
     const int r = blockIdx.x;
     const int width = (Hq + 2 * Hkv) * D;
     const int pos = positions[r];
@@ -124,7 +127,6 @@ __global__ void qkv_rope_append_vec8_kernel(const bf16* __restrict__ qkv, const 
     ChunkTables tab;
     if ((int)threadIdx.x < chunks) chunk_tables(tab, threadIdx.x, chunks_per_head, D, Hq, Hkv, rot_half, cr, sr, bias);
     pdl_wait();
-    pdl_launch_dependents();
     const bf16* src = qkv + (size_t)r * width;
     for (int c = threadIdx.x; c < chunks; c += blockDim.x) {
         if (c != (int)threadIdx.x) chunk_tables(tab, c, chunks_per_head, D, Hq, Hkv, rot_half, cr, sr, bias);
