@@ -1,5 +1,6 @@
-"""A toy architecture defined here, in the test: a mixer with per-request state of its own, another position
-encoding, a layer of each kind - registered, built from a folder and stepped with no change to the framework."""
+"""A toy architecture defined here, in the test: a mixer with per-request state of its own, a feed-forward that
+routes every row to one of several experts, another position encoding, a layer of each kind - registered, built
+from a folder and stepped with no change to the framework."""
 import json
 import os
 from dataclasses import dataclass
@@ -16,8 +17,8 @@ DEV = "cuda:0"
 
 def _define():
     from kvcache_b200.config.base import KeyReader, ModelConfig
-    from kvcache_b200.parts import (DecoderModel, GatedMLP, GQAAttention, LayerCall, Mixer, PositionEncoding, PreNormBlock,
-                                    RMSNorm, StateSpec)
+    from kvcache_b200.parts import (DecoderModel, FeedForward, GatedMLP, GQAAttention, LayerCall, Mixer, PositionEncoding,
+                                    PreNormBlock, RMSNorm, StateSpec)
     from kvcache_b200.weights import TensorSpec
 
     @dataclass(frozen=True)
@@ -67,6 +68,37 @@ def _define():
                     out[r] = (self.w @ s).to(x.dtype)
             return out
 
+    class TopOneExperts(FeedForward):
+        """delta[r] = p_e * Wout_e relu(Win_e x[r]) with e = argmax of the router's logits (float32) and p_e its
+        softmax weight: a feed-forward with routing, its sizes (experts, inner width) given as parameters."""
+
+        def __init__(self, width, inner, experts, prefix, dtype):
+            self.width, self.inner, self.experts, self.prefix, self.dtype = width, inner, experts, prefix, dtype
+            self.router = self.w_in = self.w_out = None
+
+        def tensor_specs(self):
+            p = self.prefix
+            return {p + "router.weight": TensorSpec((self.experts, self.width)),
+                    p + "in.weight": TensorSpec((self.experts, self.inner, self.width)),
+                    p + "out.weight": TensorSpec((self.experts, self.width, self.inner))}
+
+        def bind(self, tensors: Mapping[str, torch.Tensor], device):
+            p = self.prefix
+            self.router = tensors[p + "router.weight"].to(torch.float32).to(device)
+            self.w_in = tensors[p + "in.weight"].to(torch.float32).to(device)
+            self.w_out = tensors[p + "out.weight"].to(torch.float32).to(device)
+
+        def forward(self, x, ctx):
+            xf = x.float()
+            prob = torch.softmax(xf @ self.router.t(), dim=-1)
+            chosen = prob.argmax(dim=-1)
+            out = torch.empty_like(xf)
+            for e in range(self.experts):
+                rows = (chosen == e).nonzero().flatten()
+                if len(rows):
+                    out[rows] = prob[rows, e, None] * (torch.relu(xf[rows] @ self.w_in[e].t()) @ self.w_out[e].t())
+            return out.to(x.dtype)
+
     class AddedSinusoid(PositionEncoding):
         """Adds sin(pos / 10) to every element of the embedded row: an encoding that acts at the embedding."""
 
@@ -81,7 +113,7 @@ def _define():
             PreNormBlock(c.width, RMSNorm(c.width, c.eps, "l1.n1"),
                          GQAAttention(c.width, 2, 1, c.width // 2, qkv_bias=False, out_bias=False, position=None, window=None,
                                       prefix="l1.a.", dtype=dtype),
-                         RMSNorm(c.width, c.eps, "l1.n2"), GatedMLP(c.width, c.inner, activation="silu", prefix="l1.f.", dtype=dtype), dtype),
+                         RMSNorm(c.width, c.eps, "l1.n2"), TopOneExperts(c.width, c.inner, 3, "l1.moe.", dtype), dtype),
         ]
         return DecoderModel(config=c, dtype=dtype, vocab_size=c.vocab, width=c.width, embed_name="emb", head_name=None,
                             blocks=blocks, schedule=[LayerCall(0, 0), LayerCall(1, 1)],
@@ -110,8 +142,13 @@ def _plain(config, w, tokens):
     k = plain.linear(n, W["l1.a.k_proj.weight"]).view(T, 1, D)
     v = plain.linear(n, W["l1.a.v_proj.weight"]).view(T, 1, D)
     x = x + plain.linear(plain.attention(q, k, v).reshape(T, 2 * D), W["l1.a.o_proj.weight"])
-    x = x + plain.swiglu(plain.rms_norm(x, W["l1.n2"], config["eps"]), W["l1.f.gate_proj.weight"], W["l1.f.up_proj.weight"],
-                         W["l1.f.down_proj.weight"])
+    n = plain.rms_norm(x, W["l1.n2"], config["eps"])
+    prob = torch.softmax(n @ W["l1.moe.router.weight"].t(), dim=-1)
+    routed = []
+    for r in range(T):
+        e = int(prob[r].argmax())
+        routed.append(prob[r, e] * (W["l1.moe.out.weight"][e] @ torch.relu(W["l1.moe.in.weight"][e] @ n[r])))
+    x = x + torch.stack(routed)
     return plain.linear(plain.rms_norm(x, W["final"], config["eps"]), W["emb"])
 
 
