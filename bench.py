@@ -155,7 +155,7 @@ def time_decode(folder, batch, context, steps, warmup, use_graphs=True, sampler=
     return result
 
 
-def time_prefill(folder, tokens, layers_total, repeats=3):
+def time_prefill(folder, tokens, layers_total, repeats=3, warm=5):
     import torch
     from kvcache_b200.config.options import EngineOptions
     from kvcache_b200.engine.core import EngineCore
@@ -165,7 +165,7 @@ def time_prefill(folder, tokens, layers_total, repeats=3):
     core = EngineCore(folder, options)
     ids = torch.randint(0, core.model.vocab_size, (tokens,), generator=torch.Generator().manual_seed(3)).tolist()
     times = []
-    for i in range(repeats + 1):
+    for i in range(warm + repeats):                  # the step is replayed from a graph once its shape has come a few times
         slot = core.cache.admit()
         torch.cuda.synchronize()
         begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -174,7 +174,7 @@ def time_prefill(folder, tokens, layers_total, repeats=3):
         end.record()
         torch.cuda.synchronize()
         core.cache.release(slot)
-        if i > 0:
+        if i >= warm:
             times.append(begin.elapsed_time(end))
     core.kernels.check_errors()
     c = core.config

@@ -136,11 +136,13 @@ class ModelRunner:
         self._meta_device = torch.zeros(capacity, dtype=torch.int32, device=self.device)
         self._on_cuda = self.device.type == "cuda"
         self.use_graphs = use_graphs and self._on_cuda
+        self.split_mixed_steps = True     # see _split
         ring = 4 if self._on_cuda else 1
         self._staging = [torch.zeros(capacity, dtype=torch.int32, pin_memory=self._on_cuda) for _ in range(ring)]
         self._staging_events = [None] * ring
         self._ring = 0
         self._graphs: Dict[int, _DecodeGraph] = {}
+        self._portion_shapes_seen: Dict[tuple, int] = {}
         self._sample_parts = None       # asked of the sampling module when a step first samples
         # Tokens the last sampling step chose, in the order of its wanted places.  The next step may take its
         # input ids from here (StepEntry.token_from_last) without the host ever seeing them.
@@ -264,30 +266,30 @@ class ModelRunner:
         return batch, view, layout
 
     # ---- the step ----------------------------------------------------------
-    def _sample(self, logits: torch.Tensor, layout: StepLayout, workspace: Workspace) -> torch.Tensor:
+    def _sample(self, logits: torch.Tensor, layout: StepLayout, workspace: Workspace, token_offset: int = 0) -> torch.Tensor:
         R = logits.shape[0]
         dev = self._meta_device
         if self._sample_parts is None:
             self._sample_parts = self.kernels.sample_parts(self.model.vocab_size)
-        if R > self.last_tokens.shape[0]:
-            raise ValueError(f"{R} places to sample in one step; the runner was made for {self.last_tokens.shape[0]}")
-        tokens = self.last_tokens[:R]
+        if token_offset + R > self.last_tokens.shape[0]:
+            raise ValueError(f"{token_offset + R} places to sample in one step; the runner was made for {self.last_tokens.shape[0]}")
+        tokens = self.last_tokens[token_offset:token_offset + R]
         self.kernels.sample(logits, layout.view(dev, "sample_temperature").view(torch.float32),
                             layout.view(dev, "sample_seed").view(torch.int64), layout.view(dev, "sample_counter"), tokens,
                             workspace.buffer("sample.part_val", (R * self._sample_parts,), torch.float32),
                             workspace.buffer("sample.part_idx", (R * self._sample_parts,), torch.int32))
         return tokens
 
-    def _forward(self, batch, view, layout, workspace, sample: bool):
+    def _forward(self, batch, view, layout, workspace, sample: bool, token_offset: int = 0):
         scope = getattr(self.kernels, "on_current_stream", None)
         with (scope() if scope is not None else contextlib.nullcontext()):
             logits = self.model.forward(batch, self.kernels, workspace, view)
-            tokens = self._sample(logits, layout, workspace) if sample and batch.num_wanted else None
+            tokens = self._sample(logits, layout, workspace, token_offset) if sample and batch.num_wanted else None
         return logits, tokens
 
     MAX_GRAPHS = 32
 
-    def _graph_key(self, batch, sample: bool):
+    def _graph_key(self, batch, sample: bool, token_offset: int = 0):
         """The key under which a step's launches can be replayed, or None.  Two kinds of steps have launches
         that depend on nothing but a few counts: steps of single decoded tokens (the batch size), and steps
         that bring one portion of one prompt (its length and the lengths of the attention work lists, which
@@ -296,24 +298,45 @@ class ModelRunner:
         if not self.use_graphs:
             return None
         if sample and batch.num_tokens == batch.num_segments == batch.num_wanted:
-            return ("decode", batch.num_tokens)
+            return ("decode", batch.num_tokens, token_offset)
         if batch.num_segments == 1 and batch.num_tokens > 1:
             return ("portion", batch.num_tokens, batch.num_wanted, sample, batch.num_prefill_units, batch.num_prefill_tiles,
-                    batch.num_tc_units, batch.num_tc_tiles)
+                    batch.num_tc_units, batch.num_tc_tiles, token_offset)
         return None
 
-    def _graph(self, key, batch, view, layout, sample: bool) -> _DecodeGraph:
-        found = self._graphs.get(key)
+    def _portion_key(self, start: int, count: int, wanted: int, sample: bool, token_offset: int):
+        """The key `_graph_key` gives a step that brings `count` tokens of one request which has `start` cached."""
+        units, tiles = plan_prefill_units([(0, start, count)])
+        tc, tc_tiles = plan_prefill_units([(0, start, count)], TC_TILE_ROWS, TC_MIN_KEY_TILES)
+        return ("portion", count, wanted, sample, len(units), tiles, len(tc), tc_tiles, token_offset)
+
+    # Making a graph takes as long as a dozen steps, and prompts of odd lengths bring shapes that never come again: a
+    # portion's shape is recorded once it has been seen this often.
+    graph_after_sightings = 4
+
+    def _comes_again(self, key) -> bool:
+        """True if `key` has a graph, or has now been seen often enough to be given one."""
+        if key in self._graphs:
+            return True
+        if len(self._portion_shapes_seen) > 4096:
+            self._portion_shapes_seen.clear()
+        seen = self._portion_shapes_seen.get(key, 0) + 1
+        self._portion_shapes_seen[key] = seen
+        return seen >= self.graph_after_sightings
+
+    def _graph(self, key, batch, view, layout, sample: bool, token_offset: int = 0) -> _DecodeGraph:
+        found = self._graphs.pop(key, None)
         if found is not None:
+            self._graphs[key] = found                         # the most recently used is the last to go
             return found
         if len(self._graphs) >= self.MAX_GRAPHS:
-            self._graphs.pop(next(iter(self._graphs)))        # the oldest
+            self._graphs.pop(next(iter(self._graphs)))        # the one not used for longest
         ws = self.graph_workspace
         moved = ws.moved
         # A first run outside the graph sizes the buffers.  It writes what the replay writes again - except that
         # sampling overwrites `last_tokens`, which this very step may read its ids from: put them back.
         saved = self.last_tokens.clone()
-        self._forward(batch, view, layout, ws, sample)
+        self._forward(batch, view, layout, ws, sample, token_offset)
         self.last_tokens.copy_(saved)
         if ws.moved != moved:
             self._graphs.clear()                              # a buffer moved: graphs that hold its old address go
@@ -323,7 +346,7 @@ class ModelRunner:
         ws.frozen = True
         try:
             with torch.cuda.graph(graph):
-                logits, tokens = self._forward(batch, view, layout, ws, sample)
+                logits, tokens = self._forward(batch, view, layout, ws, sample, token_offset)
         finally:
             ws.frozen = False
         found = _DecodeGraph(graph, logits, tokens, self.kernels.launches - before)
@@ -352,15 +375,60 @@ class ModelRunner:
         order of the entries and of their `want` lists - or, with `sample`, the pair
         (logits, int32 tokens sampled at those places, on the device: `last_tokens`).  The
         tensors are views of buffers the next step overwrites."""
+        if sample and self.use_graphs and self.split_mixed_steps:
+            parts = self._split(entries)
+            if parts is not None:
+                return self._run_split(entries, parts)
+        logits, tokens = self._run(entries, sample, 0)
+        self.steps_run += 1
+        return (logits, tokens) if sample else logits
+
+    def _run(self, entries: Sequence[StepEntry], sample: bool, token_offset: int):
         batch, view, layout = self.prepare(entries)
-        key = self._graph_key(batch, sample)
+        key = self._graph_key(batch, sample, token_offset)
+        if key is not None and key[0] == "portion" and not self._comes_again(key):
+            key = None
         if key is not None:
-            found = self._graph(key, batch, view, layout, sample)
+            found = self._graph(key, batch, view, layout, sample, token_offset)
             found.graph.replay()
             self.kernels.launches += found.launches
             self.graph_replays += 1
-            logits, tokens = found.logits, found.tokens
-        else:
-            logits, tokens = self._forward(batch, view, layout, self.workspace, sample)
+            return found.logits, found.tokens
+        return self._forward(batch, view, layout, self.workspace, sample, token_offset)
+
+    # A step that mixes decoded tokens with portions of prompts seldom has the shape of a step before it, so it is
+    # launched kernel by kernel (about 250 launches, bound by the host).  Where the portions have shapes that came
+    # before, it is run as what can be replayed instead: the decoded tokens as one batch, then each portion by itself.
+    # Measured at seven decoded tokens beside a portion of 512: 3.1 ms as one batch, 2.2 ms split.  Longer portions keep
+    # the step whole: its kernels then take as long as the host needs to launch them.
+    SPLIT_MAX_PORTION = 1024
+
+    def _split(self, entries: Sequence[StepEntry]):
+        """The entries as [decoded tokens..., one list per portion] if the step mixes both kinds (decoded tokens first,
+        as the scheduler orders them) and no portion is long; else None."""
+        singles = [e for e in entries if len(e.tokens) == 1 and len(e.want) == 1]
+        others = [e for e in entries if not (len(e.tokens) == 1 and len(e.want) == 1)]
+        if not singles or not others or list(entries[:len(singles)]) != singles:
+            return None
+        if any(len(e.tokens) < 2 or len(e.tokens) > self.SPLIT_MAX_PORTION for e in others):
+            return None
+        # Only portions whose launches can be replayed gain from running alone.
+        offset, replayable = len(singles), True
+        for e in others:
+            key = self._portion_key(self.cache.length(e.slot), len(e.tokens), len(e.want), True, offset)
+            replayable = self._comes_again(key) and replayable
+            offset += len(e.want)
+        return [singles] + [[e] for e in others] if replayable else None
+
+    def _run_split(self, entries: Sequence[StepEntry], parts):
+        # All or nothing, as one step would be: every page the whole step needs must be there before any part runs.
+        additions = [(e.slot, len(e.tokens)) for e in entries]
+        if self.cache.pages_short(additions):
+            self.cache.extend(additions)                      # raises the error a whole step would raise
+            raise AssertionError("unreachable: extend must have refused")
+        offset = 0
+        for part in parts:
+            self._run(part, True, offset)
+            offset += sum(len(e.want) for e in part)
         self.steps_run += 1
-        return (logits, tokens) if sample else logits
+        return None, self.last_tokens[:offset]

@@ -66,23 +66,79 @@ def test_portions(tmp_path, kernels, name, dtype):
 
 @pytest.mark.parametrize("dtype", DTYPES)
 def test_portions_replayed_from_graphs_equal_eager_launches(tmp_path, kernels, dtype):
-    """A step that brings one portion of one prompt is captured once per (length, lengths of the work lists)
-    and replayed; the logits are those of eager launches, bit for bit, also when the same graph serves
-    another request at other pages."""
+    """A step that brings one portion of one prompt is captured when its (length, lengths of the work lists)
+    have come often enough (here: twice), and replayed from then on; the logits are those of eager launches, bit for bit,
+    also when the same graph serves another request at other pages."""
     runner, config, weights = _runner(tmp_path, kernels, "B", dtype)
     tokens = random_tokens(config["vocab_size"], 101, 16)
     sizes = [20, 20, 20, 20, 21]
     eager = replay_modes.portions(runner, tokens, sizes)
-    runner.use_graphs = True
+    runner.use_graphs, runner.graph_after_sightings = True, 2
     first = replay_modes.portions(runner, tokens, sizes)
     other = random_tokens(config["vocab_size"], 101, 17)
     runner.use_graphs = False
     eager_other = replay_modes.portions(runner, other, sizes)
     runner.use_graphs = True
     again = replay_modes.portions(runner, other, sizes)
-    assert 1 <= len(runner._graphs) <= 2 and runner.graph_replays == 2 * len(sizes)
+    assert len(runner._graphs) >= 1 and len(sizes) <= runner.graph_replays < 2 * len(sizes)
     assert torch.equal(first, eager) and torch.equal(again, eager_other)
     assert_close(first, logits_of(config, weights, tokens), REL[dtype])
+    kernels.check_errors()
+
+
+def test_mixed_steps_split_into_replayed_parts_sample_the_same_tokens(tmp_path, kernels):
+    """With graphs, a sampling step that mixes decoded tokens with portions of prompts runs as the decoded tokens
+    and then each portion by itself.  The sampled tokens (float32, greedy, fed with the same ids either way) are
+    those of the step run whole, in the order of the entries; the decoded tokens' ids come from the step before,
+    on the device; a split step that lacks pages fails before any part of it ran."""
+    from kvcache_b200.cache.pages import OutOfPages
+    from kvcache_b200.engine.runner import StepEntry
+    runner, config, weights = _runner(tmp_path, kernels, "B", "float32", num_pages=40)
+    vocab = config["vocab_size"]
+    prompts = [random_tokens(vocab, n, 30 + n) for n in (21, 34, 70)]
+    greedy = (0.0, 0, 0)
+    runner.graph_after_sightings = 2
+
+    def run(split):
+        runner.use_graphs, runner.split_mixed_steps = True, split
+        cache, seen = runner.cache, []
+        slots = [cache.admit() for _ in prompts]
+        for slot, prompt in zip(slots[:2], prompts[:2]):
+            _, tokens = runner.step([StepEntry(slot, prompt, [len(prompt) - 1], greedy)], sample=True)
+            seen.append(tokens.tolist())
+        _, tokens = runner.step([StepEntry(s, [0], [0], greedy, token_from_last=0) for s in slots[:2]], sample=True)
+        # decoded tokens (their ids: what the step before sampled, still on the device) beside portions of the third
+        for start in range(0, 60, 20):
+            entries = [StepEntry(s, [0], [0], greedy, token_from_last=i) for i, s in enumerate(slots[:2])]
+            entries.append(StepEntry(slots[2], prompts[2][start:start + 20], [19], greedy))
+            _, tokens = runner.step(entries, sample=True)
+            seen.append(tokens.tolist())
+            assert len(seen[-1]) == 3
+        lengths = [int(cache.lengths[s]) for s in slots]
+        for s in slots:
+            cache.release(s)
+        return seen, lengths
+
+    replays = runner.graph_replays
+    whole, lengths = run(False)
+    whole_replays = runner.graph_replays - replays
+    run(True)                                                 # the portions' shapes are seen once ...
+    replays = runner.graph_replays
+    split, lengths_split = run(True)                          # ... and replayed at the second time
+    assert split == whole and lengths == lengths_split == [25, 38, 60]
+    assert runner.graph_replays - replays > whole_replays
+    # the plain implementation agrees on the third prompt's tokens (its logits are those of the prompt so far)
+    for start, tokens in zip(range(0, 60, 20), whole[2:]):
+        assert tokens[2] == int(logits_of(config, weights, prompts[2][:start + 20])[-1].argmax())
+    # 40 pages of 8: two requests hold 2 x 38 pages' worth already, the third wants more than is left
+    slots = [runner.cache.admit() for _ in range(3)]
+    long = random_tokens(vocab, 150, 9)
+    runner.step([StepEntry(slots[0], long, [149], greedy)], sample=True)
+    runner.step([StepEntry(slots[1], long, [149], greedy)], sample=True)
+    before = [int(runner.cache.lengths[s]) for s in slots]
+    with pytest.raises(OutOfPages):
+        runner.step([StepEntry(slots[0], [1], [0], greedy), StepEntry(slots[2], long[:40], [39], greedy)], sample=True)
+    assert [int(runner.cache.lengths[s]) for s in slots] == before
     kernels.check_errors()
 
 

@@ -19,7 +19,9 @@ def _llm(folder, name, dtype, **kw):
     fields = dict(dtype=dtype, page_size=PAGE_SIZE[name], num_pages=64, max_running=4, max_tokens_per_step=64,
                   chunk_size=16, use_graphs=True)
     fields.update(kw)
-    return LLM(folder, **fields)
+    llm = LLM(folder, **fields)
+    llm.core.runner.graph_after_sightings = 2      # so that these short runs replay portions, alone and beside decoded tokens
+    return llm
 
 
 def _greedy_is_consistent(config, weights, prompt, out, slack):
