@@ -494,9 +494,62 @@ struct Shared {
     int failed;
 };
 
+// FUSED: the step's rows come straight from the q/k/v product (every segment brings one token).  The kernel adds the
+// biases and rotates the queries itself, and the block whose keys include the new position also makes the new key and
+// value (src/qwen_kernels.cu:45-53 and :63-79 of the reference, folded into its attention): it writes them into their
+// page and into the stage of shared memory that the copy of that page has filled, since the copy ran before they existed.
+struct NewRows {
+    const bf16* qkv;           // [T, (Hq + 2 Hkv) D]: queries, keys, values of each row
+    const float* bias;         // [(Hq + 2 Hkv) D] or nullptr
+    const float* cos_t;        // [table_len, rot_half]; rot_half 0: no rotation
+    const float* sin_t;
+    bf16* k_pages;
+    bf16* v_pages;
+    int rot_half, table_len;
+};
+
+// N elements of a row of the q/k/v product with their biases, rotated by the angles of a position.  What does not
+// depend on the product - the biases and the angles - is fetched by `prepare`, before the wait for the product; `finish`
+// then reads the elements and their rotation partners.  No load sits behind a branch (where a table does not apply the
+// load goes to a valid address and its value is dropped), so each of the two costs one trip to memory.
+template <int N>
+struct NewElements {
+    int idx[N], pidx[N];
+    float bx[N], bp[N], c[N], sn[N];
+    bool rot[N], low[N];
+    __device__ __forceinline__ void prepare(const NewRows& nr, const int (&head)[N], const int (&d)[N], int pos, bool rotate) {
+        const float* spare = reinterpret_cast<const float*>(nr.qkv);      // any address that can be read
+#pragma unroll
+        for (int j = 0; j < N; ++j) {
+            idx[j] = head[j] * D + d[j];
+            rot[j] = rotate && d[j] < 2 * nr.rot_half;
+            low[j] = d[j] < nr.rot_half;
+            pidx[j] = rot[j] ? (low[j] ? idx[j] + nr.rot_half : idx[j] - nr.rot_half) : idx[j];
+            const int t0 = low[j] ? d[j] : d[j] - nr.rot_half;
+            bx[j] = *(nr.bias ? nr.bias + idx[j] : spare);
+            bp[j] = *(nr.bias ? nr.bias + pidx[j] : spare);
+            c[j] = *(rot[j] ? nr.cos_t + (size_t)pos * nr.rot_half + t0 : spare);
+            sn[j] = *(rot[j] ? nr.sin_t + (size_t)pos * nr.rot_half + t0 : spare);
+        }
+    }
+    __device__ __forceinline__ void finish(const NewRows& nr, const bf16* row, float (&out)[N]) const {
+        bf16 xr[N], pr[N];
+#pragma unroll
+        for (int j = 0; j < N; ++j) { xr[j] = row[idx[j]]; pr[j] = row[pidx[j]]; }
+#pragma unroll
+        for (int j = 0; j < N; ++j) {
+            const float x = __bfloat162float(xr[j]) + (nr.bias ? bx[j] : 0.f);
+            const float xp = __bfloat162float(pr[j]) + (nr.bias ? bp[j] : 0.f);
+            out[j] = !rot[j] ? x : (low[j] ? (x * c[j] - xp * sn[j]) : (x * c[j] + xp * sn[j]));
+        }
+    }
+};
+
+template <bool FUSED>
 __global__ void __launch_bounds__(160) flash_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k,
                                                                const __grid_constant__ CUtensorMap map_v,
-                                                               const __grid_constant__ DecodeParams p, int* err) {
+                                                               const __grid_constant__ DecodeParams p,
+                                                               const __grid_constant__ NewRows nr, int* err) {
     TRACE(0)
     if (p.nsplit > 1) cluster_arrive_started();
     extern __shared__ unsigned char smem_raw[];
@@ -579,8 +632,10 @@ __global__ void __launch_bounds__(160) flash_decode_tma_kernel(const __grid_cons
             }
         };
         // The first stages are old if all their keys lie before this step's first position: fetched before the wait.
+        // Fused, all of them are: nobody but this kernel writes the pool meanwhile, and the new position's slot is
+        // made afresh in shared memory.
         const int first = min(n, STAGES);
-        const bool early = (my_begin + first * KW) * KT <= first_pos;
+        const bool early = FUSED || (my_begin + first * KW) * KT <= first_pos;
         if (early)
             for (int i = 0; i < first && ok; ++i) load_stage(i);
         pdl_wait();
@@ -589,16 +644,95 @@ __global__ void __launch_bounds__(160) flash_decode_tma_kernel(const __grid_cons
         if (!ok && lane == 0) { atomicOr(err, KVB_DEV_TIMEOUT); sh.failed = 1; }
     } else {
         // ---- scanning warps ----
+        __shared__ __align__(16) unsigned short new_q_raw[FUSED ? 16 * D : 8];
+        bf16* new_q = reinterpret_cast<bf16*>(new_q_raw);
+        const int width = (p.Hq + 2 * p.Hkv) * D;
+        // Fused: the warp whose keys of stage `new_stage` include the new position makes the new key and value.  It
+        // fetches them, like every warp its share of the queries, in one round of loads right after the wait.
+        constexpr int NK = 16 * KW;
+        constexpr int PER_LANE = D / 32;
+        int new_stage = -1, new_page = -1;
+        float kn[PER_LANE], vn[PER_LANE];
+        if (FUSED) {
+            const int tile = first_pos / KT;
+            if (tile >= my_begin && tile < my_end) {
+                const int i = (tile - my_begin) / KW;
+                if ((first_pos - (my_begin + i * KW) * KT) / NK == warp) {
+                    new_stage = i;
+                    new_page = p.block_table[(size_t)seg * p.table_stride + (first_pos >> p.page_shift)];
+                }
+            }
+        }
+        // One token a segment: row r is query head hk G + r at the position of the new key.  A thread makes elements
+        // tid, tid + 128, ... of the rows' rows * D (the first QN of them prepared ahead; indices beyond the rows are
+        // clamped: loaded, not stored).
+        constexpr int QN = 4;
+        NewElements<QN> qe;
+        NewElements<PER_LANE> ke, ve;
+        const bool pos_ok = !FUSED || nr.rot_half == 0 || first_pos < nr.table_len;
+        const int pos = pos_ok ? first_pos : 0;
+        if (FUSED) {
+            int head[QN], d[QN];
+#pragma unroll
+            for (int j = 0; j < QN; ++j) {
+                const int idx = min(128 * j + tid, rows * D - 1);
+                head[j] = hk * G + idx / D;
+                d[j] = idx % D;
+            }
+            qe.prepare(nr, head, d, pos, true);
+            if (new_stage >= 0) {
+                int khead[PER_LANE], vhead[PER_LANE], dd[PER_LANE];
+#pragma unroll
+                for (int j = 0; j < PER_LANE; ++j) { khead[j] = p.Hq + hk; vhead[j] = p.Hq + p.Hkv + hk; dd[j] = lane + 32 * j; }
+                ke.prepare(nr, khead, dd, pos, true);
+                ve.prepare(nr, vhead, dd, pos, false);                            // values are not rotated
+            }
+        }
         pdl_wait();
         pdl_launch_dependents();
         TRACE(1)
+        if (FUSED) {
+            if (!pos_ok && tid == 0) atomicOr(err, KVB_DEV_BAD_POS);
+            const bf16* src = nr.qkv + (size_t)q_start * width;
+            if (new_stage >= 0) {
+                if (new_page < 0 && lane == 0) atomicOr(err, KVB_DEV_BAD_PAGE);
+                ke.finish(nr, src, kn);
+                ve.finish(nr, src, vn);
+            }
+            float x[QN];
+            qe.finish(nr, src, x);
+#pragma unroll
+            for (int j = 0; j < QN; ++j) {
+                const int idx = 128 * j + tid;
+                if (idx < rows * D) new_q[idx] = __float2bfloat16_rn(x[j]);
+            }
+            for (int base = 128 * QN; base < rows * D; base += 128 * QN) {       // more rows than the usual groups have
+                int head[QN], d[QN];
+#pragma unroll
+                for (int j = 0; j < QN; ++j) {
+                    const int idx = min(base + 128 * j + tid, rows * D - 1);
+                    head[j] = hk * G + idx / D;
+                    d[j] = idx % D;
+                }
+                NewElements<QN> more;
+                more.prepare(nr, head, d, pos, true);
+                more.finish(nr, src, x);
+#pragma unroll
+                for (int j = 0; j < QN; ++j) {
+                    const int idx = base + 128 * j + tid;
+                    if (idx < rows * D) new_q[idx] = __float2bfloat16_rn(x[j]);
+                }
+            }
+            asm volatile("bar.sync 1, 128;\n" ::: "memory");          // the four scanning warps
+            TRACE(6)
+        }
         auto q_row = [&](int r) -> const bf16* {
+            if (FUSED) return r < rows ? new_q + r * D : nullptr;
             return r < rows ? p.q + ((size_t)(q_start + r / G) * p.Hq + hk * G + r % G) * D : nullptr;
         };
         rows_load_q(w, q_row);
         w.pos[0] = g < rows ? first_pos + g / G : -1;
         w.pos[1] = g + 8 < rows ? first_pos + (g + 8) / G : -1;
-        constexpr int NK = 16 * KW;
         for (int i = 0; i < n; ++i) {
             const int s = i % STAGES;
             if (!mbar_wait(&sh.full[s], (i / STAGES) & 1)) {
@@ -606,8 +740,23 @@ __global__ void __launch_bounds__(160) flash_decode_tma_kernel(const __grid_cons
                 break;
             }
             if (i == 0) { TRACE(2) }
-            const unsigned char* base = stages + (size_t)s * STAGE_BYTES + warp * NK * 128;   // this warp's keys: rows warp NK ..
+            unsigned char* base = stages + (size_t)s * STAGE_BYTES + warp * NK * 128;   // this warp's keys: rows warp NK ..
             const int key0 = (my_begin + i * KW) * KT + warp * NK;
+            if (FUSED && i == new_stage) {
+                // Into their page, and over what the copy left at their row.
+                const size_t at = ((size_t)max(new_page, 0) * p.Hkv + hk) * p.page_size * D + (size_t)(first_pos & (p.page_size - 1)) * D;
+                const int row = first_pos - key0;
+                const SwizzledTile kt{base, HALF_BYTES}, vt{base + KV_BYTES, HALF_BYTES};
+#pragma unroll
+                for (int j = 0; j < PER_LANE; ++j) {
+                    const int d = lane + 32 * j;
+                    const bf16 kb = __float2bfloat16_rn(kn[j]), vb = __float2bfloat16_rn(vn[j]);
+                    const_cast<bf16*>(kt.at(row, d & ~7))[d & 7] = kb;
+                    const_cast<bf16*>(vt.at(row, d & ~7))[d & 7] = vb;
+                    if (new_page >= 0) { nr.k_pages[at + d] = kb; nr.v_pages[at + d] = vb; }
+                }
+                __syncwarp();
+            }
             if (key0 < kv_len)
                 rows_tile_auto_in<NK>(w, SwizzledTile{base, HALF_BYTES}, SwizzledTile{base + KV_BYTES, HALF_BYTES}, key0,
                                       p.window, p.scale_log2, first_pos, kv_len - 1, true);
@@ -716,7 +865,7 @@ __global__ void __launch_bounds__(160) flash_decode_tma_kernel(const __grid_cons
 KVB_API int kvb_flash_decode_tma_max_clusters(int nsplit) {
     using namespace dtma;
     if (nsplit < 1 || nsplit > MAX_CLUSTER) return 0;
-    if (cudaFuncSetAttribute(flash_decode_tma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES) != cudaSuccess) return 0;
+    if (cudaFuncSetAttribute(flash_decode_tma_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES) != cudaSuccess) return 0;
     cudaLaunchConfig_t config = {};
     config.gridDim = dim3(nsplit * 64);
     config.blockDim = dim3(160);
@@ -729,22 +878,27 @@ KVB_API int kvb_flash_decode_tma_max_clusters(int nsplit) {
     config.attrs = attribute;
     config.numAttrs = 1;
     int clusters = 0;
-    if (cudaOccupancyMaxActiveClusters(&clusters, flash_decode_tma_kernel, &config) != cudaSuccess) return 0;
+    if (cudaOccupancyMaxActiveClusters(&clusters, flash_decode_tma_kernel<true>, &config) != cudaSuccess) return 0;
     return clusters;
 }
 
 // The splits as a cluster, keys and values by TMA: nsplit 1..8, page_size a power of two 8..64, num_pages the pool's
-// page count, err the device error word.
-KVB_API int kvb_flash_decode_tma(const void* q, void* out, const void* k_pages, const void* v_pages, int num_pages,
+// page count, err the device error word.  With `qkv` (then `q` is not read, `items` must be null and every segment
+// bring one token) the kernel takes the rows of the q/k/v product instead of rotated queries and appended keys:
+// bias [(Hq + 2 Hkv) D] or null, cos_t / sin_t [table_len, rot_half] (rot_half 0: no rotation).
+KVB_API int kvb_flash_decode_tma(const void* q, void* out, void* k_pages, void* v_pages, int num_pages,
                                  const int* block_table, int table_stride, const int* items, int n_items,
                                  const int* seg_q_start, const int* seg_q_len, const int* seg_kv_len, int Hq, int Hkv,
-                                 int page_size, int window, int nsplit, float scale, int* err, cudaStream_t stream) {
+                                 int page_size, int window, int nsplit, float scale, const void* qkv, const float* bias,
+                                 const float* cos_t, const float* sin_t, int rot_half, int table_len, int* err,
+                                 cudaStream_t stream) {
     using namespace dtma;
     if (n_items <= 0) return KVB_OK;
     if (Hkv < 1 || Hq % Hkv != 0 || Hq / Hkv > 16) return KVB_ERR_SHAPE;
     if (page_size < 8 || page_size > 64 || (page_size & (page_size - 1)) != 0) return KVB_ERR_SHAPE;
     if (nsplit < 1 || nsplit > MAX_CLUSTER || n_items > 65535 || Hkv > 65535) return KVB_ERR_LIMIT;
     if (((uintptr_t)k_pages | (uintptr_t)v_pages) & 15) return KVB_ERR_ALIGN;
+    if (qkv && (items != nullptr || rot_half < 0 || 2 * rot_half > D || (rot_half > 0 && (!cos_t || !sin_t)))) return KVB_ERR_SHAPE;
     CUtensorMap mk, mv;
     const long long pool_rows = (long long)num_pages * Hkv * page_size;
     int rc = make_bf16_map(&mk, k_pages, pool_rows, D, D, page_size);
@@ -761,16 +915,23 @@ KVB_API int kvb_flash_decode_tma(const void* q, void* out, const void* k_pages, 
     while ((1 << p.page_shift) < page_size) ++p.page_shift;
     p.window = window; p.nsplit = nsplit;
     p.scale_log2 = scale * 1.4426950408889634f;
+    NewRows nr{(const bf16*)qkv, bias, cos_t, sin_t, (bf16*)k_pages, (bf16*)v_pages, rot_half, table_len};
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(flash_decode_tma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
-        if (e != cudaSuccess) return (int)e;
-        e = cudaFuncSetAttribute(flash_decode_tma_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
-        if (e != cudaSuccess) return (int)e;
+        for (int fused = 0; fused < 2; ++fused) {
+            const void* kernel = fused ? (const void*)flash_decode_tma_kernel<true> : (const void*)flash_decode_tma_kernel<false>;
+            cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+            if (e != cudaSuccess) return (int)e;
+            e = cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+            if (e != cudaSuccess) return (int)e;
+        }
         configured = true;
     }
     dim3 grid(nsplit, Hkv, n_items);
-    kvb_launch_cluster(flash_decode_tma_kernel, dim3(grid), dim3(160), (unsigned)nsplit, (size_t)SMEM_BYTES, stream, mk, mv, p, err);
+    if (qkv)
+        kvb_launch_cluster(flash_decode_tma_kernel<true>, dim3(grid), dim3(160), (unsigned)nsplit, (size_t)SMEM_BYTES, stream, mk, mv, p, nr, err);
+    else
+        kvb_launch_cluster(flash_decode_tma_kernel<false>, dim3(grid), dim3(160), (unsigned)nsplit, (size_t)SMEM_BYTES, stream, mk, mv, p, nr, err);
     return kvb_launch_status();
 }
 #endif

@@ -70,12 +70,15 @@ class GQAAttention(Mixer):
         k, ws = ctx.kernels, ctx.workspace
         qkv = ws.buffer("attn.qkv", (T, self.q_size + 2 * self.kv_size), self.dtype)
         k.linear(x, self.w_qkv, qkv)
-        q = ws.buffer("attn.q", (T, self.q_size), self.dtype)
         rotation = self.position.rotation() if self.position is not None else None
-        k.qkv_rope_append(qkv, self.b_qkv, rotation.cos if rotation else None, rotation.sin if rotation else None,
-                          ctx.batch, ctx.kv, q, self.num_heads)
+        cos, sin = (rotation.cos, rotation.sin) if rotation else (None, None)
         attn = ws.buffer("attn.out", (T, self.q_size), self.dtype)
-        k.paged_attention(q, ctx.batch, ctx.kv, attn, self.num_heads, self.scale, ws)
+        # A kernel set may do bias, rotation, append and attention in one launch where it has a kernel for that.
+        fused = getattr(k, "rope_append_attention", None)
+        if fused is None or not fused(qkv, self.b_qkv, cos, sin, ctx.batch, ctx.kv, attn, self.num_heads, self.scale, ws):
+            q = ws.buffer("attn.q", (T, self.q_size), self.dtype)
+            k.qkv_rope_append(qkv, self.b_qkv, cos, sin, ctx.batch, ctx.kv, q, self.num_heads)
+            k.paged_attention(q, ctx.batch, ctx.kv, attn, self.num_heads, self.scale, ws)
         delta = ws.buffer("attn.delta", (T, self.hidden), self.dtype)
         k.linear(attn, self.w_o, delta)
         return delta

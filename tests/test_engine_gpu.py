@@ -161,6 +161,39 @@ def test_head_size_64_long_prompt_and_decoding(tmp_path, kernels, dtype):
         assert kernels.decode_merge == "tma" and kernels.tc_attention_min_rows <= 450
 
 
+def test_decoding_with_rotation_and_append_inside_attention(tmp_path, kernels, request):
+    """Decode steps whose attention kernel also adds the biases, rotates queries and keys and appends the new keys
+    and values (the engine takes that kernel from a number of requests on; here from one): two requests of
+    different lengths decoded side by side for 330 steps - over page and key-tile edges, the second layer's window
+    giving pages back behind them - against the plain implementation; then one of them goes on alone."""
+    from kvcache_b200.engine.runner import StepEntry
+    saved = kernels.fused_rope_min_requests
+    request.addfinalizer(lambda: setattr(kernels, "fused_rope_min_requests", saved))
+    kernels.fused_rope_min_requests = 1
+    runner, config, weights = _runner(tmp_path, kernels, "D", "bfloat16", num_pages=96, max_tokens_per_step=1024,
+                                      max_tokens_per_request=1024)
+    a, b = random_tokens(config["vocab_size"], 451, 31), random_tokens(config["vocab_size"], 380, 32)
+    want_a, want_b = logits_of(config, weights, a), logits_of(config, weights, b)
+    sa, sb = runner.cache.admit(), runner.cache.admit()
+    runner.step([StepEntry(sa, a[:100], [99]), StepEntry(sb, b[:50], [49])])
+    got_a, got_b = [], []
+    for i in range(330):
+        out = runner.step([StepEntry(sa, a[100 + i:101 + i], [0]), StepEntry(sb, b[50 + i:51 + i], [0])]).clone()
+        got_a.append(out[0])
+        got_b.append(out[1])
+    counts = []
+    for i in range(430, 451):
+        if i == 441:
+            kernels.fused_rope_min_requests = None           # the last ten steps with the separate rotation kernel again
+        launches = kernels.launches
+        got_a.append(runner.step([StepEntry(sa, a[i:i + 1], [0])]).clone()[0])
+        counts.append(kernels.launches - launches)
+    assert counts[0] == counts[-1] - len(runner.model.schedule)       # one launch fewer a layer
+    assert_close(torch.stack(got_a), want_a[100:], REL["bfloat16"], "the longer request")
+    assert_close(torch.stack(got_b), want_b[50:], REL["bfloat16"], "the shorter request")
+    kernels.check_errors()
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("name", NAMES)
 def test_mixed_with_page_reuse(tmp_path, kernels, name, dtype):

@@ -392,6 +392,66 @@ def test_paged_attention_flash(kernels, request, scenario):
     kernels.check_errors()
 
 
+FUSED_DECODE_SCENARIOS = [
+    # (cached tokens of each request (each brings one more), Hq, Hkv, D, page, window, rotated dimensions)
+    ([4000, 64, 63, 0, 129, 127, 128], 14, 2, 64, 16, None, 64),     # new keys first and last of a tile, of a page, of the cache
+    ([1000, 5, 2047, 15, 16], 8, 2, 64, 8, 200, 32),                 # small pages, a window that gave pages back, half the head rotated
+    ([777, 3000, 15, 63, 64], 8, 4, 128, 32, None, 128),             # head size 128, splits without keys
+    ([130, 64, 0], 3, 3, 64, 64, 100, 0),                            # a page is a whole key tile; no rotation
+    ([2500, 100], 16, 1, 128, 64, 1000, 96),                         # group of 16
+]
+
+
+@pytest.mark.parametrize("scenario", FUSED_DECODE_SCENARIOS)
+def test_rope_append_attention_fused_decode(kernels, request, scenario):
+    """Bias, rotation, append and attention of a decode step in one kernel, against the plain rotation + append followed
+    by the plain attention: the attention's output, and the pages with the new keys and values in them."""
+    from kvcache_b200.engine.workspace import Workspace
+    from kvcache_b200.parts.position import RotaryHalf
+    cached, Hq, Hkv, D, page, window, rotated = scenario
+    dtype = torch.bfloat16
+    segments = [(c, 1) for c in cached]
+    batch, kv = paged_scenario(segments, num_kv_heads=Hkv, head_dim=D, page_size=page, dtype=dtype, device="cpu",
+                               window=window, seed=21)
+    T = batch.num_tokens
+    g = torch.Generator().manual_seed(22)
+    qkv = torch.randn(T, (Hq + 2 * Hkv) * D, generator=g).to(dtype)
+    bias = torch.randn((Hq + 2 * Hkv) * D, generator=g)
+    cos = sin = None
+    if rotated:
+        rope = RotaryHalf(rotated, 10000.0, 4200)
+        rope.bind({}, torch.device("cpu"))
+        cos, sin = rope.rotation().cos, rope.rotation().sin
+    if window:                                           # as the cache manager does: pages behind the window are not held
+        for i, c in enumerate(cached):
+            kv.block_table[i, :max(0, c - window + 1) // page] = -1
+    ws = Workspace(DEV)
+    saved = (kernels.decode_ctas_wanted, kernels.decode_min_tiles, kernels.fused_rope_min_requests)
+    request.addfinalizer(lambda: [setattr(kernels, n, v) for n, v in
+                                  zip(("decode_ctas_wanted", "decode_min_tiles", "fused_rope_min_requests"), saved)])
+    kernels.fused_rope_min_requests = 1
+    to = lambda t: None if t is None else t.to(DEV)
+    for b in (bias, None):
+        kv_ref, q_ref, ref = clone_kv(kv), torch.empty(T, Hq * D, dtype=dtype), torch.empty(T, Hq * D, dtype=dtype)
+        REF.qkv_rope_append(qkv, b, cos, sin, batch, kv_ref, q_ref, Hq)
+        REF.paged_attention(q_ref, batch, kv_ref, ref, Hq, D ** -0.5)
+        for wanted, min_tiles in ((saved[0], saved[1]), (3, 4), (100000, 1), (5 * T * Hkv, 1)):
+            kernels.decode_ctas_wanted, kernels.decode_min_tiles = wanted, min_tiles
+            kv_dev = clone_kv(kv, DEV)
+            out = torch.full((T, Hq * D), float("nan"), dtype=dtype, device=DEV)
+            assert kernels.rope_append_attention(qkv.to(DEV), to(b), to(cos), to(sin), batch_to(batch, DEV), kv_dev, out, Hq,
+                                                 D ** -0.5, ws)
+            assert_close(out, ref, REL[dtype], f"attention, decode_ctas_wanted={wanted}")
+            assert_close(kv_dev.k_pages, kv_ref.k_pages, REL[dtype], "key pages")
+            assert_close(kv_dev.v_pages, kv_ref.v_pages, REL[dtype], "value pages")
+    # what the kernel does not take is left to the two calls
+    kv_dev = clone_kv(kv, DEV)
+    kv_dev.writes = False
+    assert not kernels.rope_append_attention(qkv.to(DEV), to(bias), to(cos), to(sin), batch_to(batch, DEV), kv_dev,
+                                             torch.empty(T, Hq * D, dtype=dtype, device=DEV), Hq, D ** -0.5, ws)
+    kernels.check_errors()
+
+
 TC_SCENARIOS = [
     # (segments (cached, new), Hq, Hkv, D, page, window, least key tiles of a unit)
     ([(0, 128)], 2, 1, 64, 16, None, 8),
