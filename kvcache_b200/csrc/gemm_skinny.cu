@@ -37,9 +37,11 @@ __device__ __forceinline__ void mma_bf16(float* c, uint32_t a0, uint32_t a1, uin
                  : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
-__device__ __forceinline__ uint4 ld_stream(const void* p) {      // weights: read once, keep out of L1
+// Weights: read once a step - kept out of L1 and marked as the first to leave L2.
+__device__ __forceinline__ uint4 ld_stream(const void* p, uint64_t policy) {
     uint4 v;
-    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];\n" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+    asm volatile("ld.global.nc.L1::no_allocate.L2::cache_hint.v4.u32 {%0,%1,%2,%3}, [%4], %5;\n"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p), "l"(policy));
     return v;
 }
 
@@ -72,6 +74,8 @@ __global__ void __launch_bounds__(256) gemm_skinny_kernel(const bf16* __restrict
     // kernel that makes x (they do not depend on it); after it, a buffer is refilled as soon as its products are
     // issued, so that a warp's share of K costs one trip to memory plus its streaming.  (An L2 prefetch of the rest
     // of the share was measured slower than none.)
+    uint64_t w_policy;
+    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;\n" : "=l"(w_policy));
     constexpr int U = (RT * NT >= 4) ? 1 : 2;
     constexpr int NBUF = (RT * NT == 1) ? 3 : 2;        // measured: three beat two and four for the narrowest tiles
     auto load_w = [&](uint4 (&a)[U][RT][2], int kb) {
@@ -81,8 +85,8 @@ __global__ void __launch_bounds__(256) gemm_skinny_kernel(const bf16* __restrict
             const int k = (live ? kb + u : kb) * 32;
 #pragma unroll
             for (int r = 0; r < RT; ++r) {
-                a[u][r][0] = live ? ld_stream(wrow[r][0] + k) : make_uint4(0, 0, 0, 0);
-                a[u][r][1] = live ? ld_stream(wrow[r][1] + k) : make_uint4(0, 0, 0, 0);
+                a[u][r][0] = live ? ld_stream(wrow[r][0] + k, w_policy) : make_uint4(0, 0, 0, 0);
+                a[u][r][1] = live ? ld_stream(wrow[r][1] + k, w_policy) : make_uint4(0, 0, 0, 0);
             }
         }
     };

@@ -68,6 +68,9 @@ gemm_wstream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
     // The first thread makes the barriers and at once sends for the first stages' W tiles - they depend neither on
     // the kernel before this one nor on the tensor memory that warp 1 allocates meanwhile.
     const int early = my_kblocks < STAGES ? my_kblocks : STAGES;
+    // W is read once a step: first to leave L2, so that what is read again soon (the cache of a few requests,
+    // activations) stays there.  Measured with the output head of a one-request step: 642 -> 630 us a step.
+    const uint64_t w_policy = l2_evict_first_policy();
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) { mbar_init(&sh.full[s], 1); mbar_init(&sh.empty[s], 1); }
         mbar_init(&sh.accum_full, 1);
@@ -76,7 +79,7 @@ gemm_wstream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
         asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
         for (int i = 0; i < early; ++i) {
             mbar_expect_tx(&sh.full[i], STAGE_BYTES);                          // W and x tile of the stage
-            tma_load_2d(tiles + i * STAGE_BYTES, &map_w, (rank + i * ksplit) * BK, n0, &sh.full[i]);
+            tma_load_2d_hint(tiles + i * STAGE_BYTES, &map_w, (rank + i * ksplit) * BK, n0, &sh.full[i], w_policy);
         }
     }
     if (warp == 1) {
@@ -98,7 +101,7 @@ gemm_wstream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
                 const int s = i % STAGES;
                 if (!mbar_wait(&sh.empty[s], ((i / STAGES) - 1) & 1)) { atomicOr(p.err, KVB_DEV_TIMEOUT); sh.failed = 1; ok = false; break; }
                 mbar_expect_tx(&sh.full[s], STAGE_BYTES);
-                tma_load_2d(tiles + s * STAGE_BYTES, &map_w, (rank + i * ksplit) * BK, n0, &sh.full[s]);
+                tma_load_2d_hint(tiles + s * STAGE_BYTES, &map_w, (rank + i * ksplit) * BK, n0, &sh.full[s], w_policy);
                 tma_load_2d(tiles + s * STAGE_BYTES + W_BYTES, &map_x, (rank + i * ksplit) * BK, 0, &sh.full[s]);
             }
         }

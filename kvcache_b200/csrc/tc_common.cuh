@@ -41,6 +41,19 @@ __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, i
         ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y) : "memory");
 }
 
+// The same copy with an L2 policy: weights that a step reads once are marked to be evicted first, so that what is read
+// again soon (the cache of a few requests, activations) stays in L2.
+__device__ __forceinline__ uint64_t l2_evict_first_policy() {
+    uint64_t policy;
+    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;\n" : "=l"(policy));
+    return policy;
+}
+__device__ __forceinline__ void tma_load_2d_hint(void* dst, const CUtensorMap* map, int x, int y, uint64_t* bar, uint64_t policy) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1, {%3, %4}], [%2], %5;\n"
+        ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y), "l"(policy) : "memory");
+}
+
 // Shared-memory matrix descriptor of a K-major tile whose rows are 128 bytes (64 bfloat16), 128-byte swizzle:
 // start address >> 4 in bits 0-13, stride between 8-row groups (1024 bytes) >> 4 in bits 32-45, descriptor
 // version 1 in bits 46-47, swizzle mode 2 (128 bytes) in bits 61-63.  The leading-dimension offset is not used

@@ -268,7 +268,7 @@ class CudaKernels(KernelSet):
         other, or interleaved in eights (see csrc/gemm_skinny.cu)."""
         M, K = x.shape
         I = out.shape[1]
-        if interleaved and self._skinny(x.dtype, M, K):
+        if interleaved and self._skinny(x.dtype, M, K, 2 * I):
             self.launches += 1
             _check(self._gemm_skinny.kvb_gemm_skinny(_dtype_code(out.dtype), 1, _ptr(x), _ptr(w_gate_up), _ptr(None),
                                                      _ptr(out), M, 2 * I, K, self._stream()), "gate_up_act (skinny)")
@@ -298,7 +298,15 @@ class CudaKernels(KernelSet):
         rows = self.WSTREAM_DEEP_MAX_ROWS if K >= 4 * N > 0 else self.WSTREAM_MAX_ROWS
         return self.wstream_gemm and dtype == torch.bfloat16 and self.bf16_gemm == "auto" and M <= rows and K % 8 == 0
 
-    def _skinny(self, dtype: torch.dtype, M: int, K: int) -> bool:
+    # Weights of at least this many bytes go through the weight-streaming tcgen05 kernel at any number of rows up to its
+    # limit: TMA keeps more bytes in flight per SM than register loads do.  Measured at 8 rows: the 7B model's gate/up
+    # (272 MB) 45 against 64 us, its way down (136 MB) 25 against 40 us, output heads (272 MB .. 1.1 GB) at 6.6-7.0
+    # against 5.1-6.0 TB/s; below it the register kernel is ahead (1.5B gate/up, 55 MB: 10.5 against 13.2 us).
+    WSTREAM_MIN_WEIGHT_BYTES = 96 << 20
+
+    def _skinny(self, dtype: torch.dtype, M: int, K: int, N: int = 0) -> bool:
+        if 2 * N * K >= self.WSTREAM_MIN_WEIGHT_BYTES and self._wstream(dtype, M, K, N):
+            return False
         return self.skinny_gemm and dtype == torch.bfloat16 and M <= self.SKINNY_MAX_ROWS and K % 32 == 0
 
     def _tcgen05(self, x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, fused: bool = False) -> bool:
@@ -316,7 +324,7 @@ class CudaKernels(KernelSet):
         if x.shape[1] != K or tuple(out.shape) != (M, N):
             raise KernelError(f"linear: shapes x{tuple(x.shape)} w{tuple(w.shape)} out{tuple(out.shape)} do not fit")
         self.launches += 1
-        if self._skinny(x.dtype, M, K):
+        if self._skinny(x.dtype, M, K, N):
             _check(self._gemm_skinny.kvb_gemm_skinny(_dtype_code(out.dtype), 0, _ptr(x), _ptr(w), _ptr(bias),
                                                      _ptr(out), M, N, K, self._stream()), "linear (skinny)")
             return
