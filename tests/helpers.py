@@ -92,3 +92,25 @@ def assert_close(got: torch.Tensor, want: torch.Tensor, rel: float, what: str = 
     scale = max(want.abs().max().item(), 1e-30)
     err = (got - want).abs().max().item()
     assert err <= rel * scale, f"{what}: max abs error {err:.3e} > {rel:g} * {scale:.3e}"
+
+
+def reference_attention_case():
+    """The case of the reference's own numpy attention (ref/ref_attn.py): q [8, 64], K and V [8, 128, 64] drawn from
+    numpy's default_rng(0) as that script draws them, and its output as committed under tests/golden (made by
+    tests/golden/make_ref_attn_golden.py).  The inputs are checked against the digests recorded with the output."""
+    import hashlib
+    import json
+    import os
+    import numpy as np
+    golden = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
+    with open(os.path.join(golden, "ref_attn.json"), "r", encoding="utf-8") as fh:
+        meta = json.load(fh)
+    H, S, D = meta["heads"], meta["keys"], meta["head_dim"]
+    rng = np.random.default_rng(meta["seed"])
+    q = rng.standard_normal((H, D)).astype(np.float32)
+    K = rng.standard_normal((H, S, D)).astype(np.float32)
+    V = rng.standard_normal((H, S, D)).astype(np.float32)
+    for name, arr in (("q", q), ("K", K), ("V", V)):
+        assert hashlib.sha256(arr.tobytes()).hexdigest() == meta["inputs_sha256"][name], f"{name} is not what the reference drew"
+    out = np.fromfile(os.path.join(golden, "ref_attn_out.f32"), dtype="<f4").reshape(H, D)
+    return torch.from_numpy(q), torch.from_numpy(K), torch.from_numpy(V), torch.from_numpy(out.copy())

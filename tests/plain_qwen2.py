@@ -5,7 +5,10 @@ function for each part, float64 by default.  It shares no code with `kvcache_b20
 It rests on the reference's formulas, not on running the reference: kimxinw/kvcache's
 model code is CUDA + cuBLAS with the sizes of one checkpoint compiled in
 (apps/qwen_serve.cu:20-23) and cannot be imported or run on a CPU.  Each function
-cites the lines it restates.  The window keys have no counterpart in the reference
+cites the lines it restates.  What of the reference does run on a CPU is its numpy
+attention of one query over 128 keys (ref/ref_attn.py): its output lies under
+tests/golden with the script that made it, and `attention` is held to it in
+tests/test_plain.py.  The window keys have no counterpart in the reference
 (it has no windowed layers); their meaning here is the one of the checkpoint's own
 config.json: layers at index >= max_window_layers see `sliding_window` keys, their
 own included, when use_sliding_window is true.

@@ -452,6 +452,34 @@ def test_rope_append_attention_fused_decode(kernels, request, scenario):
     kernels.check_errors()
 
 
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_attention_kernels_equal_the_references_own_numpy_attention(kernels, request, dtype):
+    """ref/ref_attn.py of the reference (one query per head over 128 keys, eight heads with a kv head each; output
+    committed under tests/golden): its keys and values laid into shuffled pages, the query as a decode step's only row.
+    float32 through the generic kernel; bfloat16 through the TMA, cluster and ticket decode kernels."""
+    from helpers import reference_attention_case
+    from kvcache_b200.engine.workspace import Workspace
+    q, K, V, want = reference_attention_case()
+    H, S, D = K.shape
+    for page in (16, 8):
+        batch, kv = paged_scenario([(S - 1, 1)], num_kv_heads=H, head_dim=D, page_size=page, dtype=dtype, device="cpu", seed=3)
+        for pos in range(S):
+            slot = int(kv.block_table[0, pos // page])
+            kv.k_pages[slot, :, pos % page, :] = K[:, pos, :].to(dtype)
+            kv.v_pages[slot, :, pos % page, :] = V[:, pos, :].to(dtype)
+        saved = kernels.decode_merge
+        request.addfinalizer(lambda: setattr(kernels, "decode_merge", saved))
+        for merge in (("tma", "cluster", "ticket") if dtype == torch.bfloat16 else (saved,)):
+            kernels.decode_merge = merge
+            out = torch.full((1, H * D), float("nan"), dtype=dtype, device=DEV)
+            kernels.paged_attention(q.reshape(1, H * D).to(dtype).to(DEV), batch_to(batch, DEV), clone_kv(kv, DEV), out, H,
+                                    D ** -0.5, Workspace(DEV))
+            # float32: summation order only.  bfloat16: q, K, V, the probabilities and the output are rounded to 8 bits
+            # of mantissa (rounding the inputs and the output alone gives 3.5e-3 here).
+            assert_close(out.reshape(H, D), want, REL[dtype], f"page {page}, {merge}")
+    kernels.check_errors()
+
+
 TC_SCENARIOS = [
     # (segments (cached, new), Hq, Hkv, D, page, window, least key tiles of a unit)
     ([(0, 128)], 2, 1, 64, 16, None, 8),

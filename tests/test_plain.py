@@ -70,6 +70,18 @@ def test_window_edge_is_exact():
     assert abs(plain.attention(q, k, v, None)[11, 0, 0] - 3.0) < 1e-9
 
 
+def test_attention_equals_the_references_own_numpy_attention():
+    """The one piece of the reference's arithmetic that runs on a CPU, ref/ref_attn.py: one query per head over 128
+    keys.  Here it is the last position of a sequence of 128 (it sees every key); eight heads with a kv head each."""
+    from helpers import reference_attention_case
+    q, K, V, want = reference_attention_case()
+    H, S, D = K.shape
+    queries = torch.zeros(S, H, D, dtype=torch.float64)
+    queries[-1] = q.double()
+    got = plain.attention(queries, K.double().transpose(0, 1).contiguous(), V.double().transpose(0, 1).contiguous())[-1]
+    assert (got - want.double()).abs().max().item() < 2e-6
+
+
 def test_swiglu_by_hand():
     x = torch.tensor([[1.0, -2.0]], dtype=torch.float64)
     wg, wu, wd = (torch.tensor(m, dtype=torch.float64) for m in ([[1.0, 0.0]], [[0.0, 1.0]], [[3.0], [1.0]]))
