@@ -76,3 +76,35 @@ def test_prefill_work_list():
     # However long the prompt, the list stays bounded.
     units, n_tiles = plan_prefill_units([(0, 0, 32768)])
     assert n_tiles == 512 and len(units) <= 2 * 512 + 256
+
+
+def test_which_mixed_steps_are_run_in_parts(tmp_path):
+    """The runner's decision to run a sampling step as its parts (decoded tokens, then each portion alone): only where
+    decoded tokens come first and beside portions of at least two and at most SPLIT_MAX_PORTION tokens whose shapes
+    have come `graph_after_sightings` times (so that their launches can be replayed); a portion's shape is its length,
+    the number of wanted places, the lengths of its attention work lists and where its sampled token goes."""
+    from kvcache_b200.engine.runner import StepEntry
+    runner, config, _ = _runner(tmp_path, "B", max_tokens_per_step=2048, max_tokens_per_request=2048, num_pages=600)
+    runner.graph_after_sightings = 2
+    a, b, c = (runner.cache.admit() for _ in range(3))
+    runner.cache.extend([(a, 40), (b, 7)])
+    one = lambda slot: StepEntry(slot, [1], [0], (0.0, 0, 0))
+    portion = lambda slot, n, want=True: StepEntry(slot, list(range(n)), [n - 1] if want else [], (0.0, 0, 0))
+    assert runner._split([one(a), one(b)]) is None                      # no portion
+    assert runner._split([portion(c, 20)]) is None                      # no decoded token
+    assert runner._split([one(a), portion(c, 20)]) is None              # the shape's first sighting
+    parts = runner._split([one(a), portion(c, 20)])                     # its second
+    assert [[e.slot for e in part] for part in parts] == [[a], [c]]
+    assert runner._split([one(a), one(b), portion(c, 20)]) is None      # another offset of the sampled token: another shape
+    assert runner._split([one(a), portion(c, 20, want=False)]) is None  # nothing wanted: another shape
+    assert runner._split([one(a), portion(c, 21)]) is None              # another length
+    assert runner._split([portion(c, 20), one(a)]) is None              # decoded tokens must come first
+    assert runner._split([one(a), portion(c, 20), one(b)]) is None
+    runner._split([one(a), portion(c, 1200)])
+    assert runner._split([one(a), portion(c, 1200)]) is None            # too long to gain from it
+    assert runner._split([one(a), StepEntry(c, [3], [], None)]) is None  # a one-token portion that wants nothing
+    # the same length further into a prompt has longer work lists: another shape, until it has come twice too
+    runner.cache.extend([(c, 700)])
+    assert runner._split([one(a), portion(c, 20)]) is None
+    assert runner._split([one(a), portion(c, 20)]) is not None
+    assert runner._portion_key(0, 20, 1, True, 1) != runner._portion_key(700, 20, 1, True, 1)
