@@ -25,8 +25,12 @@ def main(argv=None) -> int:
     parser.add_argument("--block-size", type=int, default=16, help="tokens per cache page (reference: BLOCK = 16)")
     parser.add_argument("--graph", dest="graph", action="store_true", default=True)
     parser.add_argument("--no-graph", dest="graph", action="store_false")
+    parser.add_argument("--time-kernels", action="store_true",
+                        help="CUDA events around every kernel of the decode steps; a table per class of kernel on stderr (implies --no-graph)")
     args = parser.parse_args(argv)
 
+    if args.time_kernels:
+        args.graph = False
     prompt = [int(t) for t in sys.stdin.read().split()]
     if not prompt:
         print("no prompt ids on stdin", file=sys.stderr)
@@ -48,6 +52,11 @@ def main(argv=None) -> int:
         start = time.perf_counter()
         llm.step()
         times.append((time.perf_counter() - start) * 1e6)
+        if args.time_kernels and len(times) == 1:
+            llm.core.kernels.start_timing()          # from the first decoded token on
+    if args.time_kernels:
+        from ..kernels.timing import format_report
+        print(format_report(llm.core.kernels.stop_timing(), max(len(times) - 1, 1)), file=sys.stderr)
     llm.core.kernels.check_errors()
     print(" ".join(str(t) for t in request.output))
     decode = times[1:]                               # the first step is the prompt

@@ -44,8 +44,12 @@ def main(argv=None) -> int:
     parser.add_argument("--seed", type=int, default=0)
     parser.add_argument("--ignore-eos", action="store_true")
     parser.add_argument("--no-graph", dest="graph", action="store_false", default=True)
+    parser.add_argument("--time-kernels", action="store_true",
+                        help="CUDA events around every kernel; a table per class of kernel on stderr (implies --no-graph)")
     args = parser.parse_args(argv)
 
+    if args.time_kernels:
+        args.graph = False
     try:
         requests = parse_requests(sys.stdin.read())
     except ValueError as exc:
@@ -63,11 +67,16 @@ def main(argv=None) -> int:
                                       seed=args.seed))
     params = [SamplingParams(max_new_tokens=max_new, temperature=args.temperature, seed=args.seed + i,
                              ignore_eos=args.ignore_eos) for i, (max_new, _) in enumerate(requests)]
+    if args.time_kernels:
+        llm.core.kernels.start_timing()
     try:
         outputs = llm.generate([ids for _, ids in requests], params)
     except RequestRejected as exc:
         print(f"[serve] request refused: {exc}", file=sys.stderr)
         return 1
+    if args.time_kernels:
+        from ..kernels.timing import format_report
+        print(format_report(llm.core.kernels.stop_timing(), max(llm.last_stats.steps, 1)), file=sys.stderr)
     stats = llm.last_stats
     print(f"[serve] done. decode_steps={stats.steps} peak_batch={stats.peak_running} "
           f"prefill_tokens={stats.prefill_tokens} generated={stats.generated} preemptions={stats.preemptions} "

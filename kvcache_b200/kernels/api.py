@@ -216,6 +216,7 @@ class CudaKernels(KernelSet):
         self.launches = 0
         self._pinned_stream: Optional[_c_void_p] = None
         self._tma_cluster_capacity: Dict[tuple, int] = {}
+        self._timing = None
 
     # ---- helpers -----------------------------------------------------------
     def _stream(self) -> _c_void_p:
@@ -232,6 +233,20 @@ class CudaKernels(KernelSet):
             yield
         finally:
             self._pinned_stream = saved
+
+    def start_timing(self, hold_ms: float = 4.0) -> None:
+        """From now on every operator is bracketed by CUDA events and filed under its class (kernels/timing.py).
+        For steps launched kernel by kernel: graphs cannot hold the events.  `hold_ms`: how long the GPU is kept busy
+        before each step so that the host can queue the step's launches (0: not at all)."""
+        from .timing import KernelTiming
+        if self._timing is None:
+            self._timing = KernelTiming(self, hold_ms)
+            self._timing.start()
+
+    def stop_timing(self) -> Dict[str, dict]:
+        """Ends timing; returns {class: {"us", "bytes", "calls", "launches"}} summed over the calls since `start_timing`."""
+        timing, self._timing = self._timing, None
+        return timing.stop() if timing is not None else {}
 
     def check_errors(self) -> None:
         word = int(self.error_word.item())
