@@ -133,6 +133,8 @@ class CacheManager:
             self.lengths[slot] += count
 
     def release(self, slot: int) -> None:
+        if not self.slots.is_held(slot):
+            raise ValueError(f"slot {slot} is not in use")      # before any group is touched (a negative index would wrap)
         for g in self.groups:
             g.pages.release(slot)
         self.lengths[slot] = 0

@@ -81,6 +81,11 @@ def main(argv=None) -> int:
     print(f"[serve] done. decode_steps={stats.steps} peak_batch={stats.peak_running} "
           f"prefill_tokens={stats.prefill_tokens} generated={stats.generated} preemptions={stats.preemptions} "
           f"peak_blocks={stats.peak_pages} seconds={llm.last_seconds:.3f}", file=sys.stderr)
+    # The fields of the reference's EngineStats (src/include/engine.h:33-45), as its demo prints them.
+    print(f"[serve] stats iters={stats.steps} tokens={stats.generated} gpu_ms={stats.gpu_us / 1e3:.2f} "
+          f"wall_ms={stats.wall_us / 1e3:.2f} slot_steps={stats.slot_steps} useful_steps={stats.useful_steps} "
+          f"slot_util={stats.slot_utilisation:.3f} finished={stats.finished} avg_latency_ms={stats.avg_latency_us / 1e3:.2f} "
+          f"p99_latency_ms={stats.p99_latency_us / 1e3:.2f}", file=sys.stderr)
     for out in outputs:
         print(" ".join(str(t) for t in out))
     return 0

@@ -6,11 +6,13 @@ from __future__ import annotations
 import time
 from typing import Dict, List, Optional, Sequence, Union
 
+import torch
+
 from ..config.options import EngineOptions
 from ..sampling.params import SamplingParams
 from .core import EngineCore
 from .runner import StepEntry
-from .scheduler import Request, Scheduler
+from .scheduler import Request, Scheduler, TokensNeeded
 
 
 class LLM:
@@ -28,6 +30,7 @@ class LLM:
         self.config = self.core.config
         self.scheduler = self._new_scheduler()
         self._pending = None            # the step whose tokens have not been read yet
+        self._step_events = []          # (begin, end) CUDA events of steps whose device time has not been read yet
         self.pipelined = True           # plan and launch a step before reading the one before it
         self.last_stats = None
         self.last_seconds = 0.0
@@ -41,16 +44,30 @@ class LLM:
     def has_work(self) -> bool:
         return self.scheduler.has_work() or self._pending is not None
 
-    def _launch(self):
-        """Plans and launches one step; returns (pieces, a function that waits for its tokens) or None."""
-        pieces = self.scheduler.schedule()
+    def _launch(self, done: Optional[List[Request]] = None):
+        """Plans and launches one step; returns (pieces, a function that waits for its tokens) or None.
+        Requests that end because the pending step had to be read first are added to `done`."""
+        try:
+            pieces = self.scheduler.schedule()
+        except TokensNeeded:
+            finished = self._drain()          # pages are short: every token must be known before a request is preempted
+            if done is not None:
+                done += finished
+            pieces = self.scheduler.schedule()
         if not pieces:
             return None
         entries = [StepEntry(p.request.slot, p.tokens, [p.count - 1] if p.samples else [],
                              (p.request.params.temperature, p.request.params.seed, p.output_index),
                              token_from_last=p.token_from_last)
                    for p in pieces]
+        timed = self.core.device.type == "cuda"
+        if timed:
+            begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            begin.record()
         _, tokens = self.core.runner.step(entries, sample=True)
+        if timed:
+            end.record()
+            self._step_events.append((begin, end))
         self.scheduler.launched(pieces)
         count = sum(1 for p in pieces if p.samples)
         wait = self.core.runner.read_tokens_async(count) if count else (lambda: [])
@@ -69,7 +86,7 @@ class LLM:
         done: List[Request] = []
         if self._pending is not None and self._must_wait_before_planning():
             done += self._drain()
-        launched = self._launch()
+        launched = self._launch(done)
         done += self._drain()
         self._pending = launched
         if not self.pipelined:
@@ -81,7 +98,21 @@ class LLM:
             return []
         pieces, wait = self._pending
         self._pending = None
-        return self.scheduler.commit(pieces, wait())
+        tokens = wait()
+        self._read_step_times()
+        return self.scheduler.commit(pieces, tokens)
+
+    def _read_step_times(self, wait: bool = False) -> None:
+        """Adds the device time of the steps that have ended to the statistics (gpu_us of the reference's
+        EngineStats, src/include/engine.h:37); never waits for a step unless `wait`."""
+        while self._step_events:
+            begin, end = self._step_events[0]
+            if not end.query():
+                if not wait:
+                    return
+                end.synchronize()
+            self.scheduler.add_gpu_time(begin.elapsed_time(end) * 1e3)
+            self._step_events.pop(0)
 
     def generate(self, prompts: Sequence[Sequence[int]],
                  params: Union[SamplingParams, Sequence[SamplingParams], None] = None) -> List[List[int]]:
@@ -92,6 +123,7 @@ class LLM:
             raise ValueError("one SamplingParams per prompt, or one for all")
         self.scheduler = self._new_scheduler()
         self._pending = None
+        self._step_events = []
         requests = [self.scheduler.add_request(p, sp) for p, sp in zip(prompts, per_prompt)]
         start = time.perf_counter()
         while self.has_work():
@@ -101,6 +133,7 @@ class LLM:
                     and not self.scheduler.running):
                 raise RuntimeError("the scheduler made no progress (a waiting request fits neither slots nor pages)")
         self.core.kernels.check_errors()
+        self._read_step_times(wait=True)
         self.last_seconds = time.perf_counter() - start
         self.last_stats = self.scheduler.stats
         return [r.output for r in requests]

@@ -28,6 +28,8 @@ reason "out_of_pages".
 """
 from __future__ import annotations
 
+import bisect
+import time
 from collections import deque
 from dataclasses import dataclass, field
 from typing import Deque, Dict, List, Optional, Sequence, Tuple
@@ -40,6 +42,12 @@ WAITING, RUNNING, FINISHED = "waiting", "running", "finished"
 
 class RequestRejected(ValueError):
     pass
+
+
+class TokensNeeded(RuntimeError):
+    """`schedule()` found pages short while a step's tokens are still on their way.  Preempting recomputes a request
+    from its tokens and ending one hands its output out, so both need every token known: read the pending step
+    (`commit`) and call `schedule()` again.  Nothing was changed."""
 
 
 @dataclass
@@ -58,6 +66,8 @@ class Request:
     inflight: int = 0              # placeholders at the end of `output`: sampled, not yet known on the host
     last_index: int = -1           # where the step that sampled the newest placeholder put it (device order)
     finishing: bool = False        # its last token is on its way: it takes no part in further steps
+    arrival: float = 0.0           # seconds on the scheduler's clock when it was submitted
+    finished_at: Optional[float] = None
 
     @property
     def tokens(self) -> List[int]:
@@ -88,20 +98,32 @@ class Piece:
 
 @dataclass
 class SchedulerStats:
-    """The reference's EngineStats (src/include/engine.h:33-45) plus portion counts."""
-    steps: int = 0
+    """The reference's EngineStats (src/include/engine.h:33-45: iters, tokens, gpu_us, wall_us, slot_steps,
+    useful_steps, peak_blocks, finished, avg and p99 latency) plus portion counts and preemptions."""
+    steps: int = 0                 # iters
     decode_tokens: int = 0
     prefill_tokens: int = 0
-    generated: int = 0
+    generated: int = 0             # tokens
     finished: int = 0
     preemptions: int = 0
     peak_running: int = 0
-    peak_pages: int = 0
+    peak_pages: int = 0            # peak_blocks
+    gpu_us: float = 0.0            # device time of the steps, where the caller measures it (`add_gpu_time`)
+    wall_us: float = 0.0           # first submission to last end, on the scheduler's clock
+    slot_steps: int = 0            # sum over steps of the requests that held a slot
+    useful_steps: int = 0          # sum over steps of the requests that had tokens in the step
+    avg_latency_us: float = 0.0    # submission to end, over finished requests
+    p99_latency_us: float = 0.0
+
+    @property
+    def slot_utilisation(self) -> float:
+        return self.useful_steps / self.slot_steps if self.slot_steps else 0.0
 
 
 class Scheduler:
     def __init__(self, cache: CacheManager, *, max_running: int, max_tokens_per_step: int, chunk_size: int,
-                 max_model_len: int, admission: str = "reserve", default_eos: Sequence[int] = ()):
+                 max_model_len: int, admission: str = "reserve", default_eos: Sequence[int] = (),
+                 clock=time.perf_counter):
         if admission not in ("reserve", "optimistic"):
             raise ValueError(f"unknown admission policy '{admission}'")
         self.cache = cache
@@ -117,6 +139,9 @@ class Scheduler:
         self.reserved = [0] * len(cache.groups)
         self.stats = SchedulerStats()
         self._next_id = 0
+        self._clock = clock
+        self._first_arrival: Optional[float] = None
+        self._latencies: List[float] = []
 
     # ---- submission --------------------------------------------------------
     def _worst_case(self, total_tokens: int) -> List[int]:
@@ -134,7 +159,9 @@ class Scheduler:
         if any(w > self.cache.num_pages for w in worst):
             raise RequestRejected(f"the request can need {max(worst)} pages; the pool has {self.cache.num_pages}")
         eos = () if params.ignore_eos else (params.eos_token_ids if params.eos_token_ids is not None else self.default_eos)
-        request = Request(self._next_id, prompt, params, eos=tuple(eos))
+        request = Request(self._next_id, prompt, params, eos=tuple(eos), arrival=self._clock())
+        if self._first_arrival is None:
+            self._first_arrival = request.arrival
         self._next_id += 1
         self.waiting.append(request)
         return request
@@ -161,9 +188,23 @@ class Scheduler:
         self._give_back(request)
         self.running.remove(request)
         self.finished.append(request)
-        self.stats.finished += 1
+        stats = self.stats
+        stats.finished += 1
+        # Latency figures as the reference fills them (src/include/engine.h:47-54): mean, and the sample at 0.99 n.
+        request.finished_at = self._clock()
+        bisect.insort(self._latencies, (request.finished_at - request.arrival) * 1e6)
+        ordered = self._latencies
+        stats.avg_latency_us = sum(ordered) / len(ordered)
+        stats.p99_latency_us = ordered[min(int(len(ordered) * 0.99), len(ordered) - 1)]
+        stats.wall_us = (request.finished_at - self._first_arrival) * 1e6
+
+    def add_gpu_time(self, microseconds: float) -> None:
+        """Device time of a step, measured by the caller (the scheduler itself never touches the device)."""
+        self.stats.gpu_us += microseconds
 
     def _give_back(self, request: Request) -> None:
+        if request.slot < 0:
+            raise AssertionError(f"request {request.id} holds no slot")
         self.cache.release(request.slot)
         request.slot = -1
         if request.reserved is not None:
@@ -174,8 +215,8 @@ class Scheduler:
     def _preempt_newest(self, keep: Optional[Request] = None) -> Optional[Request]:
         """Gives back the newest running request's pages; it waits again, first in line."""
         for victim in reversed(self.running):
-            if victim is keep:
-                continue
+            if victim is keep or victim.inflight or victim.finishing:
+                continue                      # its tokens are not all known, or it ends with the token on its way
             self._give_back(victim)
             self.running.remove(victim)
             victim.state, victim.num_computed = WAITING, 0
@@ -231,6 +272,10 @@ class Scheduler:
             if count <= 0 or request.finishing:
                 index += 1
                 continue
+            if not fits(request, count) and self.has_inflight():
+                # Nothing has been changed yet: tokens in flight stay in flight during a plan, so no earlier
+                # request of this loop can have preempted or ended anything.
+                raise TokensNeeded("pages are short and a step's tokens have not been read yet")
             while not fits(request, count):
                 victim = self._preempt_newest(keep=request)
                 if victim is None:
@@ -275,6 +320,8 @@ class Scheduler:
         """The step is on its way to the device: positions advance, sampling requests get a placeholder
         for the token to come, and a request whose last token this is takes no part in later steps."""
         self.stats.steps += 1
+        self.stats.slot_steps += len(self.running)
+        self.stats.useful_steps += len(pieces)
         k = 0
         for piece in pieces:
             request = piece.request

@@ -190,3 +190,98 @@ def test_pipelined_steps_with_late_tokens():
     done = s.commit(third, [8])
     assert [r.id for r in done] == [0] and a.output == [5, 6, 8] and a.finish_reason == "length"
     assert not s.has_work() and s.cache.used_pages() == 0 and s.stats.generated == 4
+
+
+def _pipelined(s, token=7, limit=10_000):
+    """The entry point's loop on the host: a step is planned and launched before the tokens of the step before
+    it are read; a plan that finds pages short while tokens are in flight has them read first."""
+    from kvcache_b200.engine.scheduler import TokensNeeded
+    pending = None
+    steps = 0
+
+    def read():
+        nonlocal pending
+        if pending is not None:
+            pieces, pending = pending, None
+            s.commit(pieces, [token(p.request) if callable(token) else token for p in pieces if p.samples])
+    while s.has_work() or pending is not None:
+        try:
+            pieces = s.schedule()
+        except TokensNeeded:
+            read()
+            pieces = s.schedule()
+        if pieces:
+            s.cache.extend([(p.request.slot, p.count) for p in pieces])
+            s.launched(pieces)
+        read()
+        pending = pieces or None
+        steps += 1
+        assert steps < limit
+        for r in list(s.running) + list(s.waiting):
+            assert r.state != "waiting" or r.slot == -1
+    return steps
+
+
+@pytest.mark.parametrize("last_is_eos", [False, True])
+def test_optimistic_preemption_waits_for_tokens_in_flight(last_is_eos):
+    """20 pages of 4.  B brings a prompt of 70 tokens in portions of 32, A a prompt of 20.  When B's second portion
+    lacks pages (8 + 5 held, 8 wanted), A's first token is still on its way - and it is A's last one (its length
+    limit, or an end token).  A must not be preempted: it would be run again from a placeholder, and its end would
+    free a slot it no longer holds.  The plan asks for the pending tokens instead; A ends and its pages serve B."""
+    from kvcache_b200.engine.scheduler import TokensNeeded
+    s = _scheduler(_cache(num_pages=20, page=4, max_tokens=128), admission="optimistic", max_tokens_per_step=64,
+                   chunk_size=32, max_model_len=128, default_eos=(9,))
+    b = s.add_request([2] * 70, SamplingParams(max_new_tokens=4, ignore_eos=True))
+    a = s.add_request([1] * 20, SamplingParams(max_new_tokens=5) if last_is_eos else SamplingParams(max_new_tokens=1, ignore_eos=True))
+    first = s.schedule()
+    s.cache.extend([(p.request.slot, p.count) for p in first])
+    s.launched(first)
+    assert [(p.request.id, p.count, p.samples) for p in first] == [(0, 32, False), (1, 20, True)]
+    assert s.cache.used_pages() == 13 and a.inflight == 1
+    with pytest.raises(TokensNeeded):
+        s.schedule()
+    assert a.state == "running" and a.slot >= 0 and b.num_computed == 32 and s.stats.preemptions == 0
+    done = s.commit(first, [9 if last_is_eos else 7])
+    assert done == [a] and a.finish_reason == ("eos" if last_is_eos else "length") and a.output == [9 if last_is_eos else 7]
+    _pipelined(s)
+    assert b.output == [7] * 4 and s.cache.used_pages() == 0 and not s.running and not s.waiting
+    assert s.stats.preemptions == 0
+
+
+def test_optimistic_pipelined_generation_never_hands_out_a_placeholder():
+    """Random loads under optimistic admission with tokens always one step late: every request ends with its
+    full output, no placeholder, and every page comes back."""
+    import random
+    rng = random.Random(3)
+    for trial in range(20):
+        s = _scheduler(_cache(num_pages=12, page=4, slots=4, max_tokens=48), admission="optimistic", max_tokens_per_step=24,
+                       chunk_size=rng.choice([4, 8, 16]), max_model_len=48)
+        reqs = [s.add_request([1] * rng.randint(1, 20), SamplingParams(max_new_tokens=rng.randint(1, 12), ignore_eos=True))
+                for _ in range(rng.randint(2, 8))]
+        _pipelined(s)
+        for r in reqs:
+            assert r.state == "finished" and -1 not in r.output
+            assert len(r.output) == r.params.max_new_tokens or r.finish_reason == "out_of_pages"
+        assert s.cache.used_pages() == 0 and s.cache.slots.num_free == 4
+
+
+def test_statistics_of_the_references_engine():
+    """iters, tokens, slot and useful steps, latencies and wall time (src/include/engine.h:33-54), on a clock the
+    test owns: every step takes one tick."""
+    now = {"t": 0.0}
+    s = _scheduler(_cache(num_pages=64), max_running=2, max_tokens_per_step=4, chunk_size=4, clock=lambda: now["t"])
+    a = s.add_request([1] * 4, SamplingParams(max_new_tokens=2, ignore_eos=True))
+    b = s.add_request([1] * 8, SamplingParams(max_new_tokens=1, ignore_eos=True))
+    while s.has_work():
+        pieces = s.schedule()
+        s.cache.extend([(p.request.slot, p.count) for p in pieces])
+        now["t"] += 1.0
+        s.add_gpu_time(5.0)
+        s.update(pieces, [7 for p in pieces if p.samples])
+    # Steps: a's prompt (budget 4 leaves nothing for b, which is not yet admitted); a decodes + 3 tokens of b; b 3..7
+    # (a has ended); b's last token + sampling.
+    st = s.stats
+    assert st.steps == 4 and st.generated == 3 and st.finished == 2 and st.gpu_us == 20.0
+    assert a.finished_at == 2.0 and b.finished_at == 4.0
+    assert st.avg_latency_us == pytest.approx(3.0e6) and st.p99_latency_us == pytest.approx(4.0e6) and st.wall_us == pytest.approx(4.0e6)
+    assert st.slot_steps == 1 + 2 + 1 + 1 and st.useful_steps == 1 + 2 + 1 + 1 and st.slot_utilisation == 1.0
