@@ -49,7 +49,7 @@ class CacheManager:
         self.lengths = np.zeros(max_slots, dtype=np.int64)
         self.groups: List[CacheGroup] = []
         self.entry_group: Dict[int, Tuple[int, int]] = {}   # cache id -> (group index, index in group)
-        self.states: Dict[int, torch.Tensor] = {}
+        self.states: Dict[int, object] = {}      # cache id -> [slots, *shape] tensor, or {name: such a tensor}
         by_spec: Dict[PagedKVSpec, int] = {}
         for cache_id, entry in enumerate(entries):
             if entry.kv is not None:
@@ -61,8 +61,9 @@ class CacheManager:
                 self.entry_group[cache_id] = (g, len(self.groups[g].cache_ids))
                 self.groups[g].cache_ids.append(cache_id)
             if entry.state is not None and self.device is not None:
-                self.states[cache_id] = torch.zeros((max_slots, *entry.state.shape),
-                                                    dtype=TORCH_DTYPES[entry.state.dtype], device=self.device)
+                make = lambda spec: torch.zeros((max_slots, *spec.shape), dtype=TORCH_DTYPES[spec.dtype], device=self.device)
+                self.states[cache_id] = {name: make(spec) for name, spec in entry.state.items()} \
+                    if isinstance(entry.state, dict) else make(entry.state)
         if self.device is not None:
             for group in self.groups:
                 shape = (len(group.cache_ids), num_pages, group.spec.num_kv_heads, page_size, group.spec.head_dim)
@@ -74,9 +75,16 @@ class CacheManager:
         """Takes a slot for a new request: empty block tables, zeroed state, length 0."""
         slot = self.slots.alloc()
         self.lengths[slot] = 0
-        for state in self.states.values():
+        for state in self.state_tensors():
             state[slot].zero_()
         return slot
+
+    def state_tensors(self) -> List[torch.Tensor]:
+        """Every per-request state tensor of every cache entry."""
+        out: List[torch.Tensor] = []
+        for state in self.states.values():
+            out.extend(state.values() if isinstance(state, dict) else [state])
+        return out
 
     def length(self, slot: int) -> int:
         """Tokens of the request that steps have run so far (its next position)."""

@@ -30,6 +30,7 @@ class EngineOptions:
     use_graphs: bool = True                # CUDA graphs for steps of decoded tokens and of one portion of one prompt
     seed: int = 0
     device: str = "cuda:0"
+    strict_weights: bool = True            # False: tensors of the folder that the model does not use are no error
 
     def __post_init__(self) -> None:
         self.dtype = canonical_dtype(self.dtype)

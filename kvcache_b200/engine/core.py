@@ -37,7 +37,7 @@ class EngineCore:
             raise ValueError("give the cache a size: EngineOptions.num_pages or max_cached_tokens")
         max_len = min(max_len, num_pages * options.page_size)
         self.max_model_len = max_len
-        self.model = load_model(folder, options.dtype, self.device, max_positions=max_len)
+        self.model = load_model(folder, options.dtype, self.device, max_positions=max_len, strict=options.strict_weights)
         self.cache = CacheManager(self.model.cache_entries(), page_size=options.page_size, num_pages=num_pages,
                                   max_slots=options.max_running, max_tokens_per_request=max_len,
                                   dtype=options.dtype, device=self.device)

@@ -25,7 +25,7 @@ import numpy as np
 import torch
 
 from ..cache.manager import CacheManager
-from ..parts.base import StepBatch
+from ..parts.base import StepBatch, StepPlan, StepPlanner
 from ..parts.model import DecoderModel
 from .workspace import Workspace
 
@@ -46,60 +46,28 @@ def _align4(n: int) -> int:
     return (n + 3) & ~3
 
 
-PREFILL_TILE_ROWS = 64          # query rows of a prefill attention tile
-PREFILL_KEY_TILE = 64           # keys the kernel takes at a time
-PREFILL_MAX_UNITS = 16          # most units one tile may be cut into (csrc/attention_flash.cu)
-PREFILL_UNITS_WANTED = 256      # about this many units beyond one per tile, however long the prompts
-
-
-TC_TILE_ROWS = 128              # query rows of a tile of the tensor-memory attention kernel
-TC_MIN_KEY_TILES = 16           # a unit of that kernel has at least this many key tiles, unless its tile has fewer
-
-
-def plan_prefill_units(segments, tile_rows: int = PREFILL_TILE_ROWS, min_key_tiles: int = 4):
-    """The work list of prefill attention.  `segments`: (segment index, tokens cached before the step, tokens
-    it brings) for every segment of more than one token.  A tile is `tile_rows` consecutive rows of a segment;
-    a tile whose rows see many keys is cut into units of about equal numbers of key tiles, so that the blocks
-    of the grid - one per (unit, head) - all have about the same work although causal tiles do not.  Tiles
-    with the most keys come first.
-    Returns (int32 array [units, 8]: segment, first row, unit, units of the tile, tile id, first unit of the
-    tile, 0, 0; number of tiles)."""
-    tiles = []
-    for seg, start, count in segments:
-        for row0 in range(0, count, tile_rows):
-            rows = min(tile_rows, count - row0)
-            tiles.append((seg, row0, (start + row0 + rows - 1) // PREFILL_KEY_TILE + 1))
-    tiles.sort(key=lambda t: -t[2])
-    total = sum(k for _, _, k in tiles)
-    per_unit = max(min_key_tiles, -(-total // PREFILL_UNITS_WANTED))
-    units = []
-    for tile_id, (seg, row0, key_tiles) in enumerate(tiles):
-        nsplit = max(1, min(PREFILL_MAX_UNITS, -(-key_tiles // per_unit)))
-        first = len(units)
-        for split in range(nsplit):
-            units.append((seg, row0, split, nsplit, tile_id, first, 0, 0))
-    return np.asarray(units, dtype=np.int32).reshape(-1, 8), len(tiles)
-
-
 class StepLayout:
-    """Where each array of a step's metadata lies in the packed int32 buffer."""
+    """Where each array of a step's metadata lies in the packed int32 buffer: the step's own arrays, then the
+    lists of every planner (sized by the planner for T tokens in S segments), then the block-table rows."""
 
     SECTIONS = (("token_ids", "T", 1), ("positions", "T", 1), ("row_segment", "T", 1), ("seg_q_start", "S", 1),
                 ("seg_q_len", "S", 1), ("seg_kv_len", "S", 1), ("seg_slot", "S", 1), ("wanted_rows", "R", 1),
-                ("sample_temperature", "R", 1), ("sample_counter", "R", 1), ("sample_seed", "R", 2),
-                ("decode_items", "S", 1), ("prefill_tiles", "UNITS", 8), ("token_src", "T", 1), ("tc_units", "TC_UNITS", 8))
+                ("sample_temperature", "R", 1), ("sample_counter", "R", 1), ("sample_seed", "R", 2), ("token_src", "T", 1))
 
-    def __init__(self, T: int, S: int, R: int, table_width: int, num_groups: int):
+    def __init__(self, T: int, S: int, R: int, table_width: int, num_groups: int, planners: Sequence[StepPlanner] = ()):
         self.T, self.S, self.R = T, S, R
         self.table_width, self.num_groups = table_width, num_groups
-        sizes = {"T": T, "S": S, "R": R, "UNITS": 2 * (T // PREFILL_TILE_ROWS + S) + PREFILL_UNITS_WANTED,
-                 "TC_UNITS": 2 * (T // TC_TILE_ROWS + S) + PREFILL_UNITS_WANTED}
+        sizes = {"T": T, "S": S, "R": R}
         offset = 0
         self.offsets = {}
         for name, dim, words in self.SECTIONS:
             count = sizes[dim] * words
             self.offsets[name] = (offset, count)
             offset += _align4(count)
+        for planner in planners:
+            for name, count in planner.sections(T, S).items():
+                self.offsets[f"{planner.name}.{name}"] = (offset, count)
+                offset += _align4(count)
         self.table_offsets = []
         for _ in range(num_groups):
             self.table_offsets.append(offset)
@@ -132,7 +100,9 @@ class ModelRunner:
         self.graph_workspace = Workspace(self.device, row_capacity=self.max_segments)
         width = cache.max_pages_per_request
         groups = len(cache.groups)
-        capacity = StepLayout(self.max_tokens, self.max_segments, self.max_tokens, width, groups).total
+        # Work lists that the kernels of this model's mixers read: planned once a step, packed with the metadata.
+        self.planners: List[StepPlanner] = list(model.step_planners(kernels))
+        capacity = StepLayout(self.max_tokens, self.max_segments, self.max_tokens, width, groups, self.planners).total
         self._meta_device = torch.zeros(capacity, dtype=torch.int32, device=self.device)
         self._on_cuda = self.device.type == "cuda"
         self.use_graphs = use_graphs and self._on_cuda
@@ -180,7 +150,7 @@ class ModelRunner:
         self.cache.extend([(e.slot, n) for e, n in zip(entries, counts)])   # raises OutOfPages before any change
 
         R = sum(len(e.want) for e in entries)
-        layout = StepLayout(T, S, R, self.cache.max_pages_per_request, len(self.cache.groups))
+        layout = StepLayout(T, S, R, self.cache.max_pages_per_request, len(self.cache.groups), self.planners)
         index, staging = self._next_staging()
         host = staging.numpy()
         counts_np = np.asarray(counts, dtype=np.int32)
@@ -224,24 +194,13 @@ class ModelRunner:
             layout.view(host, "sample_seed").view(np.int64)[:] = seeds
         for g in range(len(self.cache.groups)):
             layout.table(host, g)[:] = self.cache.table_rows(g, slots)
-        if T == S:
-            n_items, n_units, n_tiles, n_tc, n_tc_tiles = S, 0, 0, 0, 0
-            layout.view(host, "decode_items")[:] = row_segment
-        else:
-            single = counts_np == 1
-            items = np.nonzero(single)[0].astype(np.int32)
-            n_items = len(items)
-            layout.view(host, "decode_items")[:n_items] = items
-            units, n_tiles = plan_prefill_units([(int(i), starts[i], counts[i]) for i in np.nonzero(~single)[0]])
-            n_units = len(units)
-            if n_units:
-                layout.view(host, "prefill_tiles")[:8 * n_units] = units.reshape(-1)
-            # The same segments as tiles of 128 rows for the tensor-memory kernel.
-            tc, n_tc_tiles = plan_prefill_units([(int(i), starts[i], counts[i]) for i in np.nonzero(~single)[0]],
-                                                TC_TILE_ROWS, TC_MIN_KEY_TILES)
-            n_tc = len(tc)
-            if n_tc:
-                layout.view(host, "tc_units")[:8 * n_tc] = tc.reshape(-1)
+        planned = []
+        for planner in self.planners:
+            arrays, plan_counts = planner.plan(starts_np, counts_np)
+            for name, array in arrays.items():
+                if len(array):
+                    layout.view(host, f"{planner.name}.{name}")[:len(array)] = array
+            planned.append((planner.name, {name: len(array) for name, array in arrays.items()}, plan_counts))
 
         dev = self._meta_device
         dev[:layout.total].copy_(staging[:layout.total], non_blocking=True)
@@ -257,9 +216,8 @@ class ModelRunner:
             seg_q_len=layout.view(dev, "seg_q_len"), seg_kv_len=layout.view(dev, "seg_kv_len"),
             seg_slot=layout.view(dev, "seg_slot"), wanted_rows=layout.view(dev, "wanted_rows"),
             token_src=layout.view(dev, "token_src"), last_tokens=self.last_tokens,
-            decode_items=layout.view(dev, "decode_items")[:n_items], num_decode_items=n_items,
-            prefill_tiles=layout.view(dev, "prefill_tiles")[:8 * n_units].view(-1, 8), num_prefill_units=n_units,
-            num_prefill_tiles=n_tiles, tc_units=layout.view(dev, "tc_units")[:8 * n_tc].view(-1, 8), num_tc_units=n_tc, num_tc_tiles=n_tc_tiles,
+            plans={name: StepPlan({key: layout.view(dev, f"{name}.{key}")[:length] for key, length in lengths.items()}, plan_counts)
+                   for name, lengths, plan_counts in planned},
             max_q_len=int(counts_np.max()), max_kv_len=int((starts_np + counts_np).max()),
             host={"counts": counts_np, "starts": starts_np, "q_start": q_start, "slots": slots})
         view = self.cache.step_view([layout.table(dev, g) for g in range(len(self.cache.groups))])
@@ -289,55 +247,65 @@ class ModelRunner:
 
     MAX_GRAPHS = 32
 
+    @staticmethod
+    def _plan_key(plans) -> tuple:
+        return tuple((name, tuple(sorted(counts.items()))) for name, counts in plans)
+
     def _graph_key(self, batch, sample: bool, token_offset: int = 0):
         """The key under which a step's launches can be replayed, or None.  Two kinds of steps have launches
         that depend on nothing but a few counts: steps of single decoded tokens (the batch size), and steps
-        that bring one portion of one prompt (its length and the lengths of the attention work lists, which
+        that bring one portion of one prompt (its length and the counts of the planners' work lists, which
         grow with what the prompt has cached).  Everything else - the ids, positions, block tables, the work
         lists themselves - is read from the step's metadata buffer, whose layout these counts fix."""
         if not self.use_graphs:
             return None
+        plans = self._plan_key((name, plan.counts) for name, plan in batch.plans.items())
         if sample and batch.num_tokens == batch.num_segments == batch.num_wanted:
-            return ("decode", batch.num_tokens, token_offset)
+            return ("decode", batch.num_tokens, token_offset, plans)
         if batch.num_segments == 1 and batch.num_tokens > 1:
-            return ("portion", batch.num_tokens, batch.num_wanted, sample, batch.num_prefill_units, batch.num_prefill_tiles,
-                    batch.num_tc_units, batch.num_tc_tiles, token_offset)
+            return ("portion", batch.num_tokens, batch.num_wanted, sample, token_offset, plans)
         return None
 
     def _portion_key(self, start: int, count: int, wanted: int, sample: bool, token_offset: int):
         """The key `_graph_key` gives a step that brings `count` tokens of one request which has `start` cached."""
-        units, tiles = plan_prefill_units([(0, start, count)])
-        tc, tc_tiles = plan_prefill_units([(0, start, count)], TC_TILE_ROWS, TC_MIN_KEY_TILES)
-        return ("portion", count, wanted, sample, len(units), tiles, len(tc), tc_tiles, token_offset)
+        starts, counts = np.asarray([start], dtype=np.int32), np.asarray([count], dtype=np.int32)
+        plans = self._plan_key((planner.name, planner.plan(starts, counts)[1]) for planner in self.planners)
+        return ("portion", count, wanted, sample, token_offset, plans)
 
     # Making a graph takes as long as a dozen steps, and prompts of odd lengths bring shapes that never come again: a
     # portion's shape is recorded once it has been seen this often.
     graph_after_sightings = 4
 
-    def _comes_again(self, key) -> bool:
-        """True if `key` has a graph, or has now been seen often enough to be given one."""
+    def _comes_again(self, key, count: bool = True) -> bool:
+        """True if `key` has a graph, or has been seen often enough to be given one.  `count`: this call is a
+        sighting of its own (False for a second look at a key within one step)."""
         if key in self._graphs:
             return True
         if len(self._portion_shapes_seen) > 4096:
             self._portion_shapes_seen.clear()
-        seen = self._portion_shapes_seen.get(key, 0) + 1
-        self._portion_shapes_seen[key] = seen
+        seen = self._portion_shapes_seen.get(key, 0) + (1 if count else 0)
+        if count:
+            self._portion_shapes_seen[key] = seen
         return seen >= self.graph_after_sightings
 
-    def _graph(self, key, batch, view, layout, sample: bool, token_offset: int = 0) -> _DecodeGraph:
+    def _graph(self, key, batch, view, layout, sample: bool, token_offset: int = 0):
+        """The recorded launches of a step with this key, and whether this call has just made (and thereby run) them.
+
+        A step is recorded the first time its key is wanted: it runs once, launched kernel by kernel, in the graph's
+        workspace - that sizes the buffers and is the step's one execution - and then its launches are recorded
+        without being run.  The caller replays the graph only from the next step on.  The step therefore takes effect
+        exactly once, whatever state its parts keep (keys and values, a mixer's running state, the sampled tokens
+        that the step itself may read its ids from).  A part's `forward` is called twice for it on the host; parts
+        keep no state of their own on the host."""
         found = self._graphs.pop(key, None)
         if found is not None:
             self._graphs[key] = found                         # the most recently used is the last to go
-            return found
+            return found, False
         if len(self._graphs) >= self.MAX_GRAPHS:
             self._graphs.pop(next(iter(self._graphs)))        # the one not used for longest
         ws = self.graph_workspace
         moved = ws.moved
-        # A first run outside the graph sizes the buffers.  It writes what the replay writes again - except that
-        # sampling overwrites `last_tokens`, which this very step may read its ids from: put them back.
-        saved = self.last_tokens.clone()
         self._forward(batch, view, layout, ws, sample, token_offset)
-        self.last_tokens.copy_(saved)
         if ws.moved != moved:
             self._graphs.clear()                              # a buffer moved: graphs that hold its old address go
         torch.cuda.synchronize(self.device)
@@ -351,7 +319,7 @@ class ModelRunner:
             ws.frozen = False
         found = _DecodeGraph(graph, logits, tokens, self.kernels.launches - before)
         self._graphs[key] = found
-        return found
+        return found, True
 
     def read_tokens_async(self, count: int):
         """Starts the copy of the last step's sampled tokens to the host; returns a function that waits for
@@ -383,16 +351,18 @@ class ModelRunner:
         self.steps_run += 1
         return (logits, tokens) if sample else logits
 
-    def _run(self, entries: Sequence[StepEntry], sample: bool, token_offset: int):
+    def _run(self, entries: Sequence[StepEntry], sample: bool, token_offset: int, counted: bool = False):
+        """`counted`: the step's shape has already been counted as a sighting in this step (by `_split`)."""
         batch, view, layout = self.prepare(entries)
         key = self._graph_key(batch, sample, token_offset)
-        if key is not None and key[0] == "portion" and not self._comes_again(key):
+        if key is not None and key[0] == "portion" and not self._comes_again(key, count=not counted):
             key = None
         if key is not None:
-            found = self._graph(key, batch, view, layout, sample, token_offset)
-            found.graph.replay()
+            found, ran = self._graph(key, batch, view, layout, sample, token_offset)
+            if not ran:
+                found.graph.replay()
+                self.graph_replays += 1
             self.kernels.launches += found.launches
-            self.graph_replays += 1
             return found.logits, found.tokens
         return self._forward(batch, view, layout, self.workspace, sample, token_offset)
 
@@ -428,7 +398,7 @@ class ModelRunner:
             raise AssertionError("unreachable: extend must have refused")
         offset = 0
         for part in parts:
-            self._run(part, True, offset)
+            self._run(part, True, offset, counted=True)
             offset += sum(len(e.want) for e in part)
         self.steps_run += 1
         return None, self.last_tokens[:offset]

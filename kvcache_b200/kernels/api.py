@@ -16,6 +16,7 @@ import torch
 
 from ..parts.base import PagedKVView, StepBatch
 from . import build
+from .attention_plan import PagedAttentionPlanner
 
 _c_int, _c_float, _c_void_p = ctypes.c_int, ctypes.c_float, ctypes.c_void_p
 
@@ -217,6 +218,7 @@ class CudaKernels(KernelSet):
         self._pinned_stream: Optional[_c_void_p] = None
         self._tma_cluster_capacity: Dict[tuple, int] = {}
         self._timing = None
+        self._attention_planner: Optional[PagedAttentionPlanner] = None
 
     # ---- helpers -----------------------------------------------------------
     def _stream(self) -> _c_void_p:
@@ -254,6 +256,12 @@ class CudaKernels(KernelSet):
             self.error_word.zero_()
             reasons = [text for bit, text in DEVICE_ERRORS.items() if word & bit]
             raise KernelError("a kernel flagged bad input: " + "; ".join(reasons))
+
+    def paged_attention_planner(self) -> PagedAttentionPlanner:
+        """The work lists `paged_attention` and `rope_append_attention` read from `StepBatch.plans` (one planner for all layers)."""
+        if self._attention_planner is None:
+            self._attention_planner = PagedAttentionPlanner()
+        return self._attention_planner
 
     # ---- operators ---------------------------------------------------------
     def embed(self, table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor, src: Optional[torch.Tensor] = None,
@@ -415,9 +423,10 @@ class CudaKernels(KernelSet):
         False (and does nothing) otherwise; the caller then makes the two calls."""
         spec = kv.spec
         D, Hkv, n = spec.head_dim, spec.num_kv_heads, batch.num_segments
+        plan = batch.plans.get(PagedAttentionPlanner.name)
         if not (self.fused_rope_min_requests is not None and n >= self.fused_rope_min_requests
-                and self.flash_attention and qkv.dtype == torch.bfloat16 and kv.writes
-                and batch.num_tokens == n and batch.num_decode_items == n and num_heads // Hkv <= 16
+                and self.flash_attention and qkv.dtype == torch.bfloat16 and kv.writes and plan is not None
+                and batch.num_tokens == n and plan.counts["decode_items"] == n and num_heads // Hkv <= 16
                 and self._tma_decode(D, kv) and (cos is None or cos.shape[1] <= D // 2)):
             return False
         lib = self._flash_library(D)
@@ -437,34 +446,37 @@ class CudaKernels(KernelSet):
         T = q.shape[0]
         spec = kv.spec
         D, Hkv = spec.head_dim, spec.num_kv_heads
+        plan = batch.plans.get(PagedAttentionPlanner.name)
         if (self.flash_attention and q.dtype == torch.bfloat16 and D % 16 == 0 and D <= 128 and num_heads // Hkv <= 16
-                and workspace is not None and batch.decode_items is not None):
+                and workspace is not None and plan is not None):
             lib = self._flash_library(D)
-            if (batch.num_tc_units and self.tc_attention_min_rows is not None and D in (64, 128)
+            counts, lists = plan.counts, plan.arrays
+            if (counts["tc_units"] and self.tc_attention_min_rows is not None and D in (64, 128)
                     and 8 <= kv.page_size <= 64 and batch.max_q_len >= self.tc_attention_min_rows):
                 tc = self._attn_tc.get(D)
                 if tc is None:
                     tc = self._attn_tc[D] = _Library("attention_tc", f"d{D}", [f"-DKVB_HEAD_DIM={D}"])
-                units = batch.num_tc_units
+                units = counts["tc_units"]
                 scratch = workspace.buffer("attn.tc_scratch", (units * num_heads * 128 * (D + 2),), torch.float32)
-                tickets = workspace.zeros("attn.tc_tickets", (max(batch.num_tc_tiles, 1) * num_heads,), torch.int32)
+                tickets = workspace.zeros("attn.tc_tickets", (max(counts["tc_tiles"], 1) * num_heads,), torch.int32)
                 self.launches += 1
                 _check(tc.kvb_attention_tc(
                     _ptr(q), _ptr(out), _ptr(kv.k_pages), _ptr(kv.v_pages), kv.k_pages.shape[0], _ptr(kv.block_table),
-                    kv.block_table.shape[1], _ptr(batch.tc_units), units, _ptr(scratch), _ptr(tickets),
+                    kv.block_table.shape[1], _ptr(lists["tc_units"]), units, _ptr(scratch), _ptr(tickets),
                     _ptr(batch.seg_q_start), _ptr(batch.seg_q_len), _ptr(batch.seg_kv_len), T, num_heads, Hkv, kv.page_size,
                     spec.window or 0, float(scale), _ptr(self.error_word), self._stream()), "attention_tc")
-            elif batch.num_prefill_units:
-                units = batch.num_prefill_units
+            elif counts["prefill_units"]:
+                units = counts["prefill_units"]
                 scratch = workspace.buffer("attn.prefill_scratch", (units * num_heads * 64 * (D + 2),), torch.float32)
-                tickets = workspace.zeros("attn.prefill_tickets", (max(batch.num_prefill_tiles, 1) * num_heads,), torch.int32)
+                tickets = workspace.zeros("attn.prefill_tickets", (max(counts["prefill_tiles"], 1) * num_heads,), torch.int32)
                 self.launches += 1
                 _check(lib.kvb_flash_prefill(
                     _ptr(q), _ptr(out), _ptr(kv.k_pages), _ptr(kv.v_pages), _ptr(kv.block_table), kv.block_table.shape[1],
-                    _ptr(batch.prefill_tiles), units, _ptr(batch.seg_q_start), _ptr(batch.seg_q_len),
+                    _ptr(lists["prefill_units"]), units, _ptr(batch.seg_q_start), _ptr(batch.seg_q_len),
                     _ptr(batch.seg_kv_len), _ptr(scratch), _ptr(tickets), num_heads, Hkv, kv.page_size, spec.window or 0,
                     float(scale), self._stream()), "flash_prefill")
-            n = batch.num_decode_items
+            n = counts["decode_items"]
+            items = lists["decode_items"]
             if n:
                 # Sized by the longest request the block table allows, not by this step's lengths, so that the
                 # split (and with it the rounding) is the same in every step and under a CUDA graph.
@@ -477,14 +489,14 @@ class CudaKernels(KernelSet):
                         _check(lib.kvb_flash_decode_tma(
                             _ptr(q), _ptr(out), _ptr(kv.k_pages), _ptr(kv.v_pages), kv.k_pages.shape[0],
                             _ptr(kv.block_table), kv.block_table.shape[1],
-                            _ptr(None if n == batch.num_segments else batch.decode_items), n,   # every segment, in order: no list
+                            _ptr(None if n == batch.num_segments else items), n,   # every segment, in order: no list
                             _ptr(batch.seg_q_start), _ptr(batch.seg_q_len), _ptr(batch.seg_kv_len), num_heads, Hkv,
                             kv.page_size, spec.window or 0, nsplit, float(scale), None, None, None, None, 0, 0,
                             _ptr(self.error_word), self._stream()), "flash_decode_tma")
                         return
                     _check(lib.kvb_flash_decode_cluster(
                         _ptr(q), _ptr(out), _ptr(kv.k_pages), _ptr(kv.v_pages), _ptr(kv.block_table),
-                        kv.block_table.shape[1], _ptr(batch.decode_items), n, _ptr(batch.seg_q_start),
+                        kv.block_table.shape[1], _ptr(items), n, _ptr(batch.seg_q_start),
                         _ptr(batch.seg_q_len), _ptr(batch.seg_kv_len), num_heads, Hkv, kv.page_size, spec.window or 0,
                         nsplit, float(scale), self._stream()), "flash_decode_cluster")
                     return
@@ -494,7 +506,7 @@ class CudaKernels(KernelSet):
                 self.launches += 1
                 _check(lib.kvb_flash_decode(
                     _ptr(q), _ptr(out), _ptr(kv.k_pages), _ptr(kv.v_pages), _ptr(kv.block_table), kv.block_table.shape[1],
-                    _ptr(batch.decode_items), n, _ptr(batch.seg_q_start), _ptr(batch.seg_q_len), _ptr(batch.seg_kv_len),
+                    _ptr(items), n, _ptr(batch.seg_q_start), _ptr(batch.seg_q_len), _ptr(batch.seg_kv_len),
                     _ptr(scratch), _ptr(tickets), num_heads, Hkv, kv.page_size, spec.window or 0, nsplit, float(scale),
                     self._stream()), "flash_decode")
             return

@@ -40,7 +40,10 @@ def build_qwen2(config: Qwen2Config, dtype: str = "bfloat16", device: str = "cud
         embed_name="model.embed_tokens.weight",
         head_name=None if c.tie_word_embeddings else "lm_head.weight",
         blocks=blocks, schedule=[LayerCall(i, i) for i in range(c.num_hidden_layers)],
-        final_norm=RMSNorm(c.hidden_size, c.rms_norm_eps, "model.norm.weight"), position=position)
+        final_norm=RMSNorm(c.hidden_size, c.rms_norm_eps, "model.norm.weight"), position=position,
+        # Checkpoints may carry the rotation's frequencies as a buffer, and the reference's exporter stores the embedding
+        # a second time as lm_head.weight when the head is tied (tools/dump_weights.py:24-26): neither is used.
+        ignorable_tensors=["*.rotary_emb.inv_freq"] + (["lm_head.weight"] if c.tie_word_embeddings else []))
 
 
 register_architecture(QWEN2_ARCHITECTURE, Qwen2Config, build_qwen2, replace=True)

@@ -65,6 +65,10 @@ class GQAAttention(Mixer):
     def cache_spec(self) -> PagedKVSpec:
         return PagedKVSpec(self.num_kv_heads, self.head_dim, self.window)
 
+    def step_planners(self, kernels):
+        planner = getattr(kernels, "paged_attention_planner", None)
+        return () if planner is None else (planner(),)
+
     def forward(self, x: torch.Tensor, ctx: LayerContext) -> torch.Tensor:
         T = x.shape[0]
         k, ws = ctx.kernels, ctx.workspace

@@ -10,14 +10,15 @@ It declares the checkpoint tensors it wants (`tensor_specs`), takes them
                       `rotation()` for encodings that rotate queries and keys.
 * `Mixer`           - `forward(x, ctx) -> delta`; declares the cache it needs with
                       `cache_spec()` (pages of keys and values) and `state_spec()`
-                      (per-request state of fixed size).
+                      (per-request state of fixed size, one tensor or several by name),
+                      and the work lists its kernels want with `step_planners()`.
 * `FeedForward`     - `forward(x, ctx) -> delta`.
 * `Block`           - the arrangement of the four in one layer.
 """
 from __future__ import annotations
 
 from dataclasses import dataclass, field
-from typing import Any, Dict, Mapping, Optional, Tuple
+from typing import Any, Dict, Mapping, Optional, Sequence, Tuple
 
 import torch
 
@@ -42,7 +43,8 @@ class PagedKVSpec:
 
 @dataclass(frozen=True)
 class StateSpec:
-    """Per-request state of fixed size: one `shape`-sized tensor per live request, zeroed at admission."""
+    """Per-request state of fixed size: one `shape`-sized tensor per live request, zeroed at admission.
+    A mixer with several states (a convolution's tail beside a recurrent state) returns a dict of them by name."""
     shape: Tuple[int, ...]
     dtype: str = "float32"
 
@@ -56,6 +58,36 @@ class PagedKVView:
     block_table: torch.Tensor        # int32 [segments capacity, pages per request]; -1 where no page is held
     page_size: int
     writes: bool = True              # False: the call reads what another call wrote
+
+
+class StepPlanner:
+    """Work lists a kernel wants for every step, made on the host from the lengths of the step's segments.
+
+    Kernels that cut a step's rows into tiles, units or chunks of their own size need lists that say which block
+    does what.  The step function knows nothing of those sizes: the kernel set hands the mixers that use it a
+    planner, the runner calls `plan` once a step, packs the arrays into the step's metadata with everything else
+    (one copy to the device) and hands the device views back in `StepBatch.plans[name]`.
+
+    `sections(T, S)`: the most int32 words each named list can take in a step of T tokens in S segments (the
+    layout of the metadata buffer depends on T, S and nothing else, so that a recorded CUDA graph finds every list
+    where it was).  `plan(starts, counts)`: for segments that have `starts[i]` tokens cached and bring `counts[i]`,
+    the lists (flat int32 arrays) and the counts that fix the launches' shapes - those counts are part of the key
+    under which the step's launches may be replayed.
+    """
+    name: str = ""
+
+    def sections(self, num_tokens: int, num_segments: int) -> Dict[str, int]:
+        raise NotImplementedError
+
+    def plan(self, starts, counts) -> Tuple[Dict[str, Any], Dict[str, int]]:
+        raise NotImplementedError
+
+
+@dataclass
+class StepPlan:
+    """A planner's lists for one step, on the device, and the counts that go with them."""
+    arrays: Dict[str, torch.Tensor]
+    counts: Dict[str, int]
 
 
 @dataclass
@@ -75,16 +107,8 @@ class StepBatch:
     wanted_rows: torch.Tensor        # int32 [R]   rows whose logits are returned
     token_src: Optional[torch.Tensor] = None     # int32 [T]: >= 0: the row's token is last_tokens[token_src[r]]
     last_tokens: Optional[torch.Tensor] = None   # int32: tokens the previous step sampled, still on the device
-    # Attention work lists: segments that bring one token, and, for the segments that bring more, units of
-    # 64-row tiles (see engine.runner.plan_prefill_units).
-    decode_items: Optional[torch.Tensor] = None    # int32 [num_decode_items]
-    prefill_tiles: Optional[torch.Tensor] = None   # int32 [num_prefill_units, 8]
-    num_decode_items: int = 0
-    num_prefill_units: int = 0
-    num_prefill_tiles: int = 0
-    tc_units: Optional[torch.Tensor] = None        # int32 [num_tc_units, 8]: the same segments as units of 128-row tiles
-    num_tc_units: int = 0
-    num_tc_tiles: int = 0
+    # Work lists that kernels asked for (see StepPlanner), by the planner's name.
+    plans: Dict[str, "StepPlan"] = field(default_factory=dict)
     max_q_len: int = 1               # host copies, for launch shapes
     max_kv_len: int = 1
     host: Dict[str, Any] = field(default_factory=dict)
@@ -97,7 +121,7 @@ class LayerContext:
     kernels: Any                     # the kernel set (see kvcache_b200.kernels.api)
     workspace: Any                   # named scratch buffers that outlive the step
     kv: Optional[PagedKVView] = None
-    state: Optional[torch.Tensor] = None   # [slots, *StateSpec.shape]
+    state: Any = None                # [slots, *StateSpec.shape], or a dict of such tensors by the states' names
     call_index: int = 0
 
 
@@ -146,8 +170,13 @@ class Mixer(Part):
     def cache_spec(self) -> Optional[PagedKVSpec]:
         return None
 
-    def state_spec(self) -> Optional[StateSpec]:
+    def state_spec(self):
+        """None, one `StateSpec`, or `{name: StateSpec}` for a mixer that keeps several states per request."""
         return None
+
+    def step_planners(self, kernels: Any) -> Sequence[StepPlanner]:
+        """The planners whose work lists this mixer's kernels read (asked of the kernel set, which owns the tiling)."""
+        return ()
 
     def forward(self, x: torch.Tensor, ctx: LayerContext) -> torch.Tensor:
         raise NotImplementedError

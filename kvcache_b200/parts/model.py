@@ -28,13 +28,13 @@ class LayerCall:
 class CacheEntry:
     """What one cache id needs: pages of keys and values and/or per-request state."""
     kv: Optional[PagedKVSpec]
-    state: Optional[StateSpec]
+    state: Any                     # None, a StateSpec, or {name: StateSpec}
 
 
 class DecoderModel:
     def __init__(self, *, config: Any, dtype: str, vocab_size: int, width: int, embed_name: str,
                  head_name: Optional[str], blocks: Sequence[Block], schedule: Sequence[LayerCall],
-                 final_norm: Norm, position: Optional[PositionEncoding] = None):
+                 final_norm: Norm, position: Optional[PositionEncoding] = None, ignorable_tensors: Sequence[str] = ()):
         self.config = config
         self.dtype_name = dtype
         self.dtype = TORCH_DTYPES[dtype]
@@ -44,6 +44,8 @@ class DecoderModel:
         self.schedule = list(schedule)
         self.final_norm = final_norm
         self.position = position
+        # Names (shell patterns) of tensors that checkpoints of this architecture may carry without the model using them.
+        self.ignorable_tensors = tuple(ignorable_tensors)
         self.embed: Optional[torch.Tensor] = None
         self.head: Optional[torch.Tensor] = None
         self.device: Optional[torch.device] = None
@@ -112,6 +114,14 @@ class DecoderModel:
             mixer = self.blocks[self._writers[cache_id]].mixer
             entries.append(CacheEntry(mixer.cache_spec(), mixer.state_spec()))
         return entries
+
+    def step_planners(self, kernels: Any) -> List[Any]:
+        """The planners of all mixers' kernels, each once (by name), in the order of the blocks."""
+        found: Dict[str, Any] = {}
+        for block in self.blocks:
+            for planner in block.mixer.step_planners(kernels):
+                found.setdefault(planner.name, planner)
+        return list(found.values())
 
     # ---- one step ----------------------------------------------------------
     def forward(self, batch: StepBatch, kernels: Any, workspace: Any, cache: Any) -> torch.Tensor:

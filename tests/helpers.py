@@ -53,14 +53,14 @@ def paged_scenario(segments, *, num_kv_heads: int, head_dim: int, page_size: int
     row_seg = np.concatenate([np.full(n, i) for i, (s, n) in enumerate(segments)]).astype(np.int32)
     q_start = np.cumsum([0] + [n for _, n in segments[:-1]]).astype(np.int32)
     dev = lambda a: torch.as_tensor(a, dtype=torch.int32).to(device)
-    items = [i for i, (_, n) in enumerate(segments) if n == 1]
-    from kvcache_b200.engine.runner import plan_prefill_units
-    units, n_tiles = plan_prefill_units([(i, s, n) for i, (s, n) in enumerate(segments) if n > 1])
-    tc, n_tc_tiles = plan_prefill_units([(i, s, n) for i, (s, n) in enumerate(segments) if n > 1], 128, tc_min_key_tiles)
+    from kvcache_b200.kernels.attention_plan import PagedAttentionPlanner, plan_prefill_units
+    from kvcache_b200.parts.base import StepPlan
+    arrays, counts = PagedAttentionPlanner().plan(np.asarray([s for s, _ in segments]), np.asarray([n for _, n in segments]))
+    if tc_min_key_tiles != 16 and "tc_units" in arrays:
+        tc, counts["tc_tiles"] = plan_prefill_units([(i, s, n) for i, (s, n) in enumerate(segments) if n > 1], 128, tc_min_key_tiles)
+        arrays["tc_units"], counts["tc_units"] = tc.reshape(-1), len(tc)
     batch = StepBatch(
-        tc_units=dev(tc), num_tc_units=len(tc), num_tc_tiles=n_tc_tiles,
-        decode_items=dev(items), num_decode_items=len(items),
-        prefill_tiles=dev(units), num_prefill_units=len(units), num_prefill_tiles=n_tiles,
+        plans={PagedAttentionPlanner.name: StepPlan({k: dev(v) for k, v in arrays.items()}, counts)},
         num_tokens=T, num_segments=S, num_wanted=0, token_ids=dev(np.zeros(T)), positions=dev(pos),
         row_segment=dev(row_seg), seg_q_start=dev(q_start), seg_q_len=dev([n for _, n in segments]),
         seg_kv_len=dev([s + n for s, n in segments]), seg_slot=dev(np.arange(S)), wanted_rows=dev([]),

@@ -56,7 +56,7 @@ def test_mixed_with_page_reuse(tmp_path, name):
 
 def test_prefill_work_list():
     """Tiles of 64 rows; long tiles are cut into units of about equal numbers of key tiles."""
-    from kvcache_b200.engine.runner import plan_prefill_units
+    from kvcache_b200.kernels.attention_plan import plan_prefill_units
     units, n_tiles = plan_prefill_units([(0, 0, 2048), (3, 100, 2)])
     assert n_tiles == 33 and units.shape[1] == 8
     by_tile = {}
@@ -82,10 +82,12 @@ def test_which_mixed_steps_are_run_in_parts(tmp_path):
     """The runner's decision to run a sampling step as its parts (decoded tokens, then each portion alone): only where
     decoded tokens come first and beside portions of at least two and at most SPLIT_MAX_PORTION tokens whose shapes
     have come `graph_after_sightings` times (so that their launches can be replayed); a portion's shape is its length,
-    the number of wanted places, the lengths of its attention work lists and where its sampled token goes."""
+    the number of wanted places, the counts of its planners' work lists and where its sampled token goes."""
     from kvcache_b200.engine.runner import StepEntry
     runner, config, _ = _runner(tmp_path, "B", max_tokens_per_step=2048, max_tokens_per_request=2048, num_pages=600)
     runner.graph_after_sightings = 2
+    from kvcache_b200.kernels.attention_plan import PagedAttentionPlanner
+    runner.planners = [PagedAttentionPlanner()]                         # the work lists of the CUDA kernel set's attention
     a, b, c = (runner.cache.admit() for _ in range(3))
     runner.cache.extend([(a, 40), (b, 7)])
     one = lambda slot: StepEntry(slot, [1], [0], (0.0, 0, 0))

@@ -18,7 +18,7 @@ DEV = "cuda:0"
 def _define():
     from kvcache_b200.config.base import KeyReader, ModelConfig
     from kvcache_b200.parts import (DecoderModel, FeedForward, GatedMLP, GQAAttention, LayerCall, Mixer, PositionEncoding,
-                                    PreNormBlock, RMSNorm, StateSpec)
+                                    PreNormBlock, RMSNorm, StateSpec, StepPlanner)
     from kvcache_b200.weights import TensorSpec
 
     @dataclass(frozen=True)
@@ -41,9 +41,25 @@ def _define():
             return {"architectures": [self.architecture], "width": self.width, "vocab": self.vocab, "inner": self.inner,
                     "decay": self.decay, "eps": self.eps}
 
+    class FirstRows(StepPlanner):
+        """A work list of the toy mixer's own: the first row of every segment, and the longest segment as the count
+        that fixes how many passes the mixer makes.  The runner packs it like the attention kernels' lists."""
+        name = "toy_first_rows"
+
+        def sections(self, num_tokens, num_segments):
+            return {"first_rows": num_segments}
+
+        def plan(self, starts, counts):
+            import numpy as np
+            first = np.zeros(len(counts), dtype=np.int32)
+            np.cumsum(np.asarray(counts)[:-1], out=first[1:])
+            return {"first_rows": first}, {"longest": int(max(counts))}
+
     class RunningMean(Mixer):
-        """delta[r] = W . s[r], s[r] = decay * s[r - 1] + x[r] over the request's rows: a state of fixed size that
-        has to survive from step to step, in the slot the cache manager gave the request."""
+        """delta[r] = W . (s[r] / n[r]) with s[r] = decay * s[r - 1] + x[r] and n[r] = decay * n[r - 1] + 1 over the
+        request's rows: two states of fixed size that have to survive from step to step, in the slot the cache manager
+        gave the request.  Everything runs on the device from the step's device arrays, so that a step can be recorded
+        in a CUDA graph and replayed."""
 
         def __init__(self, width, decay, prefix, dtype):
             self.width, self.decay, self.prefix, self.dtype = width, decay, prefix, dtype
@@ -56,17 +72,28 @@ def _define():
             self.w = tensors[self.prefix + "mix.weight"].to(torch.float32).to(device)
 
         def state_spec(self):
-            return StateSpec((self.width,), "float32")
+            return {"sum": StateSpec((self.width,), "float32"), "weight": StateSpec((1,), "float32")}
+
+        def step_planners(self, kernels):
+            return (FirstRows(),)
 
         def forward(self, x, ctx):
-            out = torch.empty_like(x)
-            host = ctx.batch.host
-            for start, count, slot in zip(host["q_start"], host["counts"], host["slots"]):
-                s = ctx.state[slot]
-                for r in range(start, start + count):
-                    s.mul_(self.decay).add_(x[r].float())
-                    out[r] = (self.w @ s).to(x.dtype)
-            return out
+            b, plan = ctx.batch, ctx.batch.plans["toy_first_rows"]
+            T = x.shape[0]
+            slots = b.seg_slot.long()
+            s, n = ctx.state["sum"].index_select(0, slots), ctx.state["weight"].index_select(0, slots)
+            xf = torch.cat([x.float(), x.new_zeros((1, self.width), dtype=torch.float32)])
+            out = torch.zeros((T + 1, self.width), dtype=torch.float32, device=x.device)     # row T takes what no segment owns
+            first = plan.arrays["first_rows"].long()
+            for j in range(plan.counts["longest"]):
+                live = (b.seg_q_len > j)[:, None]
+                rows = torch.where(live[:, 0], first + j, torch.full_like(first, T))
+                s = torch.where(live, self.decay * s + xf[rows], s)
+                n = torch.where(live, self.decay * n + 1.0, n)
+                out.index_copy_(0, rows, (s / n.clamp(min=1e-30)) @ self.w.t())
+            ctx.state["sum"].index_copy_(0, slots, s)
+            ctx.state["weight"].index_copy_(0, slots, n)
+            return out[:T].to(x.dtype)
 
     class TopOneExperts(FeedForward):
         """delta[r] = p_e * Wout_e relu(Win_e x[r]) with e = argmax of the router's logits (float32) and p_e its
@@ -91,13 +118,13 @@ def _define():
         def forward(self, x, ctx):
             xf = x.float()
             prob = torch.softmax(xf @ self.router.t(), dim=-1)
-            chosen = prob.argmax(dim=-1)
-            out = torch.empty_like(xf)
-            for e in range(self.experts):
-                rows = (chosen == e).nonzero().flatten()
-                if len(rows):
-                    out[rows] = prob[rows, e, None] * (torch.relu(xf[rows] @ self.w_in[e].t()) @ self.w_out[e].t())
-            return out.to(x.dtype)
+            chosen = prob.argmax(dim=-1, keepdim=True)                                  # [T, 1]
+            # Every expert on every row, then the chosen one is picked: shapes that do not depend on the routing, so
+            # that the step can be recorded in a CUDA graph.
+            hidden = torch.relu(torch.einsum("tw,eiw->tei", xf, self.w_in))
+            every = torch.einsum("tei,ewi->tew", hidden, self.w_out)
+            picked = every.gather(1, chosen[:, :, None].expand(-1, 1, self.width)).squeeze(1)
+            return (prob.gather(1, chosen) * picked).to(x.dtype)
 
     class AddedSinusoid(PositionEncoding):
         """Adds sin(pos / 10) to every element of the embedded row: an encoding that acts at the embedding."""
@@ -129,10 +156,11 @@ def _plain(config, w, tokens):
     T = len(tokens)
     x = W["emb"][torch.tensor(tokens)] + torch.sin(torch.arange(T).double() / 10.0)[:, None]
     n = plain.rms_norm(x, W["l0.n1"], config["eps"])
-    s, mixed = torch.zeros(config["width"], dtype=torch.float64), []
+    s, weight, mixed = torch.zeros(config["width"], dtype=torch.float64), 0.0, []
     for r in range(T):
         s = config["decay"] * s + n[r]
-        mixed.append(W["l0.mix.weight"] @ s)
+        weight = config["decay"] * weight + 1.0
+        mixed.append(W["l0.mix.weight"] @ (s / weight))
     x = x + torch.stack(mixed)
     x = x + plain.swiglu(plain.rms_norm(x, W["l0.n2"], config["eps"]), W["l0.f.gate_proj.weight"], W["l0.f.up_proj.weight"],
                          W["l0.f.down_proj.weight"])
@@ -152,7 +180,8 @@ def _plain(config, w, tokens):
     return plain.linear(plain.rms_norm(x, W["final"], config["eps"]), W["emb"])
 
 
-def test_toy_architecture_with_state_runs_through_the_unchanged_engine(tmp_path):
+@pytest.mark.parametrize("use_graphs", [False, True])
+def test_toy_architecture_with_state_runs_through_the_unchanged_engine(tmp_path, use_graphs):
     from safetensors.torch import load_file
     from kvcache_b200.config import EngineOptions, register_architecture, unregister_architecture
     from kvcache_b200.engine.core import EngineCore
@@ -167,30 +196,44 @@ def test_toy_architecture_with_state_runs_through_the_unchanged_engine(tmp_path)
             assert json.load(fh)["architectures"] == ["ToyRunningMeanLM"]
         weights = load_file(os.path.join(folder, "model.safetensors"))
         core = EngineCore(folder, EngineOptions(dtype="float32", page_size=8, num_pages=16, max_running=2,
-                                                max_tokens_per_step=64, max_model_len=64, use_graphs=False))
+                                                max_tokens_per_step=64, max_model_len=64, use_graphs=use_graphs))
+        core.runner.graph_after_sightings = 1          # a portion's launches are recorded the first time its shape comes
         entries = core.model.cache_entries()
-        assert entries[0].kv is None and entries[0].state.shape == (32,)       # the toy mixer: state, no pages
-        assert entries[1].kv is not None and entries[1].state is None          # attention: pages, no state
-        assert core.cache.states[0].shape == (2, 32)
+        assert entries[0].kv is None and set(entries[0].state) == {"sum", "weight"}   # the toy mixer: two states, no pages
+        assert entries[1].kv is not None and entries[1].state is None                 # attention: pages, no state
+        assert core.cache.states[0]["sum"].shape == (2, 32) and core.cache.states[0]["weight"].shape == (2, 1)
+        assert [p.name for p in core.runner.planners] == ["toy_first_rows", "paged_attention"]
         a = [3, 14, 15, 9, 2, 6, 5, 35, 8, 9, 7, 9, 3, 2, 38, 4, 6]
         b = [27, 18, 28, 18, 2, 8, 4, 5, 9, 0, 45]
         want_a, want_b = _plain(data, weights, a), _plain(data, weights, b)
         sa, sb = core.cache.admit(), core.cache.admit()
         got_a, got_b = [], []
+        step = lambda entries: core.runner.step(entries).clone()
         # a in portions and then token by token, b beside it: the state has to be carried in a's slot.
-        out = core.runner.step([StepEntry(sa, a[:5], range(5)), StepEntry(sb, b[:3], range(3))]).clone()
+        out = step([StepEntry(sa, a[:5], range(5)), StepEntry(sb, b[:3], range(3))])
         got_a.append(out[:5]); got_b.append(out[5:])
-        out = core.runner.step([StepEntry(sb, b[3:], range(8)), StepEntry(sa, a[5:7], range(2))]).clone()
+        out = step([StepEntry(sb, b[3:], range(8)), StepEntry(sa, a[5:7], range(2))])
         got_b.append(out[:8]); got_a.append(out[8:])
+        # One token a step, sampled on the device: with graphs the first of these steps records the launches (and
+        # runs once), the others replay them.
         for i in range(7, len(a)):
-            got_a.append(core.runner.step([StepEntry(sa, a[i:i + 1], [0])]).clone())
+            got_a.append(core.runner.step([StepEntry(sa, a[i:i + 1], [0])], sample=True)[0].clone())
         assert_close(torch.cat(got_a), want_a, 1e-4, "a")
         assert_close(torch.cat(got_b), want_b, 1e-4, "b")
+        if use_graphs:
+            assert core.runner.graph_replays == len(a) - 7 - 1
         # A slot that is used again starts from a zeroed state.
         core.cache.release(sa)
         sc = core.cache.admit()
-        assert sc == sa and float(core.cache.states[0][sc].abs().sum()) == 0.0
-        again = core.runner.step([StepEntry(sc, b, range(len(b)))]).clone()
+        assert sc == sa and all(float(t[sc].abs().sum()) == 0.0 for t in core.cache.states[0].values())
+        again = step([StepEntry(sc, b, range(len(b)))])                     # one portion of one prompt: recorded as it runs
         assert_close(again, want_b, 1e-4, "b in a's old slot")
+        core.cache.release(sc)
+        sd = core.cache.admit()
+        replayed = step([StepEntry(sd, b, range(len(b)))])                  # the same shape again: replayed
+        assert_close(replayed, want_b, 1e-4, "b again, replayed")
+        if use_graphs:
+            assert core.runner.graph_replays == len(a) - 7 - 1 + 1
+        core.kernels.check_errors()
     finally:
         unregister_architecture("ToyRunningMeanLM")

@@ -78,9 +78,56 @@ def test_untied_model_needs_lm_head_and_tied_model_refuses_it(tmp_path):
     folder = make_model_folder(tmp_path, "A")
     path = os.path.join(folder, "model.safetensors")
     tensors = load_file(path)
-    tensors["lm_head.weight"] = torch.zeros(256, 64)
+    tensors["model.layers.0.self_attn.o_proj.bias"] = torch.zeros(64)      # a tensor this architecture has no place for
     save_file(tensors, path)
     with pytest.raises(WeightError, match="unexpected"):
+        load_model(folder, "float32", "cpu")
+    model = load_model(folder, "float32", "cpu", strict=False)                # on request: a warning, not an error
+    assert model.head is model.embed
+
+
+def test_tensors_a_checkpoint_may_carry_unused(tmp_path, capsys):
+    """The reference's exporter stores the embedding a second time as lm_head.weight when the head is tied
+    (tools/dump_weights.py:24-26), and checkpoints carry the rotation's frequencies as a buffer: both are left
+    alone, named in a warning, and the tied head stays the embedding's own buffer."""
+    folder = make_model_folder(tmp_path, "A")
+    path = os.path.join(folder, "model.safetensors")
+    tensors = load_file(path)
+    tensors["lm_head.weight"] = tensors["model.embed_tokens.weight"].clone()
+    tensors["model.layers.0.self_attn.rotary_emb.inv_freq"] = torch.zeros(8)
+    save_file(tensors, path)
+    model = load_model(folder, "float32", "cpu")
+    assert model.head is model.embed
+    warning = capsys.readouterr().err
+    assert "lm_head.weight" in warning and "inv_freq" in warning and "2 tensors" in warning
+    ignored = []
+    load_tensors(folder, model.tensor_specs(), ignorable=model.ignorable_tensors, ignored=ignored)
+    assert sorted(ignored) == ["lm_head.weight", "model.layers.0.self_attn.rotary_emb.inv_freq"]
+    # An untied model does use lm_head.weight; for it the name is not ignorable.
+    assert "lm_head.weight" not in build_qwen2(config_from_dict(TINY_B), dtype="float32").ignorable_tensors
+
+
+def test_sharded_checkpoint_through_its_index(tmp_path):
+    """A checkpoint in several files: model.safetensors.index.json maps every tensor to its file."""
+    folder = make_model_folder(tmp_path, "B")
+    path = os.path.join(folder, "model.safetensors")
+    tensors = load_file(path)
+    whole = load_model(folder, "float32", "cpu")
+    os.remove(path)
+    names = sorted(tensors)
+    shards = {"model-00001-of-00002.safetensors": names[:len(names) // 2], "model-00002-of-00002.safetensors": names[len(names) // 2:]}
+    for file, members in shards.items():
+        save_file({n: tensors[n] for n in members}, os.path.join(folder, file))
+    with open(os.path.join(folder, "model.safetensors.index.json"), "w") as fh:
+        json.dump({"metadata": {}, "weight_map": {n: file for file, members in shards.items() for n in members}}, fh)
+    sharded = load_model(folder, "float32", "cpu")
+    assert torch.equal(sharded.embed, whole.embed) and torch.equal(sharded.head, whole.head)
+    assert torch.equal(sharded.blocks[2].mixer.w_qkv, whole.blocks[2].mixer.w_qkv)
+    assert torch.equal(sharded.blocks[0].ffn.w_down, whole.blocks[0].ffn.w_down)
+    # A tensor missing from every shard is reported like any missing tensor; a shard the index names but the folder
+    # lacks is an error of its own.
+    os.remove(os.path.join(folder, "model-00002-of-00002.safetensors"))
+    with pytest.raises(WeightError, match="model-00002-of-00002.safetensors"):
         load_model(folder, "float32", "cpu")
 
 

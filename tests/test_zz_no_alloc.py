@@ -48,7 +48,7 @@ def test_static_scratch_entry_point_matches_the_regular_one(head_dim):
         TorchKernels(wide=True).paged_attention(q, batch, kv, want, Hq, head_dim ** -0.5)
         b, c, qd = batch_to(batch, DEV), clone_kv(kv, DEV), q.to(DEV)
         n = batch.num_segments
-        common_head = [_ptr(c.k_pages), _ptr(c.v_pages), _ptr(c.block_table), c.block_table.shape[1], _ptr(b.decode_items), n,
+        common_head = [_ptr(c.k_pages), _ptr(c.v_pages), _ptr(c.block_table), c.block_table.shape[1], _ptr(b.plans["paged_attention"].arrays["decode_items"]), n,
                        _ptr(b.seg_q_start), _ptr(b.seg_q_len), _ptr(b.seg_kv_len)]
         common_tail = [Hq, Hkv, page, 0, nsplit, head_dim ** -0.5, stream]
         regular = torch.full_like(qd, float("nan"))
