@@ -1,6 +1,6 @@
 """Trace replay: feeds given token ids through the model step by step and writes logits.
 
-    trace_run --model DIR --dtype bfloat16|float32 --out DIR --max-tokens N
+    trace_run --model DIR --dtype bfloat16|float32 --out DIR --max-tokens N [--page-size P] [--max-live L]
 
 Standard input carries one JSON object a line,
     {"step": 0, "entries": [{"id": "a", "tokens": [5, 17, 3], "want": [0, 2]}], "end": []}
@@ -19,8 +19,8 @@ import os
 import sys
 from typing import Dict
 
-PAGE_SIZE = 16          # divides 64, the rounding of --max-tokens
-MAX_LIVE_REQUESTS = 8
+PAGE_SIZE = 16          # default of --page-size; divides 64, the rounding of --max-tokens
+MAX_LIVE_REQUESTS = 8   # default of --max-live
 
 
 def main(argv=None) -> int:
@@ -30,6 +30,8 @@ def main(argv=None) -> int:
     parser.add_argument("--out", required=True, help="folder for <step>.f32 files")
     parser.add_argument("--max-tokens", type=int, required=True,
                         help="most tokens that live requests hold at any time (each rounded up to 64)")
+    parser.add_argument("--page-size", type=int, default=PAGE_SIZE, help="tokens in a page of the cache (a power of two)")
+    parser.add_argument("--max-live", type=int, default=MAX_LIVE_REQUESTS, help="most requests that are live at a time")
     args = parser.parse_args(argv)
 
     import numpy as np
@@ -39,9 +41,10 @@ def main(argv=None) -> int:
     from ..engine.runner import StepEntry
 
     os.makedirs(args.out, exist_ok=True)
-    capacity = max(64, (args.max_tokens + 63) // 64 * 64)
-    options = EngineOptions(dtype=args.dtype, page_size=PAGE_SIZE, max_cached_tokens=capacity,
-                            max_running=MAX_LIVE_REQUESTS, max_tokens_per_step=capacity, use_graphs=False)
+    unit = max(64, args.page_size)                       # a request's tokens are rounded up to this
+    capacity = max(unit, (args.max_tokens + unit - 1) // unit * unit)
+    options = EngineOptions(dtype=args.dtype, page_size=args.page_size, max_cached_tokens=capacity,
+                            max_running=args.max_live, max_tokens_per_step=capacity, use_graphs=False)
     core = EngineCore(args.model, options)
     slots: Dict[str, int] = {}
 

@@ -9,7 +9,10 @@
 
 namespace tc {
 
-constexpr uint32_t SPIN_LIMIT = 1u << 24;
+#ifndef KVB_SPIN_LIMIT
+#define KVB_SPIN_LIMIT (1u << 24)
+#endif
+constexpr uint32_t SPIN_LIMIT = KVB_SPIN_LIMIT;   // polls after which a wait gives up (a build may set a shorter one)
 constexpr int KVB_DEV_TIMEOUT = 8;   // bit of the error word: an mbarrier wait ran out
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }

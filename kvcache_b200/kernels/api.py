@@ -10,6 +10,7 @@ from __future__ import annotations
 
 import contextlib
 import ctypes
+from collections import Counter
 from typing import Dict, Optional, Sequence
 
 import torch
@@ -130,6 +131,9 @@ _SIGNATURES = {
                              _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float,
                              _c_void_p, _c_void_p],
     },
+    "wait_probe": {
+        "kvb_wait_probe": [_c_void_p, _c_void_p, _c_void_p],
+    },
     "sampling": {
         "kvb_sample_parts": [_c_int],
         "kvb_sample": [_c_void_p, _c_int, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p],
@@ -215,12 +219,18 @@ class CudaKernels(KernelSet):
         self.sm_count = torch.cuda.get_device_properties(self.device).multi_processor_count
         self.error_word = torch.zeros(1, dtype=torch.int32, device=self.device)
         self.launches = 0
+        self.launch_counts: Counter = Counter()      # launches by kernel, as issued from the host (a replayed graph adds none)
         self._pinned_stream: Optional[_c_void_p] = None
         self._tma_cluster_capacity: Dict[tuple, int] = {}
         self._timing = None
         self._attention_planner: Optional[PagedAttentionPlanner] = None
 
     # ---- helpers -----------------------------------------------------------
+    def _count(self, kernel: str) -> None:
+        """One launch of `kernel` (while a graph is being recorded: one launch of every later replay)."""
+        self.launches += 1
+        self.launch_counts[kernel] += 1
+
     def _stream(self) -> _c_void_p:
         if self._pinned_stream is not None:
             return self._pinned_stream
@@ -257,6 +267,18 @@ class CudaKernels(KernelSet):
             reasons = [text for bit, text in DEVICE_ERRORS.items() if word & bit]
             raise KernelError("a kernel flagged bad input: " + "; ".join(reasons))
 
+    def probe_wait_timeout(self) -> int:
+        """Runs a kernel whose only wait cannot end (csrc/wait_probe.cu: the bounded mbarrier wait of the TMA and tcgen05
+        kernels, on a barrier nothing arrives on, with a short poll limit).  The kernel gives up, sets the time-out bit of
+        the error word and returns; the next `check_errors()` raises.  Returns the number of polls it made."""
+        outcome = torch.zeros(2, dtype=torch.int32, device=self.device)
+        self._count("wait_probe")
+        _check(_Library("wait_probe").kvb_wait_probe(_ptr(self.error_word), _ptr(outcome), self._stream()), "wait_probe")
+        gave_up, polls = (int(v) for v in outcome.tolist())
+        if gave_up != 2:
+            raise KernelError("the wait of the probe kernel ended although nothing arrived on its barrier")
+        return polls
+
     def paged_attention_planner(self) -> PagedAttentionPlanner:
         """The work lists `paged_attention` and `rope_append_attention` read from `StepBatch.plans` (one planner for all layers)."""
         if self._attention_planner is None:
@@ -268,21 +290,21 @@ class CudaKernels(KernelSet):
               last: Optional[torch.Tensor] = None) -> None:
         """out[r] = table[ids[r]], or table[last[src[r]]] where src[r] >= 0 (a token still on the device)."""
         T, H = out.shape
-        self.launches += 1
+        self._count("embed")
         _check(self._elementwise.kvb_embed(_dtype_code(table.dtype), _ptr(table), _ptr(ids), _ptr(src), _ptr(last), _ptr(out),
                                            T, H, table.shape[0], _ptr(self.error_word), self._stream()), "embed")
 
     def add_rmsnorm(self, h: torch.Tensor, delta: Optional[torch.Tensor], weight: torch.Tensor, eps: float,
                     out: torch.Tensor, rows: Optional[torch.Tensor] = None) -> None:
         n_out, H = out.shape
-        self.launches += 1
+        self._count("add_rmsnorm")
         _check(self._elementwise.kvb_add_rmsnorm(_dtype_code(out.dtype), _ptr(h), _ptr(delta), _ptr(weight),
                                                  _ptr(out), _ptr(rows), n_out, H, float(eps), self._stream()),
                "add_rmsnorm")
 
     def silu_mul(self, gate_up: torch.Tensor, out: torch.Tensor, interleaved: bool = False) -> None:
         T, I = out.shape
-        self.launches += 1
+        self._count("silu_mul")
         _check(self._elementwise.kvb_silu_mul(_dtype_code(out.dtype), _ptr(gate_up), _ptr(out), T, I,
                                               1 if interleaved else 0, self._stream()), "silu_mul")
 
@@ -292,17 +314,17 @@ class CudaKernels(KernelSet):
         M, K = x.shape
         I = out.shape[1]
         if interleaved and self._skinny(x.dtype, M, K, 2 * I):
-            self.launches += 1
+            self._count("gemm_skinny")
             _check(self._gemm_skinny.kvb_gemm_skinny(_dtype_code(out.dtype), 1, _ptr(x), _ptr(w_gate_up), _ptr(None),
                                                      _ptr(out), M, 2 * I, K, self._stream()), "gate_up_act (skinny)")
             return
         if interleaved and self._wstream(x.dtype, M, K):
-            self.launches += 1
+            self._count("gemm_wstream")
             _check(self._gemm_ws.kvb_gemm_wstream(_dtype_code(out.dtype), 1, _ptr(x), _ptr(w_gate_up), _ptr(None), _ptr(out), M,
                                                   2 * I, K, _ptr(self.error_word), self._stream()), "gate_up_act (wstream)")
             return
         if interleaved and self._tcgen05(x, w_gate_up, out, fused=True):
-            self.launches += 1
+            self._count("gemm_tcgen05")
             _check(self._gemm_tc.kvb_gemm_tcgen05(_dtype_code(out.dtype), 1, _ptr(x), _ptr(w_gate_up), _ptr(None), _ptr(out), M,
                                                   2 * I, K, _ptr(self.error_word), self._stream()), "gate_up_act (tcgen05)")
             return
@@ -346,21 +368,24 @@ class CudaKernels(KernelSet):
         N, K = w.shape
         if x.shape[1] != K or tuple(out.shape) != (M, N):
             raise KernelError(f"linear: shapes x{tuple(x.shape)} w{tuple(w.shape)} out{tuple(out.shape)} do not fit")
-        self.launches += 1
         if self._skinny(x.dtype, M, K, N):
+            self._count("gemm_skinny")
             _check(self._gemm_skinny.kvb_gemm_skinny(_dtype_code(out.dtype), 0, _ptr(x), _ptr(w), _ptr(bias),
                                                      _ptr(out), M, N, K, self._stream()), "linear (skinny)")
             return
         if self._wstream(x.dtype, M, K, N):
+            self._count("gemm_wstream")
             _check(self._gemm_ws.kvb_gemm_wstream(_dtype_code(out.dtype), 0, _ptr(x), _ptr(w), _ptr(bias), _ptr(out), M, N, K,
                                                   _ptr(self.error_word), self._stream()), "linear (wstream)")
             return
         if self._tcgen05(x, w, out):
+            self._count("gemm_tcgen05")
             _check(self._gemm_tc.kvb_gemm_tcgen05(_dtype_code(out.dtype), 0, _ptr(x), _ptr(w), _ptr(bias), _ptr(out), M, N, K,
                                                   _ptr(self.error_word), self._stream()), "linear (tcgen05)")
             return
         if x.dtype == torch.bfloat16 and self.bf16_gemm != "simt":
             # Library matrix product, as the reference's cublasGemmEx (apps/qwen_serve.cu:27-39).
+            self._count("gemm_library")
             if out.dtype == torch.bfloat16:
                 torch.matmul(x, w.t(), out=out)
             else:
@@ -368,6 +393,7 @@ class CudaKernels(KernelSet):
             if bias is not None:
                 out.add_(bias)
             return
+        self._count("gemm_simt")
         _check(self._gemm_simt.kvb_gemm_simt(_dtype_code(x.dtype), _dtype_code(out.dtype), _ptr(x), _ptr(w),
                                              _ptr(bias), _ptr(out), M, N, K, self._stream()), "linear")
 
@@ -378,7 +404,7 @@ class CudaKernels(KernelSet):
         spec = kv.spec
         rot_half = 0 if cos is None else cos.shape[1]
         table_len = 0 if cos is None else cos.shape[0]
-        self.launches += 1
+        self._count("rope_append")
         _check(self._rope.kvb_qkv_rope_append(
             _dtype_code(qkv.dtype), _ptr(qkv), _ptr(bias), _ptr(cos), _ptr(sin), rot_half, table_len,
             _ptr(batch.positions), _ptr(batch.row_segment), _ptr(kv.block_table), kv.block_table.shape[1],
@@ -432,7 +458,7 @@ class CudaKernels(KernelSet):
         lib = self._flash_library(D)
         tiles = -(-(kv.block_table.shape[1] * kv.page_size) // 64)
         nsplit = self._fit_clusters(lib, D, n * Hkv, self._cluster_splits(n, Hkv, tiles))
-        self.launches += 1
+        self._count("flash_decode_tma_fused")
         _check(lib.kvb_flash_decode_tma(
             None, _ptr(out), _ptr(kv.k_pages), _ptr(kv.v_pages), kv.k_pages.shape[0], _ptr(kv.block_table),
             kv.block_table.shape[1], None, n, _ptr(batch.seg_q_start), _ptr(batch.seg_q_len), _ptr(batch.seg_kv_len),
@@ -459,7 +485,7 @@ class CudaKernels(KernelSet):
                 units = counts["tc_units"]
                 scratch = workspace.buffer("attn.tc_scratch", (units * num_heads * 128 * (D + 2),), torch.float32)
                 tickets = workspace.zeros("attn.tc_tickets", (max(counts["tc_tiles"], 1) * num_heads,), torch.int32)
-                self.launches += 1
+                self._count("attention_tc")
                 _check(tc.kvb_attention_tc(
                     _ptr(q), _ptr(out), _ptr(kv.k_pages), _ptr(kv.v_pages), kv.k_pages.shape[0], _ptr(kv.block_table),
                     kv.block_table.shape[1], _ptr(lists["tc_units"]), units, _ptr(scratch), _ptr(tickets),
@@ -469,7 +495,7 @@ class CudaKernels(KernelSet):
                 units = counts["prefill_units"]
                 scratch = workspace.buffer("attn.prefill_scratch", (units * num_heads * 64 * (D + 2),), torch.float32)
                 tickets = workspace.zeros("attn.prefill_tickets", (max(counts["prefill_tiles"], 1) * num_heads,), torch.int32)
-                self.launches += 1
+                self._count("flash_prefill")
                 _check(lib.kvb_flash_prefill(
                     _ptr(q), _ptr(out), _ptr(kv.k_pages), _ptr(kv.v_pages), _ptr(kv.block_table), kv.block_table.shape[1],
                     _ptr(lists["prefill_units"]), units, _ptr(batch.seg_q_start), _ptr(batch.seg_q_len),
@@ -483,8 +509,8 @@ class CudaKernels(KernelSet):
                 tiles = -(-(kv.block_table.shape[1] * kv.page_size) // 64)
                 if self.decode_merge in ("cluster", "tma"):
                     nsplit = self._cluster_splits(n, Hkv, tiles)
-                    self.launches += 1
                     if self._tma_decode(D, kv):
+                        self._count("flash_decode_tma")
                         nsplit = self._fit_clusters(lib, D, n * Hkv, nsplit)
                         _check(lib.kvb_flash_decode_tma(
                             _ptr(q), _ptr(out), _ptr(kv.k_pages), _ptr(kv.v_pages), kv.k_pages.shape[0],
@@ -494,6 +520,7 @@ class CudaKernels(KernelSet):
                             kv.page_size, spec.window or 0, nsplit, float(scale), None, None, None, None, 0, 0,
                             _ptr(self.error_word), self._stream()), "flash_decode_tma")
                         return
+                    self._count("flash_decode_cluster")
                     _check(lib.kvb_flash_decode_cluster(
                         _ptr(q), _ptr(out), _ptr(kv.k_pages), _ptr(kv.v_pages), _ptr(kv.block_table),
                         kv.block_table.shape[1], _ptr(items), n, _ptr(batch.seg_q_start),
@@ -503,14 +530,14 @@ class CudaKernels(KernelSet):
                 nsplit = max(1, min(32, 2 * self.decode_ctas_wanted // (n * Hkv), tiles // self.decode_min_tiles))
                 scratch = workspace.buffer("attn.decode_scratch", (n * Hkv * nsplit * 16 * (D + 2),), torch.float32)
                 tickets = workspace.zeros("attn.decode_tickets", (n * Hkv,), torch.int32)
-                self.launches += 1
+                self._count("flash_decode_ticket")
                 _check(lib.kvb_flash_decode(
                     _ptr(q), _ptr(out), _ptr(kv.k_pages), _ptr(kv.v_pages), _ptr(kv.block_table), kv.block_table.shape[1],
                     _ptr(items), n, _ptr(batch.seg_q_start), _ptr(batch.seg_q_len), _ptr(batch.seg_kv_len),
                     _ptr(scratch), _ptr(tickets), num_heads, Hkv, kv.page_size, spec.window or 0, nsplit, float(scale),
                     self._stream()), "flash_decode")
             return
-        self.launches += 1
+        self._count("attention_generic")
         _check(self._attn_generic.kvb_paged_attention_generic(
             _dtype_code(q.dtype), _ptr(q), _ptr(kv.k_pages), _ptr(kv.v_pages), _ptr(kv.block_table),
             kv.block_table.shape[1], _ptr(batch.positions), _ptr(batch.row_segment), _ptr(out), T, num_heads,
@@ -520,7 +547,7 @@ class CudaKernels(KernelSet):
     def sample(self, logits: torch.Tensor, temperature: torch.Tensor, seeds: torch.Tensor, counters: torch.Tensor,
                out: torch.Tensor, scratch_val: torch.Tensor, scratch_idx: torch.Tensor) -> None:
         R, V = logits.shape
-        self.launches += 1
+        self._count("sample")
         _check(self._sampling.kvb_sample(_ptr(logits), R, V, _ptr(temperature), _ptr(seeds), _ptr(counters),
                                          _ptr(scratch_val), _ptr(scratch_idx), _ptr(out), self._stream()), "sample")
 

@@ -492,6 +492,10 @@ TC_SCENARIOS = [
     ([(0, 1100), (2000, 300)], 4, 2, 64, 16, None, 16),     # tiles cut into units over the keys and merged
     ([(0, 700), (100, 70)], 6, 2, 64, 32, None, 1),         # units of a single key tile
     ([(900, 700)], 4, 1, 128, 32, 300, 2),                  # units of a windowed layer: some hold no keys
+    # one-row segments beside long ones: the tensor-memory kernel and the decode kernel in one call
+    ([(700, 1), (100, 450), (30, 1), (2000, 1)], 14, 2, 64, 16, None, 16),
+    ([(515, 1), (200, 400), (64, 1)], 12, 2, 128, 16, None, 16),
+    ([(400, 1), (350, 390)], 7, 1, 64, 32, 300, 16),
 ]
 
 
@@ -516,7 +520,7 @@ def test_paged_attention_tc(kernels, request, scenario):
     kernels.tc_attention_min_rows = 2
     request.addfinalizer(lambda: setattr(kernels, "tc_attention_min_rows", saved))
     ws = Workspace(DEV)
-    rows = torch.cat([torch.arange(n) + sum(m for _, m in segments[:i]) for i, (_, n) in enumerate(segments) if n > 1])
+    rows = torch.arange(T)                                    # every row: segments of one row go through the decode kernel
     for _ in range(2):                                        # twice: the tickets of the first call must be zero again
         out = torch.full((T, Hq * D), float("nan"), dtype=dtype, device=DEV)
         kernels.paged_attention(q.to(DEV), batch_to(batch, DEV), clone_kv(kv, DEV), out, Hq, D ** -0.5, ws)
@@ -594,3 +598,22 @@ def test_sample(kernels, R, V):
         elif V <= 5000:
             scores = gumbel_scores(logits[r], 0.7, int(seeds[r]), int(counters[r]))
             assert scores[int(out[r])] >= scores.max() - 1e-4
+
+
+def test_a_wait_that_runs_out_reaches_the_host_as_an_error(kernels):
+    """Every mbarrier wait of the TMA and tensor-memory kernels is bounded.  A kernel whose wait cannot end (nothing
+    arrives on its barrier) gives up after its poll limit, sets the time-out bit of the error word and returns: the host
+    reads the error, and the device goes on working."""
+    from kvcache_b200.kernels.api import KernelError
+    kernels.check_errors()
+    polls = kernels.probe_wait_timeout()
+    assert 0 < polls < 1 << 20
+    with pytest.raises(KernelError, match="a wait inside a kernel ran out"):
+        kernels.check_errors()
+    kernels.check_errors()                                    # read and cleared: the next check is clean
+    x = torch.randn(4, 64, device=DEV).to(torch.bfloat16)
+    w = torch.randn(32, 64, device=DEV).to(torch.bfloat16)
+    out = torch.empty(4, 32, dtype=torch.bfloat16, device=DEV)
+    kernels.linear(x, w, out)                                 # the context is as usable as before
+    assert_close(out, x.float() @ w.float().t(), 2e-2)
+    kernels.check_errors()
