@@ -59,7 +59,7 @@ __global__ void __launch_bounds__(128) flash_decode_kernel(const DecodeParams p)
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
     const int G = p.Hq / p.Hkv;
     const int q_start = p.seg_q_start[seg], q_len = p.seg_q_len[seg], kv_len = p.seg_kv_len[seg];
-    const int rows = q_len * G;
+    const int rows = min(q_len * G, 16);   // an item is one warp tile of 16 rows; rows beyond it are not this kernel's (see no_alloc.h)
     const int first_pos = kv_len - q_len;
     const int key_lo = (p.window > 0 && first_pos - p.window + 1 > 0) ? first_pos - p.window + 1 : 0;
     const int tile_begin = key_lo / KT, tile_end = (kv_len + KT - 1) / KT;
@@ -287,7 +287,7 @@ __global__ void __launch_bounds__(128) flash_decode_cluster_kernel(const __grid_
     // Written by the host's copy at the start of the step: safe to read before the wait.
     const int seg = p.items ? p.items[item] : item;
     const int q_start = p.seg_q_start[seg], q_len = p.seg_q_len[seg], kv_len = p.seg_kv_len[seg];
-    const int rows = q_len * G;
+    const int rows = min(q_len * G, 16);   // an item is one warp tile of 16 rows; rows beyond it are not this kernel's (see no_alloc.h)
     const int first_pos = kv_len - q_len;
     const int key_lo = (p.window > 0 && first_pos - p.window + 1 > 0) ? first_pos - p.window + 1 : 0;
     const int tile_begin = key_lo / KT, tile_end = (kv_len + KT - 1) / KT;
@@ -561,7 +561,7 @@ __global__ void __launch_bounds__(160) flash_decode_tma_kernel(const __grid_cons
     // Written by the host's copy at the start of the step: safe to read before the wait.
     const int seg = p.items ? p.items[item] : item;
     const int q_start = p.seg_q_start[seg], q_len = p.seg_q_len[seg], kv_len = p.seg_kv_len[seg];
-    const int rows = q_len * G;
+    const int rows = min(q_len * G, 16);   // an item is one warp tile of 16 rows; rows beyond it are not this kernel's (see no_alloc.h)
     const int first_pos = kv_len - q_len;
     const int key_lo = (p.window > 0 && first_pos - p.window + 1 > 0) ? first_pos - p.window + 1 : 0;
     const int tile_begin = key_lo / KT, tile_end = (kv_len + KT - 1) / KT;
@@ -1158,7 +1158,10 @@ int kvb_flash_decode_static(const void* q, void* out, const void* k_pages, const
     constexpr int MAX_DEVICES = 64;
     static unsigned char* base_of_device[MAX_DEVICES] = {nullptr};
     if (n_items <= 0) return KVB_OK;
-    if (Hkv < 1 || nsplit < 1) return KVB_ERR_SHAPE;
+    // Everything the regular entry point would refuse is refused here first, before anything is queued on the stream.
+    if (Hkv < 1 || Hq % Hkv != 0 || Hq / Hkv > 16) return KVB_ERR_SHAPE;
+    if (page_size < 1 || (page_size & (page_size - 1)) != 0) return KVB_ERR_SHAPE;
+    if (nsplit < 1 || nsplit > MAX_SPLITS || n_items > 65535 || Hkv > 65535) return KVB_ERR_LIMIT;
     const size_t floats = (size_t)n_items * Hkv * nsplit * 16 * (D + 2);
     const size_t tickets = (size_t)n_items * Hkv;
     if (floats * sizeof(float) > KVB_STATIC_SCRATCH_BYTES - KVB_STATIC_TICKET_BYTES ||

@@ -11,12 +11,23 @@
 // keys and one ticket counter per (item, kv head).  This variant brings its own: a fixed array
 // in the library's device image, KVB_STATIC_SCRATCH_BYTES long, which every GPU that loads the
 // library holds until the process exits.  Inputs and outputs are still the caller's.
+// The library is built once per head size (kvb200_attention_flash-d64, -d128, ...): each of
+// those modules carries an array of its own, so a process that loads two of them holds two.
+// Calls into different modules neither share an array nor race with each other; calls into the
+// same module do both.
 //
 // Contract.
 //  * Arguments are those of kvb_flash_decode without `scratch` and `tickets`; the result is the same.
+//  * Each item is a segment whose rows fit one tile: seg_q_len * (Hq / Hkv) <= 16 (the engine lists
+//    segments of one token, with at most 16 query heads per kv head).  Rows beyond 16 are not
+//    computed by either entry point; nothing is read or written outside the item's share.
+//  * What the regular entry point refuses (Hq no multiple of Hkv, more than 16 query heads per kv
+//    head, a page size that is no power of two, more than 32 splits) is refused before anything is
+//    queued on the stream.
 //  * It calls no cudaMalloc, cudaFree or other allocating routine.  The first call on a device
 //    (with that device current) looks the array's device address up once; make that first call
-//    before any stream capture begins.
+//    before any stream capture begins.  Host threads that make their first calls at the same time
+//    look the same address up twice, which is harmless.
 //  * A call needs items * Hkv * nsplit * 16 * (head_dim + 2) floats of partial results plus
 //    items * Hkv tickets.  If that exceeds the array the call launches nothing and returns
 //    KVB_ERR_STATIC_SCRATCH; use fewer splits, fewer items per call, or the regular entry point.

@@ -68,6 +68,8 @@ def _ptr(t: Optional[torch.Tensor]) -> _c_void_p:
         return _c_void_p(0)
     if not t.is_contiguous():
         raise KernelError("kernels take contiguous tensors")
+    if not t.is_cuda:
+        raise KernelError("kernels take tensors on the device; a host tensor's address means nothing there")
     return _c_void_p(t.data_ptr())
 
 

@@ -79,8 +79,12 @@ def clone_kv(kv, device=None):
 
 def batch_to(batch, device):
     import dataclasses
+    from kvcache_b200.parts.base import StepPlan
     changes = {f.name: getattr(batch, f.name).to(device) for f in dataclasses.fields(batch)
                if isinstance(getattr(batch, f.name), torch.Tensor)}
+    # The planners' work lists are read by the kernels too: they move with the rest.
+    changes["plans"] = {name: StepPlan({k: v.to(device) for k, v in plan.arrays.items()}, dict(plan.counts))
+                        for name, plan in batch.plans.items()}
     return dataclasses.replace(batch, **changes)
 
 
