@@ -8,32 +8,42 @@
 
 // out[r, :] = float(table[id, :]) with id = ids[r], or, where src[r] >= 0, last[src[r]]: a token that the
 // previous step sampled and left on the device.  A token id outside [0, V) sets the error word and yields zeros.
+// `out16` (optional): the same rows rounded to bfloat16, for products that take the residual stream in that form.
 template <typename T>
 __global__ void embed_kernel(const T* __restrict__ table, const int* __restrict__ ids, const int* __restrict__ src,
-                             const int* __restrict__ last, float* __restrict__ out, int H, int V, int* __restrict__ err) {
+                             const int* __restrict__ last, float* __restrict__ out, bf16* __restrict__ out16, int H, int V,
+                             int* __restrict__ err) {
     pdl_wait();
     pdl_launch_dependents();
     const int r = blockIdx.x;
     const int from = src ? src[r] : -1;
     const int tok = from >= 0 ? last[from] : ids[r];
     float* dst = out + (size_t)r * H;
+    bf16* dst16 = out16 ? out16 + (size_t)r * H : nullptr;
     if (tok < 0 || tok >= V) {
         if (threadIdx.x == 0) atomicOr(err, KVB_DEV_BAD_TOKEN);
-        for (int i = threadIdx.x; i < H; i += blockDim.x) dst[i] = 0.f;
+        for (int i = threadIdx.x; i < H; i += blockDim.x) {
+            dst[i] = 0.f;
+            if (dst16) dst16[i] = __float2bfloat16_rn(0.f);
+        }
         return;
     }
     const T* row = table + (size_t)tok * H;
-    for (int i = threadIdx.x; i < H; i += blockDim.x) dst[i] = to_f32<T>(row[i]);
+    for (int i = threadIdx.x; i < H; i += blockDim.x) {
+        const float v = to_f32<T>(row[i]);
+        dst[i] = v;
+        if (dst16) dst16[i] = __float2bfloat16_rn(v);
+    }
 }
 
-KVB_API int kvb_embed(int dtype, const void* table, const int* ids, const int* src, const int* last, float* out, int T,
-                      int H, int V, int* err, cudaStream_t stream) {
+KVB_API int kvb_embed(int dtype, const void* table, const int* ids, const int* src, const int* last, float* out, void* out16,
+                      int T, int H, int V, int* err, cudaStream_t stream) {
     if (T <= 0) return KVB_OK;
     const int threads = H >= 512 ? 256 : 128;
     if (dtype == KVB_F32)
-        kvb_launch(embed_kernel<float>, dim3(T), dim3(threads), 0, stream, (const float*)table, ids, src, last, out, H, V, err);
+        kvb_launch(embed_kernel<float>, dim3(T), dim3(threads), 0, stream, (const float*)table, ids, src, last, out, (bf16*)out16, H, V, err);
     else if (dtype == KVB_BF16)
-        kvb_launch(embed_kernel<bf16>, dim3(T), dim3(threads), 0, stream, (const bf16*)table, ids, src, last, out, H, V, err);
+        kvb_launch(embed_kernel<bf16>, dim3(T), dim3(threads), 0, stream, (const bf16*)table, ids, src, last, out, (bf16*)out16, H, V, err);
     else
         return KVB_ERR_DTYPE;
     return kvb_launch_status();

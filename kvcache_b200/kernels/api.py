@@ -86,7 +86,7 @@ def _check(code: int, what: str) -> None:
 
 _SIGNATURES = {
     "elementwise": {
-        "kvb_embed": [_c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_void_p, _c_void_p],
+        "kvb_embed": [_c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_void_p, _c_void_p],
         "kvb_add_rmsnorm": [_c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_float, _c_void_p],
         "kvb_silu_mul": [_c_int, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_void_p],
     },
@@ -105,6 +105,11 @@ _SIGNATURES = {
     },
     "gemm_skinny": {
         "kvb_gemm_skinny": [_c_int, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_void_p],
+        "kvb_gemm_skinny_norm_act": [_c_void_p, _c_void_p, _c_void_p, _c_float, _c_void_p, _c_int, _c_int, _c_int, _c_void_p],
+        "kvb_gemm_skinny_residual": [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_void_p],
+        "kvb_gemm_skinny_qkv": [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_float, _c_void_p, _c_void_p, _c_int, _c_void_p,
+                                _c_void_p, _c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int,
+                                _c_int, _c_int, _c_int, _c_void_p, _c_void_p],
     },
     "gemm_wstream": {
         "kvb_gemm_wstream": [_c_int, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_void_p, _c_void_p],
@@ -289,12 +294,69 @@ class CudaKernels(KernelSet):
 
     # ---- operators ---------------------------------------------------------
     def embed(self, table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor, src: Optional[torch.Tensor] = None,
-              last: Optional[torch.Tensor] = None) -> None:
-        """out[r] = table[ids[r]], or table[last[src[r]]] where src[r] >= 0 (a token still on the device)."""
+              last: Optional[torch.Tensor] = None, out16: Optional[torch.Tensor] = None) -> None:
+        """out[r] = table[ids[r]], or table[last[src[r]]] where src[r] >= 0 (a token still on the device);
+        `out16`: the same rows in bfloat16 as well."""
         T, H = out.shape
         self._count("embed")
         _check(self._elementwise.kvb_embed(_dtype_code(table.dtype), _ptr(table), _ptr(ids), _ptr(src), _ptr(last), _ptr(out),
-                                           T, H, table.shape[0], _ptr(self.error_word), self._stream()), "embed")
+                                           _ptr(out16), T, H, table.shape[0], _ptr(self.error_word), self._stream()), "embed")
+
+    # ---- the folded chain of a decode layer ------------------------------------------------------------------
+    # For steps of few rows a layer is five launches instead of eight: the norm before a product runs inside that product
+    # (`norm=(weight, eps)`: x holds the residual stream in bfloat16, not normalised), the add after a product runs
+    # inside it (`linear_into_residual`), and bias, rotation and cache append run inside the q/k/v projection.
+    fold_norms = True
+
+    @property
+    def fold_key(self) -> tuple:
+        """The switches `can_fold` depends on (a model caches its answer per value of this)."""
+        return (self.fold_norms, self.skinny_gemm, self.wstream_gemm, self.bf16_gemm)
+
+    def can_fold(self, dtype: torch.dtype, rows: int, K: int, N: int) -> bool:
+        """Whether a product of `rows` rows with a [N, K] weight can take the folded forms (the register kernel's)."""
+        return self.fold_norms and self._skinny(dtype, rows, K, N)
+
+    def norm_gate_up_act(self, x16: torch.Tensor, w_gate_up: torch.Tensor, norm_w: torch.Tensor, eps: float, out: torch.Tensor) -> None:
+        """out[M, I] = silu(g) * u with [g | u] = rmsnorm(x16; norm_w, eps) . w_gate_up^T (rows interleaved in eights)."""
+        M, K = x16.shape
+        self._count("gemm_skinny_norm_act")
+        _check(self._gemm_skinny.kvb_gemm_skinny_norm_act(_ptr(x16), _ptr(w_gate_up), _ptr(norm_w), float(eps), _ptr(out), M,
+                                                          w_gate_up.shape[0], K, self._stream()), "norm_gate_up_act")
+
+    def linear_into_residual(self, x: torch.Tensor, w: torch.Tensor, h: torch.Tensor, h16: torch.Tensor,
+                             bias: Optional[torch.Tensor] = None) -> None:
+        """h += x . w^T + bias (float32, in place); h16 = bfloat16(h)."""
+        M, K = x.shape
+        self._count("gemm_skinny_residual")
+        _check(self._gemm_skinny.kvb_gemm_skinny_residual(_ptr(x), _ptr(w), _ptr(bias), _ptr(h), _ptr(h16), M, w.shape[0], K,
+                                                          self._stream()), "linear_into_residual")
+
+    def norm_qkv_rope_append(self, x16: torch.Tensor, w_paired: torch.Tensor, bias_paired: Optional[torch.Tensor],
+                             norm_w: torch.Tensor, eps: float, cos: Optional[torch.Tensor], sin: Optional[torch.Tensor],
+                             batch: StepBatch, kv: PagedKVView, q_out: torch.Tensor, num_heads: int) -> None:
+        """The q/k/v projection of rmsnorm(x16) with bias, rotation and append: `qkv_rope_append` after `linear` after the
+        norm, in one launch.  `w_paired` / `bias_paired`: rows permuted within each head so that rows 16 j + i and
+        16 j + 8 + i (i < 8) are dimensions 8 j + i and D / 2 + 8 j + i (see `pair_rotation_rows`)."""
+        M, K = x16.shape
+        spec = kv.spec
+        if cos is not None and cos.shape[1] * 2 != spec.head_dim:
+            raise KernelError("the folded q/k/v projection rotates whole heads only")
+        self._count("gemm_skinny_qkv")
+        _check(self._gemm_skinny.kvb_gemm_skinny_qkv(
+            _ptr(x16), _ptr(w_paired), _ptr(bias_paired), _ptr(norm_w), float(eps), _ptr(cos), _ptr(sin),
+            0 if cos is None else cos.shape[0], _ptr(batch.positions), _ptr(batch.row_segment), _ptr(kv.block_table),
+            kv.block_table.shape[1], _ptr(kv.k_pages), _ptr(kv.v_pages), _ptr(q_out), M, K, num_heads, spec.num_kv_heads,
+            spec.head_dim, kv.page_size, 1 if kv.writes else 0, _ptr(self.error_word), self._stream()), "norm_qkv_rope_append")
+
+    @staticmethod
+    def pair_rotation_rows(num_heads_total: int, head_dim: int) -> torch.Tensor:
+        """The row order `norm_qkv_rope_append` wants: for every head, tiles of 16 rows holding dimensions
+        8 j .. 8 j + 7 and D / 2 + 8 j .. D / 2 + 8 j + 7.  Returns the source row of each row of the permuted matrix."""
+        half = head_dim // 2
+        within = torch.cat([torch.cat([torch.arange(8 * j, 8 * j + 8), torch.arange(half + 8 * j, half + 8 * j + 8)])
+                            for j in range(head_dim // 16)])
+        return (torch.arange(num_heads_total)[:, None] * head_dim + within[None, :]).reshape(-1)
 
     def add_rmsnorm(self, h: torch.Tensor, delta: Optional[torch.Tensor], weight: torch.Tensor, eps: float,
                     out: torch.Tensor, rows: Optional[torch.Tensor] = None) -> None:

@@ -148,6 +148,11 @@ class Norm(Part):
                  ctx: LayerContext, rows: Optional[torch.Tensor] = None) -> None:
         raise NotImplementedError
 
+    def fold_params(self) -> Optional[Tuple[torch.Tensor, float]]:
+        """(weight, eps) if this norm is y = v * rsqrt(mean(v^2) + eps) * weight, so that a matrix product that follows
+        it can apply it on the way in (see `Mixer.forward_folded`); None for norms that cannot be folded."""
+        return None
+
 
 @dataclass(frozen=True)
 class Rotation:
@@ -181,9 +186,25 @@ class Mixer(Part):
     def forward(self, x: torch.Tensor, ctx: LayerContext) -> torch.Tensor:
         raise NotImplementedError
 
+    # The folded form, which a part may offer for steps of few rows: it takes the residual stream itself (`h`, float32,
+    # and `h16`, the same rounded to the compute type), applies `norm` inside its first matrix product and adds its
+    # result into `h` and `h16` inside its last - two kernels and two round trips through memory fewer per part.
+    def supports_fold(self, norm: "Norm", kernels: Any, num_rows: int) -> bool:
+        return False
+
+    def forward_folded(self, h: torch.Tensor, h16: torch.Tensor, norm: "Norm", ctx: LayerContext) -> None:
+        raise NotImplementedError
+
 
 class FeedForward(Part):
     def forward(self, x: torch.Tensor, ctx: LayerContext) -> torch.Tensor:
+        raise NotImplementedError
+
+    def supports_fold(self, norm: "Norm", kernels: Any, num_rows: int) -> bool:
+        """See `Mixer.supports_fold`."""
+        return False
+
+    def forward_folded(self, h: torch.Tensor, h16: torch.Tensor, norm: "Norm", ctx: LayerContext) -> None:
         raise NotImplementedError
 
 
@@ -194,4 +215,12 @@ class Block(Part):
     mixer: Mixer
 
     def forward(self, h: torch.Tensor, pending: Optional[torch.Tensor], ctx: LayerContext) -> Optional[torch.Tensor]:
+        raise NotImplementedError
+
+    def supports_fold(self, kernels: Any, num_rows: int) -> bool:
+        """Whether every part of the layer offers its folded form for a step of `num_rows` rows."""
+        return False
+
+    def forward_folded(self, h: torch.Tensor, h16: torch.Tensor, ctx: LayerContext) -> None:
+        """The layer on `h` and `h16` in place; nothing is left pending."""
         raise NotImplementedError

@@ -44,6 +44,14 @@ class PreNormBlock(Block):
     def weight_bytes(self) -> int:
         return sum(part.weight_bytes() for part in self._parts())
 
+    def supports_fold(self, kernels, num_rows: int) -> bool:
+        return (self.mixer.supports_fold(self.norm1, kernels, num_rows)
+                and self.ffn.supports_fold(self.norm2, kernels, num_rows))
+
+    def forward_folded(self, h: torch.Tensor, h16: torch.Tensor, ctx: LayerContext) -> None:
+        self.mixer.forward_folded(h, h16, self.norm1, ctx)
+        self.ffn.forward_folded(h, h16, self.norm2, ctx)
+
     def forward(self, h: torch.Tensor, pending: Optional[torch.Tensor], ctx: LayerContext) -> Optional[torch.Tensor]:
         T = h.shape[0]
         x = ctx.workspace.buffer("block.normed", (T, self.width), self.dtype)

@@ -47,6 +47,20 @@ class GatedMLP(FeedForward):
     def weight_bytes(self) -> int:
         return (self.w_gate_up.numel() + self.w_down.numel()) * self.w_down.element_size()
 
+    def supports_fold(self, norm, kernels, num_rows: int) -> bool:
+        can = getattr(kernels, "can_fold", None)
+        return (can is not None and self.interleaved and norm.fold_params() is not None
+                and can(self.dtype, num_rows, self.hidden, 2 * self.intermediate)
+                and can(self.dtype, num_rows, self.intermediate, self.hidden))
+
+    def forward_folded(self, h: torch.Tensor, h16: torch.Tensor, norm, ctx: LayerContext) -> None:
+        T = h.shape[0]
+        k, ws = ctx.kernels, ctx.workspace
+        weight, eps = norm.fold_params()
+        act = ws.buffer("ffn.act", (T, self.intermediate), self.dtype)
+        k.norm_gate_up_act(h16, self.w_gate_up, weight, eps, act)
+        k.linear_into_residual(act, self.w_down, h, h16)
+
     def forward(self, x: torch.Tensor, ctx: LayerContext) -> torch.Tensor:
         T = x.shape[0]
         k, ws = ctx.kernels, ctx.workspace

@@ -46,6 +46,7 @@ class DecoderModel:
         self.position = position
         # Names (shell patterns) of tensors that checkpoints of this architecture may carry without the model using them.
         self.ignorable_tensors = tuple(ignorable_tensors)
+        self._fold_cache: Dict[tuple, bool] = {}
         self.embed: Optional[torch.Tensor] = None
         self.head: Optional[torch.Tensor] = None
         self.device: Optional[torch.device] = None
@@ -123,13 +124,32 @@ class DecoderModel:
                 found.setdefault(planner.name, planner)
         return list(found.values())
 
+    def _folds(self, kernels: Any, num_rows: int) -> bool:
+        """Whether a step of `num_rows` rows runs every layer in its folded form: all layers must offer it, and nothing
+        may change the embedded rows behind the back of their rounded copy."""
+        if self.position is not None and type(self.position).on_embed is not PositionEncoding.on_embed:
+            return False
+        key = (id(kernels), num_rows, getattr(kernels, "fold_key", None))
+        found = self._fold_cache.get(key)
+        if found is None:
+            found = self._fold_cache[key] = all(self.blocks[call.layer].supports_fold(kernels, num_rows) for call in self.schedule)
+        return found
+
     # ---- one step ----------------------------------------------------------
     def forward(self, batch: StepBatch, kernels: Any, workspace: Any, cache: Any) -> torch.Tensor:
         """Runs the rows of `batch` through the layer calls; returns float32 logits
         [batch.num_wanted, vocab] for `batch.wanted_rows`."""
         T, R = batch.num_tokens, batch.num_wanted
         h = workspace.buffer("model.h", (T, self.width), torch.float32)
-        kernels.embed(self.embed, batch.token_ids, h, batch.token_src, batch.last_tokens)
+        # Steps of few rows take every layer's folded form, if every layer offers one: the residual stream then also
+        # exists rounded to the compute type (`h16`), norms run inside the products after them and adds inside the
+        # products before them.
+        fold = self._folds(kernels, T)
+        h16 = workspace.buffer("model.h16", (T, self.width), self.dtype) if fold else None
+        if fold:
+            kernels.embed(self.embed, batch.token_ids, h, batch.token_src, batch.last_tokens, h16)
+        else:
+            kernels.embed(self.embed, batch.token_ids, h, batch.token_src, batch.last_tokens)
         base = LayerContext(batch=batch, kernels=kernels, workspace=workspace)
         if self.position is not None:
             self.position.on_embed(h, base)
@@ -138,7 +158,10 @@ class DecoderModel:
             ctx = LayerContext(batch=batch, kernels=kernels, workspace=workspace,
                                kv=cache.kv_view(call.cache, call.writes_cache),
                                state=cache.state(call.cache), call_index=index)
-            pending = self.blocks[call.layer].forward(h, pending, ctx)
+            if fold:
+                self.blocks[call.layer].forward_folded(h, h16, ctx)
+            else:
+                pending = self.blocks[call.layer].forward(h, pending, ctx)
         logits = workspace.buffer("model.logits", (R, self.vocab_size), torch.float32)
         if R > 0:
             normed = workspace.buffer("model.final", (R, self.width), self.dtype)

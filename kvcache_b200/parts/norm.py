@@ -32,3 +32,6 @@ class RMSNorm(Norm):
 
     def add_norm(self, h, delta, out, ctx: LayerContext, rows=None) -> None:
         ctx.kernels.add_rmsnorm(h, delta, self.weight, self.eps, out, rows)
+
+    def fold_params(self):
+        return self.weight, self.eps

@@ -95,7 +95,9 @@ def test_decode_batches_of_the_benchmark(folders, kernels, shape, batch, dtype):
         else:
             assert counts["flash_decode_tma"] > 0
             if shape == "0.5B":                           # (tiny D's widths are no multiples of 32: its products stream through tcgen05)
-                assert counts["gemm_skinny"] > 0
+                # up to 16 rows a layer is five launches: norms, adds, bias, rotation and append run inside its products
+                assert counts["gemm_skinny"] > 0 and counts["gemm_skinny_qkv"] > 0 and counts["gemm_skinny_norm_act"] > 0
+                assert counts["gemm_skinny_residual"] > 0 and counts["rope_append"] <= config["num_hidden_layers"]
         if 17 <= batch <= 32:
             assert counts["gemm_wstream"] > 0
         if batch >= 33:

@@ -617,3 +617,101 @@ def test_a_wait_that_runs_out_reaches_the_host_as_an_error(kernels):
     kernels.linear(x, w, out)                                 # the context is as usable as before
     assert_close(out, x.float() @ w.float().t(), 2e-2)
     kernels.check_errors()
+
+
+# ---- the folded forms of the register product (decode steps of up to 16 rows) -------------------------------------------
+
+FOLD_SHAPES = [(1, 96), (5, 896), (8, 1536), (13, 224), (16, 896)]      # (rows, width)
+
+
+@pytest.mark.parametrize("M,K", FOLD_SHAPES)
+def test_norm_folded_into_the_gated_product(kernels, M, K):
+    """out = silu(g) * u with [g | u] = rmsnorm(x) . W^T, the norm applied inside the product: against the norm, the
+    product and the activation one after the other in float64."""
+    g = torch.Generator().manual_seed(40 + M)
+    I = 136 if K < 500 else 1216
+    x16 = (torch.randn(M, K, generator=g) * 2).to(torch.bfloat16)
+    w = (torch.randn(2 * I, K, generator=g) * 0.05).to(torch.bfloat16)
+    norm_w, eps = 1 + 0.1 * torch.randn(K, generator=g), 1e-5
+    normed = torch.empty(M, K, dtype=torch.float64)
+    REF.add_rmsnorm(x16.float(), None, norm_w, eps, normed)
+    want = torch.empty(M, I, dtype=torch.float64)
+    REF.gate_up_act(normed, w.double(), want, None, True)
+    out = torch.full((M, I), float("nan"), dtype=torch.bfloat16, device=DEV)
+    kernels.norm_gate_up_act(x16.to(DEV), w.to(DEV), norm_w.to(DEV), eps, out)
+    assert_close(out, want, REL[torch.bfloat16])
+    kernels.check_errors()
+
+
+@pytest.mark.parametrize("M,K", FOLD_SHAPES)
+def test_product_added_into_the_residual_stream(kernels, M, K):
+    """h += x . W^T and h16 = bfloat16(h) inside the product, for a weight with few rows (K split over a cluster) and
+    one with many."""
+    g = torch.Generator().manual_seed(50 + M)
+    for N in (K, 4 * K if K < 500 else 1152):
+        x = torch.randn(M, K, generator=g).to(torch.bfloat16)
+        w = (torch.randn(N, K, generator=g) * 0.05).to(torch.bfloat16)
+        h = torch.randn(M, N, generator=g) * 3
+        want = h.double() + x.double() @ w.double().t()
+        h_dev, h16 = h.clone().to(DEV), torch.full((M, N), float("nan"), dtype=torch.bfloat16, device=DEV)
+        kernels.linear_into_residual(x.to(DEV), w.to(DEV), h_dev, h16)
+        assert_close(h_dev, want, 1e-5, f"residual stream, N={N}")          # float32 sums, float32 add
+        assert torch.equal(h16, h_dev.to(torch.bfloat16)), "the rounded copy is the stream's own rounding"
+    kernels.check_errors()
+
+
+FOLD_QKV = [
+    # (segments (cached, new), Hq, Hkv, D, page, width)
+    ([(130, 1), (31, 1), (200, 1), (0, 1), (15, 1), (16, 1), (4095, 1), (77, 1)], 14, 2, 64, 16, 896),
+    ([(300, 1)], 3, 1, 32, 8, 96),
+    ([(5, 1), (63, 1), (64, 1)], 12, 2, 128, 32, 1536),
+    ([(0, 3), (40, 2), (9, 1)], 4, 4, 16, 4, 224),                       # short portions take the same path
+    ([(i * 7, 1) for i in range(16)], 6, 2, 48, 16, 288),
+]
+
+
+@pytest.mark.parametrize("rotate", [True, False])
+@pytest.mark.parametrize("scenario", FOLD_QKV)
+def test_norm_bias_rotation_and_append_folded_into_the_qkv_product(kernels, scenario, rotate):
+    """The q/k/v projection of rmsnorm(x) with bias, rotation and append in one launch, from row-paired weights, against
+    the norm, the product and `qkv_rope_append` one after the other on the weights in their natural order."""
+    from kvcache_b200.kernels.api import CudaKernels
+    from kvcache_b200.parts.position import RotaryHalf
+    segments, Hq, Hkv, D, page, K = scenario
+    dtype = torch.bfloat16
+    batch, kv = paged_scenario(segments, num_kv_heads=Hkv, head_dim=D, page_size=page, dtype=dtype, device="cpu", seed=61)
+    T = batch.num_tokens
+    g = torch.Generator().manual_seed(62)
+    N = (Hq + 2 * Hkv) * D
+    x16 = (torch.randn(T, K, generator=g) * 1.5).to(dtype)
+    w = (torch.randn(N, K, generator=g) * 0.05).to(dtype)
+    bias = torch.randn(N, generator=g)
+    norm_w, eps = 1 + 0.1 * torch.randn(K, generator=g), 1e-6
+    cos = sin = None
+    if rotate:
+        rope = RotaryHalf(D, 1000000.0, 4200)
+        rope.bind({}, torch.device("cpu"))
+        cos, sin = rope.rotation().cos, rope.rotation().sin
+    normed = torch.empty(T, K, dtype=torch.float64)
+    REF.add_rmsnorm(x16.float(), None, norm_w, eps, normed)
+    qkv = torch.empty(T, N, dtype=torch.float64)
+    REF.linear(normed, w.double(), qkv)
+    for b in (bias, None):
+        kv_ref, q_ref = clone_kv(kv), torch.empty(T, Hq * D, dtype=dtype)
+        REF.qkv_rope_append(qkv, b, cos, sin, batch, kv_ref, q_ref, Hq)
+        order = CudaKernels.pair_rotation_rows(Hq + 2 * Hkv, D)
+        kv_dev, q_out = clone_kv(kv, DEV), torch.full((T, Hq * D), float("nan"), dtype=dtype, device=DEV)
+        to = lambda t: None if t is None else t.to(DEV)
+        kernels.norm_qkv_rope_append(x16.to(DEV), w[order].contiguous().to(DEV), to(b[order].contiguous()) if b is not None else None,
+                                     norm_w.to(DEV), eps, to(cos), to(sin), batch_to(batch, DEV), kv_dev, q_out, Hq)
+        assert_close(q_out, q_ref, REL[dtype], "queries")
+        assert_close(kv_dev.k_pages, kv_ref.k_pages, REL[dtype], "key pages")
+        assert_close(kv_dev.v_pages, kv_ref.v_pages, REL[dtype], "value pages")
+    # A call that only reads the cache another call wrote leaves the pages alone.
+    kv_dev = clone_kv(kv, DEV)
+    kv_dev.writes = False
+    before = kv_dev.k_pages.clone()
+    kernels.norm_qkv_rope_append(x16.to(DEV), w[order].contiguous().to(DEV), None, norm_w.to(DEV), eps, to(cos), to(sin),
+                                 batch_to(batch, DEV), kv_dev, q_out, Hq)
+    assert torch.equal(kv_dev.k_pages, before)
+    kernels.check_errors()
