@@ -108,7 +108,7 @@ __global__ void __launch_bounds__(256) gemm_skinny_kernel(const bf16* __restrict
                                                           const __grid_constant__ Fused fz) {
     SKINNY_TRACE(0)
     if (ksplit > 1) cluster_arrive_started();
-    extern __shared__ __align__(16) float red[];          // [warps + ksplit][RT][NT][32 lanes][4], then (PRE) [warps + ksplit][16] sums of squares
+    extern __shared__ __align__(16) float red[];          // [warps + ksplit][RT][NT][32 lanes][4]; PRE: then sums of squares and the norm's weight
     const int warps = blockDim.x >> 5, warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
     const int rank = blockIdx.x % ksplit;                  // the cluster spans x
     const int n0 = (blockIdx.x / ksplit) * 16 * RT;
@@ -149,10 +149,30 @@ __global__ void __launch_bounds__(256) gemm_skinny_kernel(const bf16* __restrict
 #pragma unroll
     for (int nb = 0; nb < NBUF; ++nb)
         if (kb_begin + nb * U < kb_end) load_w(a[nb], kb_begin + nb * U);
+    constexpr int F = RT * NT * 32;                        // fragments (float4) of a block's tile
+    float* ssq_s = red + (size_t)(warps + ksplit) * F * 4;                             // PRE: [warps][16], then [ksplit][16]
+    float* nw_s = ssq_s + (warps + ksplit) * 16;                                       // PRE: the norm's weight [K]
+    if (PRE) {                                             // no kernel writes the norm's weight: fetched before the wait
+        for (int i = threadIdx.x * 4; i < K; i += blockDim.x * 4)
+            *reinterpret_cast<float4*>(nw_s + i) = __ldg(reinterpret_cast<const float4*>(fz.norm_w + i));
+    }
     SKINNY_TRACE(1)
     pdl_wait();
     pdl_launch_dependents();
+    if (PRE) __syncthreads();
     SKINNY_TRACE(2)
+    // EPI_RESID: the four elements of the residual stream that this thread will update first, requested now.
+    const int first_idx = threadIdx.x * ksplit + rank;
+    float h_first[4] = {0.f, 0.f, 0.f, 0.f};
+    if (EPI == EPI_RESID && first_idx < F) {
+        const int l2 = first_idx & 31, rj = first_idx >> 5, r = rj / NT, j = rj - r * NT;
+        const int m = 8 * j + 2 * (l2 & 3), n = n0 + 16 * r + (l2 >> 2);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const int nn = n + 8 * (e >> 1), mm = m + (e & 1);
+            if (nn < N && mm < M) h_first[e] = fz.h[(size_t)mm * N + nn];
+        }
+    }
 
     float acc[RT][NT][4];
 #pragma unroll
@@ -175,29 +195,34 @@ __global__ void __launch_bounds__(256) gemm_skinny_kernel(const bf16* __restrict
         for (int u = 0; u < U; ++u) {
             const bool live = kb + u < kb_end;
             const int k = (live ? kb + u : kb) * 32;
-            float4 nw0, nw1;
-            if (PRE) {                                     // the norm's weight for this thread's eight columns
-                nw0 = __ldg(reinterpret_cast<const float4*>(fz.norm_w + k + 8 * t));
-                nw1 = __ldg(reinterpret_cast<const float4*>(fz.norm_w + k + 8 * t + 4));
-            }
 #pragma unroll
             for (int j = 0; j < NT; ++j) {
                 if (live && xok[j]) {
                     b[u][j] = __ldg(reinterpret_cast<const uint4*>(xrow[j] + k));
-                    if (PRE) {
-                        float f[8];
-                        unpack8(b[u][j], f);
-                        const float nw[8] = {nw0.x, nw0.y, nw0.z, nw0.w, nw1.x, nw1.y, nw1.z, nw1.w};
-#pragma unroll
-                        for (int e = 0; e < 8; ++e) {
-                            ssq[j] += f[e] * f[e];
-                            f[e] *= nw[e];
-                        }
-                        b[u][j] = pack8(f);
-                    }
                 } else {
                     b[u][j] = make_uint4(0, 0, 0, 0);
                 }
+            }
+        }
+    };
+    // PRE: the rows as they arrived are squared and summed, multiplied by the norm's weight and rounded again, just
+    // before they are used (so that the loads stay in flight meanwhile).
+    auto fold_norm = [&](uint4 (&b)[U][NT], int kb) {
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const int k = min(kb + u, kb_end - 1) * 32 + 8 * t;
+            const float4 nw0 = *reinterpret_cast<const float4*>(nw_s + k), nw1 = *reinterpret_cast<const float4*>(nw_s + k + 4);
+            const float nw[8] = {nw0.x, nw0.y, nw0.z, nw0.w, nw1.x, nw1.y, nw1.z, nw1.w};
+#pragma unroll
+            for (int j = 0; j < NT; ++j) {
+                float f[8];
+                unpack8(b[u][j], f);
+#pragma unroll
+                for (int e = 0; e < 8; ++e) {
+                    ssq[j] += f[e] * f[e];
+                    f[e] *= nw[e];
+                }
+                b[u][j] = pack8(f);
             }
         }
     };
@@ -220,6 +245,7 @@ __global__ void __launch_bounds__(256) gemm_skinny_kernel(const bf16* __restrict
         for (int nb = 0; nb < NBUF; ++nb) {
             const int kb = base + nb * U;
             if (kb < kb_end) {
+                if (PRE) fold_norm(bx[nb], kb);
                 multiply(a[nb], bx[nb]);
                 if (kb + NBUF * U < kb_end) { load_w(a[nb], kb + NBUF * U); load_x(bx[nb], kb + NBUF * U); }
             }
@@ -233,8 +259,6 @@ __global__ void __launch_bounds__(256) gemm_skinny_kernel(const bf16* __restrict
     for (int r = 0; r < RT; ++r)
 #pragma unroll
         for (int j = 0; j < NT; ++j) mine[(r * NT + j) * 32] = make_float4(acc[r][j][0], acc[r][j][1], acc[r][j][2], acc[r][j][3]);
-    constexpr int F = RT * NT * 32;
-    float* ssq_s = red + (size_t)(warps + ksplit) * F * 4;                             // [warps][16], then [ksplit][16]
     if (PRE) {
         // A row's squares lie with the four threads of its group, the warps of the block and the blocks of the cluster:
         // added in that order, each in a fixed order.
@@ -319,12 +343,18 @@ __global__ void __launch_bounds__(256) gemm_skinny_kernel(const bf16* __restrict
                 }
             }
         } else if (EPI == EPI_RESID) {
+            float hv[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {                  // all four loads before the first store
+                const int nn = n + 8 * (e >> 1), mm = m + (e & 1);
+                hv[e] = idx == first_idx ? h_first[e] : ((nn < N && mm < M) ? fz.h[(size_t)mm * N + nn] : 0.f);
+            }
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
                 const int nn = n + 8 * (e >> 1), mm = m + (e & 1);
                 if (nn < N && mm < M) {
                     const size_t at = (size_t)mm * N + nn;
-                    const float v = fz.h[at] + vals[e] + (bias ? bias[nn] : 0.f);
+                    const float v = hv[e] + vals[e] + (bias ? bias[nn] : 0.f);
                     fz.h[at] = v;
                     fz.hb[at] = __float2bfloat16_rn(v);
                 }
@@ -397,8 +427,9 @@ static inline Split choose_split(int N, int kblocks) {
     return s;
 }
 
-static inline size_t smem_bytes(const Split& s, int RT, int NT, bool pre) {
-    return (size_t)(s.warps + s.ksplit) * RT * NT * 32 * 4 * sizeof(float) + (pre ? (size_t)(s.warps + s.ksplit) * 16 * sizeof(float) : 0);
+static inline size_t smem_bytes(const Split& s, int RT, int NT, bool pre, int K) {
+    return (size_t)(s.warps + s.ksplit) * RT * NT * 32 * 4 * sizeof(float) +
+           (pre ? ((size_t)(s.warps + s.ksplit) * 16 + K) * sizeof(float) : 0);
 }
 
 // Whether all blocks of this shape are on the SMs at once (no second wave that costs a block's whole latency again).
@@ -413,7 +444,7 @@ bool resident(int N, int K) {
         cudaGetDevice(&device);
         cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, device);
         if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&cached, gemm_skinny_kernel<RT, NT, EPI, PRE, TOut>, s.warps * 32,
-                                                          smem_bytes(s, RT, NT, PRE)) != cudaSuccess)
+                                                          smem_bytes(s, RT, NT, PRE, K)) != cudaSuccess)
             cached = 1;
     }
     return (long long)blocks * s.ksplit <= (long long)cached * sm_count;
@@ -425,7 +456,7 @@ int launch(const bf16* x, const bf16* w, const float* bias, TOut* y, int M, int 
     const int blocks = (N + 16 * RT - 1) / (16 * RT);
     const Split s = choose_split(N, K / 32);
     const int ksplit = s.ksplit, warps = s.warps;
-    const size_t smem = smem_bytes(s, RT, NT, PRE);
+    const size_t smem = smem_bytes(s, RT, NT, PRE, K);
     auto kernel = gemm_skinny_kernel<RT, NT, EPI, PRE, TOut>;
     if (smem > 48 * 1024) {
         cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);

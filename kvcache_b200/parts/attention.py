@@ -57,18 +57,22 @@ class GQAAttention(Mixer):
         if self.qkv_bias:
             self.b_qkv = torch.cat([tensors[f"{p}{n}_proj.bias"] for n in "qkv"], dim=0).to(torch.float32).to(device).contiguous()
         self.w_o = tensors[f"{p}o_proj.weight"].to(self.dtype).to(device).contiguous()
-        # A second copy of the q/k/v weight for the folded projection of decode steps, which rotates inside the product:
-        # within each head the rows are reordered so that a rotation pair (d, d + D / 2) lies eight rows apart in one
-        # 16-row tile.  Made where a kernel set can use it: bfloat16, whole-head rotation (or none), heads in steps of 16.
+        # The folded projection of decode steps rotates inside the product and wants a second copy of the q/k/v weight
+        # with each head's rows reordered (made when first asked for): possible in bfloat16, with whole-head rotation (or
+        # none) and heads in steps of 16.
         self.w_qkv_paired = self.b_qkv_paired = None
+        self._can_pair = self.dtype == torch.bfloat16 and self.head_dim % 16 == 0 and device.type == "cuda"
+
+    def _pair_rows(self, kernels) -> bool:
+        """Makes the row-paired copy of the q/k/v weight and bias if the kernel set can use one."""
         rotation = self.position.rotation() if self.position is not None else None
         whole = rotation is None or rotation.cos.shape[1] * 2 == self.head_dim
-        if self.dtype == torch.bfloat16 and self.head_dim % 16 == 0 and whole and device.type == "cuda":
-            from ..kernels.api import CudaKernels
-            order = CudaKernels.pair_rotation_rows(self.num_heads + 2 * self.num_kv_heads, self.head_dim).to(device)
+        if self.w_qkv_paired is None and self._can_pair and whole and hasattr(kernels, "pair_rotation_rows"):
+            order = kernels.pair_rotation_rows(self.num_heads + 2 * self.num_kv_heads, self.head_dim).to(self.w_qkv.device)
             self.w_qkv_paired = self.w_qkv.index_select(0, order).contiguous()
             if self.b_qkv is not None:
                 self.b_qkv_paired = self.b_qkv.index_select(0, order).contiguous()
+        return self.w_qkv_paired is not None
 
     def weight_bytes(self) -> int:
         n = self.w_qkv.numel() * self.w_qkv.element_size() + self.w_o.numel() * self.w_o.element_size()
@@ -83,9 +87,9 @@ class GQAAttention(Mixer):
 
     def supports_fold(self, norm, kernels, num_rows: int) -> bool:
         can = getattr(kernels, "can_fold", None)
-        return (can is not None and self.w_qkv_paired is not None and norm.fold_params() is not None
+        return (can is not None and norm.fold_params() is not None
                 and can(self.dtype, num_rows, self.hidden, self.q_size + 2 * self.kv_size)
-                and can(self.dtype, num_rows, self.q_size, self.hidden))
+                and can(self.dtype, num_rows, self.q_size, self.hidden) and self._pair_rows(kernels))
 
     def forward_folded(self, h: torch.Tensor, h16: torch.Tensor, norm, ctx: LayerContext) -> None:
         T = h.shape[0]
@@ -99,6 +103,7 @@ class GQAAttention(Mixer):
         attn = ws.buffer("attn.out", (T, self.q_size), self.dtype)
         k.paged_attention(q, ctx.batch, ctx.kv, attn, self.num_heads, self.scale, ws)
         k.linear_into_residual(attn, self.w_o, h, h16)
+
 
     def forward(self, x: torch.Tensor, ctx: LayerContext) -> torch.Tensor:
         T = x.shape[0]

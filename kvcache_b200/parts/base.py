@@ -143,6 +143,7 @@ class Part:
         return 0
 
 
+
 class Norm(Part):
     def add_norm(self, h: torch.Tensor, delta: Optional[torch.Tensor], out: torch.Tensor,
                  ctx: LayerContext, rows: Optional[torch.Tensor] = None) -> None:

@@ -61,6 +61,7 @@ class GatedMLP(FeedForward):
         k.norm_gate_up_act(h16, self.w_gate_up, weight, eps, act)
         k.linear_into_residual(act, self.w_down, h, h16)
 
+
     def forward(self, x: torch.Tensor, ctx: LayerContext) -> torch.Tensor:
         T = x.shape[0]
         k, ws = ctx.kernels, ctx.workspace

@@ -95,15 +95,27 @@ def test_decode_batches_of_the_benchmark(folders, kernels, shape, batch, dtype):
         else:
             assert counts["flash_decode_tma"] > 0
             if shape == "0.5B":                           # (tiny D's widths are no multiples of 32: its products stream through tcgen05)
-                # up to 16 rows a layer is five launches: norms, adds, bias, rotation and append run inside its products
-                assert counts["gemm_skinny"] > 0 and counts["gemm_skinny_qkv"] > 0 and counts["gemm_skinny_norm_act"] > 0
-                assert counts["gemm_skinny_residual"] > 0 and counts["rope_append"] <= config["num_hidden_layers"]
+                assert counts["gemm_skinny"] > 0
+                if kernels.fold_norms:
+                    # a layer in five launches: norms, adds, bias, rotation and append run inside its products
+                    assert counts["gemm_skinny_qkv"] > 0 and counts["gemm_skinny_norm_act"] > 0
+                    assert counts["gemm_skinny_residual"] > 0 and counts["rope_append"] <= config["num_hidden_layers"]
         if 17 <= batch <= 32:
             assert counts["gemm_wstream"] > 0
         if batch >= 33:
             assert counts["gemm_library"] > 0
     else:
         assert counts["gemm_simt"] > 0 and counts["attention_generic"] > 0 and not counts["gemm_library"]
+
+
+@pytest.mark.parametrize("batch", [8, 13])
+def test_decode_batches_through_the_folded_chain(folders, kernels, request, batch):
+    """The same schedule with the folded forms switched on (a layer in five launches: the norms inside the products after
+    them, the adds inside the products before them, bias, rotation and append inside the q/k/v projection)."""
+    saved = kernels.fold_norms
+    kernels.fold_norms = True
+    request.addfinalizer(lambda: setattr(kernels, "fold_norms", saved))
+    test_decode_batches_of_the_benchmark(folders, kernels, "0.5B", batch, "bfloat16")
 
 
 @pytest.mark.parametrize("shape", ["D", "1.5B"])
