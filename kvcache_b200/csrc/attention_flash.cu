@@ -481,16 +481,16 @@ namespace dtma {
 using namespace tc;
 constexpr int HALVES = D / 64;
 constexpr int KW = D == 64 ? 2 : 1;                       // 64-key tiles per stage
-constexpr int STAGES = 3;
+constexpr int MAX_STAGES = 4;                             // a ring of three stages, or of four where a block has an SM to itself
 constexpr int NKEYS = 64 * KW;
 constexpr int HALF_BYTES = NKEYS * 128;                   // a [NKEYS x 64 columns] swizzled sub-tile
 constexpr int KV_BYTES = HALVES * HALF_BYTES;             // keys of a stage; values follow
 constexpr int STAGE_BYTES = 2 * KV_BYTES;
 constexpr int RECV_BYTES = 24 * (D + 2) * 4;               // nsplit * ceil(16 / nsplit) <= 24 row slots of (m, l, acc)
-constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + RECV_BYTES + 1024;
+constexpr int smem_bytes(int stages) { return stages * STAGE_BYTES + RECV_BYTES + 1024; }
 
 struct Shared {
-    uint64_t full[STAGES], empty[STAGES];
+    uint64_t full[MAX_STAGES], empty[MAX_STAGES];
     int failed;
 };
 
@@ -545,7 +545,7 @@ struct NewElements {
     }
 };
 
-template <bool FUSED>
+template <bool FUSED, int STAGES>
 __global__ void __launch_bounds__(160) flash_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k,
                                                                const __grid_constant__ CUtensorMap map_v,
                                                                const __grid_constant__ DecodeParams p,
@@ -631,16 +631,18 @@ __global__ void __launch_bounds__(160) flash_decode_tma_kernel(const __grid_cons
                 }
             }
         };
-        // The first stages are old if all their keys lie before this step's first position: fetched before the wait.
-        // Fused, all of them are: nobody but this kernel writes the pool meanwhile, and the new position's slot is
-        // made afresh in shared memory.
+        // A stage is old if all its keys lie before this step's first position: the old ones among the ring's first
+        // round are fetched before the wait.  Fused, all of them are old: nobody but this kernel writes the pool
+        // meanwhile, and the new position's slot is made afresh in shared memory.
         const int first = min(n, STAGES);
-        const bool early = FUSED || (my_begin + first * KW) * KT <= first_pos;
-        if (early)
-            for (int i = 0; i < first && ok; ++i) load_stage(i);
+        unsigned early = 0;
+        for (int i = 0; i < first && ok; ++i)
+            if (FUSED || (my_begin + (i + 1) * KW) * KT <= first_pos) { load_stage(i); early |= 1u << i; }
         pdl_wait();
         pdl_launch_dependents();
-        for (int i = early ? first : 0; i < n && ok; ++i) load_stage(i);
+        for (int i = 0; i < first && ok; ++i)
+            if (!((early >> i) & 1u)) load_stage(i);
+        for (int i = first; i < n && ok; ++i) load_stage(i);
         if (!ok && lane == 0) { atomicOr(err, KVB_DEV_TIMEOUT); sh.failed = 1; }
     } else {
         // ---- scanning warps ----
@@ -858,18 +860,16 @@ __global__ void __launch_bounds__(160) flash_decode_tma_kernel(const __grid_cons
     }
     TRACE(5)
 }
-}  // namespace dtma
 
 // How many clusters of `nsplit` blocks of the TMA decode kernel the GPU holds at once (0 on an error): a grid with more
 // clusters than that runs in waves, which costs a whole kernel's latency again.
-KVB_API int kvb_flash_decode_tma_max_clusters(int nsplit) {
-    using namespace dtma;
-    if (nsplit < 1 || nsplit > MAX_CLUSTER) return 0;
-    if (cudaFuncSetAttribute(flash_decode_tma_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES) != cudaSuccess) return 0;
+template <int STAGES>
+static int max_clusters(int nsplit) {
+    if (cudaFuncSetAttribute(flash_decode_tma_kernel<true, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes(STAGES)) != cudaSuccess) return 0;
     cudaLaunchConfig_t config = {};
     config.gridDim = dim3(nsplit * 64);
     config.blockDim = dim3(160);
-    config.dynamicSmemBytes = SMEM_BYTES;
+    config.dynamicSmemBytes = smem_bytes(STAGES);
     cudaLaunchAttribute attribute[1];
     attribute[0].id = cudaLaunchAttributeClusterDimension;
     attribute[0].val.clusterDim.x = nsplit;
@@ -878,14 +878,22 @@ KVB_API int kvb_flash_decode_tma_max_clusters(int nsplit) {
     config.attrs = attribute;
     config.numAttrs = 1;
     int clusters = 0;
-    if (cudaOccupancyMaxActiveClusters(&clusters, flash_decode_tma_kernel<true>, &config) != cudaSuccess) return 0;
+    if (cudaOccupancyMaxActiveClusters(&clusters, flash_decode_tma_kernel<true, STAGES>, &config) != cudaSuccess) return 0;
     return clusters;
+}
+}  // namespace dtma
+
+KVB_API int kvb_flash_decode_tma_max_clusters(int nsplit) {
+    if (nsplit < 1 || nsplit > MAX_CLUSTER) return 0;
+    return dtma::max_clusters<3>(nsplit);
 }
 
 // The splits as a cluster, keys and values by TMA: nsplit 1..8, page_size a power of two 8..64, num_pages the pool's
 // page count, err the device error word.  With `qkv` (then `q` is not read, `items` must be null and every segment
 // bring one token) the kernel takes the rows of the q/k/v product instead of rotated queries and appended keys:
 // bias [(Hq + 2 Hkv) D] or null, cos_t / sin_t [table_len, rot_half] (rot_half 0: no rotation).
+// Where the grid's clusters all fit with one block on an SM, the blocks take a ring of four stages instead of three:
+// at 4,096 tokens over eight splits that is a block's whole share, all of it requested before the wait.
 KVB_API int kvb_flash_decode_tma(const void* q, void* out, void* k_pages, void* v_pages, int num_pages,
                                  const int* block_table, int table_stride, const int* items, int n_items,
                                  const int* seg_q_start, const int* seg_q_len, const int* seg_kv_len, int Hq, int Hkv,
@@ -917,21 +925,29 @@ KVB_API int kvb_flash_decode_tma(const void* q, void* out, void* k_pages, void* 
     p.scale_log2 = scale * 1.4426950408889634f;
     NewRows nr{(const bf16*)qkv, bias, cos_t, sin_t, (bf16*)k_pages, (bf16*)v_pages, rot_half, table_len};
     static bool configured = false;
+    static int deep_clusters[MAX_CLUSTER + 1];                 // clusters of each size that fit with the ring of four
     if (!configured) {
-        for (int fused = 0; fused < 2; ++fused) {
-            const void* kernel = fused ? (const void*)flash_decode_tma_kernel<true> : (const void*)flash_decode_tma_kernel<false>;
-            cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+        const void* kernels[4] = {(const void*)flash_decode_tma_kernel<false, 3>, (const void*)flash_decode_tma_kernel<true, 3>,
+                                  (const void*)flash_decode_tma_kernel<false, 4>, (const void*)flash_decode_tma_kernel<true, 4>};
+        for (int i = 0; i < 4; ++i) {
+            cudaError_t e = cudaFuncSetAttribute(kernels[i], cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes(i < 2 ? 3 : 4));
             if (e != cudaSuccess) return (int)e;
-            e = cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+            e = cudaFuncSetAttribute(kernels[i], cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
             if (e != cudaSuccess) return (int)e;
         }
+        for (int c = 1; c <= MAX_CLUSTER; ++c) deep_clusters[c] = max_clusters<4>(c);
         configured = true;
     }
     dim3 grid(nsplit, Hkv, n_items);
-    if (qkv)
-        kvb_launch_cluster(flash_decode_tma_kernel<true>, dim3(grid), dim3(160), (unsigned)nsplit, (size_t)SMEM_BYTES, stream, mk, mv, p, nr, err);
+    const bool deep = (long long)n_items * Hkv <= deep_clusters[nsplit];
+    if (qkv && deep)
+        kvb_launch_cluster(flash_decode_tma_kernel<true, 4>, dim3(grid), dim3(160), (unsigned)nsplit, (size_t)smem_bytes(4), stream, mk, mv, p, nr, err);
+    else if (qkv)
+        kvb_launch_cluster(flash_decode_tma_kernel<true, 3>, dim3(grid), dim3(160), (unsigned)nsplit, (size_t)smem_bytes(3), stream, mk, mv, p, nr, err);
+    else if (deep)
+        kvb_launch_cluster(flash_decode_tma_kernel<false, 4>, dim3(grid), dim3(160), (unsigned)nsplit, (size_t)smem_bytes(4), stream, mk, mv, p, nr, err);
     else
-        kvb_launch_cluster(flash_decode_tma_kernel<false>, dim3(grid), dim3(160), (unsigned)nsplit, (size_t)SMEM_BYTES, stream, mk, mv, p, nr, err);
+        kvb_launch_cluster(flash_decode_tma_kernel<false, 3>, dim3(grid), dim3(160), (unsigned)nsplit, (size_t)smem_bytes(3), stream, mk, mv, p, nr, err);
     return kvb_launch_status();
 }
 #endif
