@@ -252,7 +252,7 @@ def time_kernel_classes(folder, batch, context, peaks, repeats=5):
     for _ in range(3):
         loop.step()
     torch.cuda.synchronize()
-    core.kernels.start_timing()
+    core.kernels.start_timing(hold_ms=12.0)           # longer than the host needs to queue a step's launches and events
     for _ in range(repeats):
         loop.step()
     report = core.kernels.stop_timing()

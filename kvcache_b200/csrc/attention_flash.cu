@@ -41,6 +41,7 @@ struct DecodeParams {
     int* tickets;              // [items, Hkv], zero between launches
     int table_stride, Hq, Hkv, page_size, page_shift, window, nsplit;
     float scale_log2;
+    int nsuper;                // TMA kernel: clusters per (item, kv head), each with its own run of keys (1: the cluster is all)
 };
 
 constexpr int MAX_SPLITS = 32;
@@ -555,7 +556,9 @@ __global__ void __launch_bounds__(160) flash_decode_tma_kernel(const __grid_cons
     extern __shared__ unsigned char smem_raw[];
     unsigned char* stages = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     __shared__ Shared sh;
-    const int split = blockIdx.x, hk = blockIdx.y, item = blockIdx.z;       // the cluster spans x: split is the rank
+    // The cluster spans x: split is the rank.  With several clusters per (item, kv head), y counts (kv head, cluster)
+    // and the keys are cut into nsuper * nsplit runs, cluster c taking runs c nsplit .. c nsplit + nsplit - 1.
+    const int split = blockIdx.x, hk = blockIdx.y / p.nsuper, super = blockIdx.y - hk * p.nsuper, item = blockIdx.z;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
     const int G = p.Hq / p.Hkv;
     // Written by the host's copy at the start of the step: safe to read before the wait.
@@ -566,8 +569,9 @@ __global__ void __launch_bounds__(160) flash_decode_tma_kernel(const __grid_cons
     const int key_lo = (p.window > 0 && first_pos - p.window + 1 > 0) ? first_pos - p.window + 1 : 0;
     const int tile_begin = key_lo / KT, tile_end = (kv_len + KT - 1) / KT;
     const int num_tiles = tile_end - tile_begin;
-    const int per_split = ((num_tiles + p.nsplit - 1) / p.nsplit + KW - 1) / KW * KW;
-    const int my_begin = tile_begin + split * per_split;
+    const int runs = p.nsplit * p.nsuper;
+    const int per_split = ((num_tiles + runs - 1) / runs + KW - 1) / KW * KW;
+    const int my_begin = min(tile_end, tile_begin + (super * p.nsplit + split) * per_split);
     const int my_end = min(tile_end, my_begin + per_split);
     const int n = max(0, (my_end - my_begin + KW - 1) / KW);                // stages to scan
 
@@ -848,15 +852,56 @@ __global__ void __launch_bounds__(160) flash_decode_tma_kernel(const __grid_cons
             e[s] = exp2f(ml[s].x - base);
             L += e[s] * ml[s].y;
         }
-        const float inv = L > 0.f ? 1.f / L : 0.f;
+        const float inv = p.nsuper > 1 ? 1.f : (L > 0.f ? 1.f / L : 0.f);     // several clusters: the sums stay unscaled
         float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
         for (int s = 0; s < MAX_CLUSTER; ++s) {
             const float ws = e[s] * inv;
             acc.x += ws * v[s].x; acc.y += ws * v[s].y; acc.z += ws * v[s].z; acc.w += ws * v[s].w;
         }
-        bf16* o = p.out + ((size_t)(q_start + row / G) * p.Hq + hk * G + row % G) * D + d;
-        *reinterpret_cast<uint2*>(o) = make_uint2(pack_bf16(acc.x, acc.y), pack_bf16(acc.z, acc.w));
+        if (p.nsuper > 1) {
+            // This cluster's (m, l, acc) of the row, left for the cluster that finishes last.
+            const size_t slot = (((size_t)item * p.Hkv + hk) * p.nsuper + super) * 16 + row;
+            *reinterpret_cast<float4*>(p.part_o + slot * D + d) = acc;
+            if (d == 0) *reinterpret_cast<float2*>(p.part_ml + slot * 2) = make_float2(M, L);
+        } else {
+            bf16* o = p.out + ((size_t)(q_start + row / G) * p.Hq + hk * G + row % G) * D + d;
+            *reinterpret_cast<uint2*>(o) = make_uint2(pack_bf16(acc.x, acc.y), pack_bf16(acc.z, acc.w));
+        }
+    }
+    if (p.nsuper > 1) {
+        // The clusters of an (item, kv head) meet through memory: each block counts in on the ticket of its rows
+        // (rows split, split + nsplit, ...); the last one to arrive adds the clusters' sums in cluster order.
+        __shared__ int last_s;
+        __threadfence();
+        __syncthreads();
+        int* ticket = p.tickets + ((size_t)item * p.Hkv + hk) * p.nsplit + split;
+        if (tid == 0) {
+            last_s = atomicAdd(ticket, 1) == p.nsuper - 1;
+            if (last_s) *ticket = 0;                                 // zero again for the next launch
+        }
+        __syncthreads();
+        if (!last_s) return;
+        __threadfence();
+        for (int idx = tid; idx < my_rows * (D / 4); idx += 160) {
+            const int k = idx / (D / 4), row = split + k * p.nsplit, d = (idx % (D / 4)) * 4;
+            const size_t slot0 = (((size_t)item * p.Hkv + hk) * p.nsuper) * 16 + row;
+            float M = NEG_INF;
+            for (int c = 0; c < p.nsuper; ++c) M = fmaxf(M, __ldcg(p.part_ml + (slot0 + (size_t)c * 16) * 2));
+            const float base = M == NEG_INF ? 0.f : M;
+            float L = 0.f;
+            float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+            for (int c = 0; c < p.nsuper; ++c) {
+                const float2 ml = __ldcg(reinterpret_cast<const float2*>(p.part_ml + (slot0 + (size_t)c * 16) * 2));
+                const float4 v = __ldcg(reinterpret_cast<const float4*>(p.part_o + (slot0 + (size_t)c * 16) * D + d));
+                const float e = exp2f(ml.x - base);
+                L += e * ml.y;
+                acc.x += e * v.x; acc.y += e * v.y; acc.z += e * v.z; acc.w += e * v.w;
+            }
+            const float inv = L > 0.f ? 1.f / L : 0.f;
+            bf16* o = p.out + ((size_t)(q_start + row / G) * p.Hq + hk * G + row % G) * D + d;
+            *reinterpret_cast<uint2*>(o) = make_uint2(pack_bf16(acc.x * inv, acc.y * inv), pack_bf16(acc.z * inv, acc.w * inv));
+        }
     }
     TRACE(5)
 }
@@ -898,10 +943,14 @@ KVB_API int kvb_flash_decode_tma(const void* q, void* out, void* k_pages, void* 
                                  const int* block_table, int table_stride, const int* items, int n_items,
                                  const int* seg_q_start, const int* seg_q_len, const int* seg_kv_len, int Hq, int Hkv,
                                  int page_size, int window, int nsplit, float scale, const void* qkv, const float* bias,
-                                 const float* cos_t, const float* sin_t, int rot_half, int table_len, int* err,
-                                 cudaStream_t stream) {
+                                 const float* cos_t, const float* sin_t, int rot_half, int table_len, int nsuper,
+                                 float* scratch, int* tickets, int* err, cudaStream_t stream) {
     using namespace dtma;
     if (n_items <= 0) return KVB_OK;
+    // Several clusters per (item, kv head): `scratch` holds n_items * Hkv * nsuper * 16 * (D + 2) floats, `tickets`
+    // n_items * Hkv * nsplit ints that are zero before the first launch (the kernel leaves them zero).
+    if (nsuper < 1 || nsuper > 64 || (nsuper > 1 && (nsplit < 2 || qkv || !scratch || !tickets))) return KVB_ERR_SHAPE;
+    if ((long long)Hkv * nsuper > 65535) return KVB_ERR_LIMIT;
     if (Hkv < 1 || Hq % Hkv != 0 || Hq / Hkv > 16) return KVB_ERR_SHAPE;
     if (page_size < 8 || page_size > 64 || (page_size & (page_size - 1)) != 0) return KVB_ERR_SHAPE;
     if (nsplit < 1 || nsplit > MAX_CLUSTER || n_items > 65535 || Hkv > 65535) return KVB_ERR_LIMIT;
@@ -917,11 +966,11 @@ KVB_API int kvb_flash_decode_tma(const void* q, void* out, void* k_pages, void* 
     p.q = (const bf16*)q; p.out = (bf16*)out; p.k_pages = (const bf16*)k_pages; p.v_pages = (const bf16*)v_pages;
     p.block_table = block_table; p.items = items; p.seg_q_start = seg_q_start; p.seg_q_len = seg_q_len;
     p.seg_kv_len = seg_kv_len;
-    p.part_o = nullptr; p.part_ml = nullptr; p.tickets = nullptr;
+    p.part_o = scratch; p.part_ml = scratch ? scratch + (size_t)n_items * Hkv * nsuper * 16 * D : nullptr; p.tickets = tickets;
     p.table_stride = table_stride; p.Hq = Hq; p.Hkv = Hkv; p.page_size = page_size;
     p.page_shift = 0;
     while ((1 << p.page_shift) < page_size) ++p.page_shift;
-    p.window = window; p.nsplit = nsplit;
+    p.window = window; p.nsplit = nsplit; p.nsuper = nsuper;
     p.scale_log2 = scale * 1.4426950408889634f;
     NewRows nr{(const bf16*)qkv, bias, cos_t, sin_t, (bf16*)k_pages, (bf16*)v_pages, rot_half, table_len};
     static bool configured = false;
@@ -938,8 +987,8 @@ KVB_API int kvb_flash_decode_tma(const void* q, void* out, void* k_pages, void* 
         for (int c = 1; c <= MAX_CLUSTER; ++c) deep_clusters[c] = max_clusters<4>(c);
         configured = true;
     }
-    dim3 grid(nsplit, Hkv, n_items);
-    const bool deep = (long long)n_items * Hkv <= deep_clusters[nsplit];
+    dim3 grid(nsplit, Hkv * nsuper, n_items);
+    const bool deep = (long long)n_items * Hkv * nsuper <= deep_clusters[nsplit];
     if (qkv && deep)
         kvb_launch_cluster(flash_decode_tma_kernel<true, 4>, dim3(grid), dim3(160), (unsigned)nsplit, (size_t)smem_bytes(4), stream, mk, mv, p, nr, err);
     else if (qkv)

@@ -166,6 +166,20 @@ static inline cudaError_t kvb_launch_cluster(void (*kernel)(KArgs...), dim3 grid
     return cudaLaunchKernelEx(&config, kernel, static_cast<KArgs>(args)...);
 }
 
+// The number of SMs of the current device, asked once.
+static inline int kvb_sm_count() {
+    static int count = 0;
+    if (count == 0) {
+        int device = 0, found = 0;
+        if (cudaGetDevice(&device) == cudaSuccess &&
+            cudaDeviceGetAttribute(&found, cudaDevAttrMultiProcessorCount, device) == cudaSuccess && found > 0)
+            count = found;
+        else
+            return 1;
+    }
+    return count;
+}
+
 static inline int kvb_launch_status() {
     cudaError_t e = cudaGetLastError();
     return e == cudaSuccess ? KVB_OK : (int)e;

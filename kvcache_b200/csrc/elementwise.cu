@@ -245,11 +245,12 @@ KVB_API int kvb_silu_mul(int dtype, const void* gate_up, void* out, int T, int I
     if (total == 0) return KVB_OK;
     const int threads = 256;
     size_t blocks = (total + threads - 1) / threads;
-    if (blocks > 148 * 16) blocks = 148 * 16;
+    const size_t most = (size_t)kvb_sm_count() * 16;         // a grid-stride loop takes the rest
+    if (blocks > most) blocks = most;
     if (dtype == KVB_BF16 && I % 8 == 0 && ((((uintptr_t)gate_up | (uintptr_t)out) & 15) == 0)) {
         const size_t groups = total / 8;
         size_t vblocks = (groups + threads - 1) / threads;
-        if (vblocks > 148 * 16) vblocks = 148 * 16;
+        if (vblocks > most) vblocks = most;
         kvb_launch(silu_mul_vec8_kernel, dim3((int)vblocks), dim3(threads), 0, stream, (const bf16*)gate_up, (bf16*)out, I, groups, interleaved);
         return kvb_launch_status();
     }

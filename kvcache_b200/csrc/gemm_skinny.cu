@@ -59,7 +59,7 @@ __device__ __forceinline__ uint4 ld_stream(const void* p, uint64_t policy) {
     return v;
 }
 
-constexpr int BLOCKS_WANTED = 148 * 2;
+static inline int blocks_wanted() { return 2 * kvb_sm_count(); }     // two blocks an SM
 
 enum { EPI_PLAIN = 0, EPI_ACT = 1, EPI_RESID = 2, EPI_ROPE = 3 };
 
@@ -421,7 +421,7 @@ static inline Split choose_split(int N, int kblocks) {
     const int blocks = (N + 15) / 16;
     // K over a cluster while that still leaves blocks wanted and every warp of a block something to do.
     Split s{1, 4};
-    while (s.ksplit < 8 && blocks * s.ksplit * 2 <= BLOCKS_WANTED && kblocks / (s.ksplit * 2) >= 4) s.ksplit *= 2;
+    while (s.ksplit < 8 && blocks * s.ksplit * 2 <= blocks_wanted() && kblocks / (s.ksplit * 2) >= 4) s.ksplit *= 2;
     // Warps split a block's share of K: enough of them to keep loads in flight, not so many that a warp has nothing to do.
     s.warps = kblocks / s.ksplit >= 32 ? 8 : 4;
     return s;

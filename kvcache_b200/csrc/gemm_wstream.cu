@@ -229,16 +229,7 @@ static int make_map(CUtensorMap* map, const void* base, int rows, int cols, int 
     return make_bf16_map(map, base, rows, cols, cols, box_rows);
 }
 
-static int sm_count() {
-    static int count = 0;
-    if (count == 0) {
-        int device = 0;
-        if (cudaGetDevice(&device) != cudaSuccess ||
-            cudaDeviceGetAttribute(&count, cudaDevAttrMultiProcessorCount, device) != cudaSuccess)
-            count = 148;
-    }
-    return count;
-}
+static int sm_count() { return kvb_sm_count(); }
 
 // K over a cluster while the grid stays within two blocks a SM and every block keeps a K block.  It depends on the
 // weight's shape alone.

@@ -128,7 +128,8 @@ _SIGNATURES = {
         "kvb_flash_decode_tma_max_clusters": [_c_int],
         "kvb_flash_decode_tma": [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_int, _c_void_p, _c_int,
                                  _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float,
-                                 _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_void_p, _c_void_p],
+                                 _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_void_p, _c_void_p,
+                                 _c_void_p, _c_void_p],
         "kvb_flash_prefill": [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_int, _c_void_p,
                               _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_float, _c_void_p],
     },
@@ -221,9 +222,15 @@ class CudaKernels(KernelSet):
         self.decode_merge = "tma"
         self.decode_cluster_max = 8          # the kernel's limit
         self.decode_pow2_splits = True
-        self.decode_ctas_wanted = 148 * 2    # the split over the keys aims at this many blocks in flight
-        self.decode_min_tiles = 4            # ... but gives a split at least this many 64-key tiles
         self.sm_count = torch.cuda.get_device_properties(self.device).multi_processor_count
+        self.decode_ctas_wanted = 2 * self.sm_count    # the split over the keys aims at this many blocks in flight
+        self.decode_min_tiles = 4            # ... but gives a split at least this many 64-key tiles
+        # Most clusters one (request, kv head) is given by the TMA kernel (0: always one).  The clusters meet through memory,
+        # which costs about 5 us; it pays where there are fewer blocks than SMs and each block still keeps eight 64-key tiles -
+        # one request: 10.5 -> 8.9 us a layer at 8,192 tokens, 18.0 -> 10.9 at 16,000, 34.6 -> 11.8 at 32,000 - and not where
+        # the blocks fill the GPU already (8 requests at 8,192 tokens: 11.7 -> 17.3 us).
+        self.decode_superclusters = 16
+        self.decode_super_min_tiles = 8
         self.error_word = torch.zeros(1, dtype=torch.int32, device=self.device)
         self.launches = 0
         self.launch_counts: Counter = Counter()      # launches by kernel, as issued from the host (a replayed graph adds none)
@@ -531,8 +538,8 @@ class CudaKernels(KernelSet):
             None, _ptr(out), _ptr(kv.k_pages), _ptr(kv.v_pages), kv.k_pages.shape[0], _ptr(kv.block_table),
             kv.block_table.shape[1], None, n, _ptr(batch.seg_q_start), _ptr(batch.seg_q_len), _ptr(batch.seg_kv_len),
             num_heads, Hkv, kv.page_size, spec.window or 0, nsplit, float(scale), _ptr(qkv), _ptr(bias), _ptr(cos), _ptr(sin),
-            0 if cos is None else cos.shape[1], 0 if cos is None else cos.shape[0], _ptr(self.error_word), self._stream()),
-            "flash_decode_tma (rotation and append fused)")
+            0 if cos is None else cos.shape[1], 0 if cos is None else cos.shape[0], 1, None, None, _ptr(self.error_word),
+            self._stream()), "flash_decode_tma (rotation and append fused)")
         return True
 
     def paged_attention(self, q: torch.Tensor, batch: StepBatch, kv: PagedKVView, out: torch.Tensor,
@@ -579,14 +586,30 @@ class CudaKernels(KernelSet):
                     nsplit = self._cluster_splits(n, Hkv, tiles)
                     if self._tma_decode(D, kv):
                         self._count("flash_decode_tma")
-                        nsplit = self._fit_clusters(lib, D, n * Hkv, nsplit)
+                        # Few requests with many keys: several clusters for each (request, kv head), each with a run of
+                        # the keys, so that the whole GPU streams them; their sums meet in scratch, the last to finish
+                        # adds them in cluster order.  Like the split itself this follows from the block table's
+                        # capacity and the number of requests, never from the lengths of the moment.
+                        nsuper = 1
+                        if nsplit > 1 and self.decode_superclusters:
+                            nsuper = max(1, min(self.decode_superclusters, self.sm_count // (n * Hkv * nsplit),
+                                                tiles // (max(self.decode_min_tiles, self.decode_super_min_tiles) * nsplit)))
+                            while nsuper > 1 and n * Hkv * nsuper > self._tma_clusters(lib, D, nsplit):
+                                nsuper -= 1
+                        nsplit = self._fit_clusters(lib, D, n * Hkv * nsuper, nsplit)
+                        if nsplit == 1:
+                            nsuper = 1
+                        scratch = tickets = None
+                        if nsuper > 1:
+                            scratch = workspace.buffer("attn.decode_super", (n * Hkv * nsuper * 16 * (D + 2),), torch.float32)
+                            tickets = workspace.zeros("attn.decode_super_tickets", (n * Hkv * 8,), torch.int32)
                         _check(lib.kvb_flash_decode_tma(
                             _ptr(q), _ptr(out), _ptr(kv.k_pages), _ptr(kv.v_pages), kv.k_pages.shape[0],
                             _ptr(kv.block_table), kv.block_table.shape[1],
                             _ptr(None if n == batch.num_segments else items), n,   # every segment, in order: no list
                             _ptr(batch.seg_q_start), _ptr(batch.seg_q_len), _ptr(batch.seg_kv_len), num_heads, Hkv,
                             kv.page_size, spec.window or 0, nsplit, float(scale), None, None, None, None, 0, 0,
-                            _ptr(self.error_word), self._stream()), "flash_decode_tma")
+                            nsuper, _ptr(scratch), _ptr(tickets), _ptr(self.error_word), self._stream()), "flash_decode_tma")
                         return
                     self._count("flash_decode_cluster")
                     _check(lib.kvb_flash_decode_cluster(

@@ -160,6 +160,14 @@ def compile_module(module: str, variant: str = "", extra_flags: Sequence[str] = 
         raise BuildError(f"nvcc failed on {info['src']} (exit {proc.returncode}):\n{' '.join(cmd)}\n{output}")
     os.replace(tmp, out)
     _log(f"  built {os.path.basename(out)} in {time.time() - start:.1f} s")
+    # Libraries of this module made from older sources are of no use any more.
+    prefix = os.path.basename(out).rsplit(".", 2)[0] + "."
+    for name in os.listdir(os.path.dirname(out)):
+        if name.startswith(prefix) and name.endswith(".so") and name != os.path.basename(out):
+            try:
+                os.remove(os.path.join(os.path.dirname(out), name))
+            except OSError:
+                pass
     return out
 
 
