@@ -373,7 +373,7 @@ def run_ours(args) -> int:
     clocks = ClockSampler().start()
     with tempfile.TemporaryDirectory() as tmp:
         folder = make_folder(tmp, args.layers)
-        main_run = time_decode(folder, args.batch, CONTEXT, args.steps, args.warmup, clocks, "decode", use_graphs=not args.no_graphs)
+        main_run = time_decode(folder, args.batch, args.context, args.steps, args.warmup, clocks, "decode", use_graphs=not args.no_graphs)
         points = {}
         if not args.skip_points:
             for b in (1, 64):
@@ -383,20 +383,21 @@ def run_ours(args) -> int:
             points["b1_prompt29_new256"] = round(1e6 / published["median_us"], 1)
         prefill = {"ms": float("nan"), "tok_s": float("nan"), "flops": float("nan")} if args.skip_prefill else \
             time_prefill(folder, PREFILL_TOKENS, clocks)
-        e2e = None if args.skip_e2e else time_e2e(folder, args.batch, CONTEXT, args.steps, args.warmup, clocks)
-        kernels = None if args.skip_kernels else time_kernel_classes(folder, args.batch, CONTEXT, peaks)
+        e2e = None if args.skip_e2e else time_e2e(folder, args.batch, args.context, args.steps, args.warmup, clocks)
+        kernels = None if args.skip_kernels else time_kernel_classes(folder, args.batch, args.context, peaks)
     clocks.stop()
 
     achieved = main_run["bytes_per_step"] / (main_run["ms_per_step"] / 1e3) / 1e9
     headline_clocks = dict(clocks.regions.get("decode", {}), how=clocks.how,
                            regions={k: v for k, v in clocks.regions.items() if k != "decode"})
     line = {
-        "metric": METRIC, "value": round(main_run["tok_s"], 1), "unit": "tok/s", "n_gpus": 1, "steps": args.steps,
+        "metric": METRIC if (args.batch, args.context) == (8, CONTEXT) else f"decode tok/s at batch {args.batch} (Qwen2.5-0.5B shape, context {args.context})",
+        "value": round(main_run["tok_s"], 1), "unit": "tok/s", "n_gpus": 1, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": round(main_run["ms_per_step"], 4), "ms_per_step_p50": round(main_run["ms_p50"], 4),
         "higher_is_better": True, "scaling": "weak",
         "vs_baseline": round(points["b1_prompt29_new256"] / PUBLISHED_TOK_S, 2) if "b1_prompt29_new256" in points else None,
         "dtype": "bf16", "data": "synthetic", "impl": "ours",
-        "config": bench_config(args.batch, args.layers, args.steps, args.warmup, peaks["source"]),
+        "config": dict(bench_config(args.batch, args.layers, args.steps, args.warmup, peaks["source"]), seq_len=args.context),
         "prefill": {"value": round(prefill["tok_s"], 1), "tokens": PREFILL_TOKENS, "ms": round(prefill["ms"], 3),
                     "frac": round(prefill["flops"] / (prefill["ms"] / 1e3) / (peaks["bf16_tflops"] * 1e12), 4)},
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peaks["hbm_gbs"], "unit": "GB/s",
@@ -493,6 +494,7 @@ def main() -> int:
     parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
     parser.add_argument("--layers", type=int, default=QWEN25_05B["num_hidden_layers"])
     parser.add_argument("--batch", type=int, default=8)
+    parser.add_argument("--context", type=int, default=CONTEXT, help="tokens each request has cached while it decodes")
     parser.add_argument("--skip-e2e", action="store_true")
     parser.add_argument("--skip-points", action="store_true")
     parser.add_argument("--skip-prefill", action="store_true")
