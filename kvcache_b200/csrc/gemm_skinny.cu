@@ -35,6 +35,8 @@
 //    the pair by the row's position, and writes queries to their buffer and keys and values straight into their
 //    cache pages (k_add_bias, k_rope_pos and k_batched_write_kv of the reference, src/qwen_kernels.cu:45-53,
 //    :253-290, folded in).
+#include <stdio.h>
+
 #include "common.cuh"
 
 #ifdef KVB_TRACE
@@ -80,6 +82,7 @@ struct Fused {
     bf16* q_out;              // [M, Hq * D]
     int* err;
     int table_len, table_stride, Hq, Hkv, D, page_size, page_shift, writes;
+    unsigned hold_ns;         // the block sleeps this long before it asks for its weights (see `hold_of`)
 };
 
 __device__ __forceinline__ void unpack8(const uint4& v, float (&f)[8]) {
@@ -101,13 +104,16 @@ __device__ __forceinline__ uint4 pack8(const float (&f)[8]) {
     return make_uint4(raw[0], raw[1], raw[2], raw[3]);
 }
 
+// One 16-row tile per block: the blocks of the widest products (the gate/up projection) are all on the SMs at once only
+// with five blocks of four warps per SM, that is within 96 registers a thread.
 template <int RT, int NT, int EPI, bool PRE, typename TOut>
-__global__ void __launch_bounds__(256) gemm_skinny_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w,
+__global__ void __maxnreg__((RT == 1 && NT <= 2) ? 96 : 255) gemm_skinny_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w,
                                                           const float* __restrict__ bias, TOut* __restrict__ y, int M,
                                                           int N, int K, int x_stride, int ksplit,
                                                           const __grid_constant__ Fused fz) {
     SKINNY_TRACE(0)
     if (ksplit > 1) cluster_arrive_started();
+    if (fz.hold_ns) __nanosleep(fz.hold_ns);
     extern __shared__ __align__(16) float red[];          // [warps + ksplit][RT][NT][32 lanes][4]; PRE: then sums of squares and the norm's weight
     const int warps = blockDim.x >> 5, warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
     const int rank = blockIdx.x % ksplit;                  // the cluster spans x
@@ -156,23 +162,42 @@ __global__ void __launch_bounds__(256) gemm_skinny_kernel(const bf16* __restrict
         for (int i = threadIdx.x * 4; i < K; i += blockDim.x * 4)
             *reinterpret_cast<float4*>(nw_s + i) = __ldg(reinterpret_cast<const float4*>(fz.norm_w + i));
     }
+    // What the first fragment this thread finishes will need beyond the sums, none of it made by the kernel before:
+    // the elements of the residual stream it updates (last written three kernels ago), or the positions, angles,
+    // biases and pages of its rows (the step's metadata).  Asked for now, in registers by the time they are wanted.
+    const int first_idx = threadIdx.x * ksplit + rank;
+    float h_first[4] = {0.f, 0.f, 0.f, 0.f};
+    int pos_first[2] = {0, 0}, page_first[2] = {-1, -1};
+    float cs_first[2] = {1.f, 1.f}, sn_first[2] = {0.f, 0.f};
+    if ((EPI == EPI_RESID || EPI == EPI_ROPE) && first_idx < F) {
+        const int l2 = first_idx & 31, rj = first_idx >> 5, r = rj / NT, j = rj - r * NT;
+        const int m = 8 * j + 2 * (l2 & 3), n = n0 + 16 * r + (l2 >> 2);
+        if (EPI == EPI_RESID) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int nn = n + 8 * (e >> 1), mm = m + (e & 1);
+                if (nn < N && mm < M) h_first[e] = fz.h[(size_t)mm * N + nn];
+            }
+        } else {
+            const int head = n / fz.D, d = ((n - head * fz.D) >> 4) * 8 + (l2 >> 2);
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+                if (m + e >= M || n + 8 >= N) continue;
+                const int pos = fz.positions[m + e];
+                pos_first[e] = pos;
+                if (head < fz.Hq + fz.Hkv && fz.cos_t && pos < fz.table_len) {
+                    cs_first[e] = fz.cos_t[(size_t)pos * (fz.D >> 1) + d];
+                    sn_first[e] = fz.sin_t[(size_t)pos * (fz.D >> 1) + d];
+                }
+                if (head >= fz.Hq) page_first[e] = fz.block_table[(size_t)fz.row_segment[m + e] * fz.table_stride + (pos >> fz.page_shift)];
+            }
+        }
+    }
     SKINNY_TRACE(1)
     pdl_wait();
     pdl_launch_dependents();
     if (PRE) __syncthreads();
     SKINNY_TRACE(2)
-    // EPI_RESID: the four elements of the residual stream that this thread will update first, requested now.
-    const int first_idx = threadIdx.x * ksplit + rank;
-    float h_first[4] = {0.f, 0.f, 0.f, 0.f};
-    if (EPI == EPI_RESID && first_idx < F) {
-        const int l2 = first_idx & 31, rj = first_idx >> 5, r = rj / NT, j = rj - r * NT;
-        const int m = 8 * j + 2 * (l2 & 3), n = n0 + 16 * r + (l2 >> 2);
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-            const int nn = n + 8 * (e >> 1), mm = m + (e & 1);
-            if (nn < N && mm < M) h_first[e] = fz.h[(size_t)mm * N + nn];
-        }
-    }
 
     float acc[RT][NT][4];
 #pragma unroll
@@ -370,11 +395,13 @@ __global__ void __launch_bounds__(256) gemm_skinny_kernel(const bf16* __restrict
                     const int mm = m + e;
                     if (mm >= M) continue;
                     const float lo = vals[e] + b_lo, hi = vals[e + 2] + b_hi;
-                    const int pos = fz.positions[mm];
+                    const bool ahead = idx == first_idx;                   // fetched before the wait
+                    const int pos = ahead ? pos_first[e] : fz.positions[mm];
                     float out_lo = lo, out_hi = hi;
                     if (head < fz.Hq + fz.Hkv && fz.cos_t) {
                         if (pos < fz.table_len) {
-                            const float c = fz.cos_t[(size_t)pos * half + d], sn = fz.sin_t[(size_t)pos * half + d];
+                            const float c = ahead ? cs_first[e] : fz.cos_t[(size_t)pos * half + d];
+                            const float sn = ahead ? sn_first[e] : fz.sin_t[(size_t)pos * half + d];
                             out_lo = lo * c - hi * sn;
                             out_hi = hi * c + lo * sn;
                         } else {
@@ -388,7 +415,8 @@ __global__ void __launch_bounds__(256) gemm_skinny_kernel(const bf16* __restrict
                     } else if (fz.writes) {
                         const bool is_k = head < fz.Hq + fz.Hkv;
                         const int hk = head - fz.Hq - (is_k ? 0 : fz.Hkv);
-                        const int page = fz.block_table[(size_t)fz.row_segment[mm] * fz.table_stride + (pos >> fz.page_shift)];
+                        const int page = ahead ? page_first[e]
+                                               : fz.block_table[(size_t)fz.row_segment[mm] * fz.table_stride + (pos >> fz.page_shift)];
                         if (page < 0) {
                             atomicOr(fz.err, KVB_DEV_BAD_PAGE);
                         } else {
@@ -450,9 +478,25 @@ bool resident(int N, int K) {
     return (long long)blocks * s.ksplit <= (long long)cached * sm_count;
 }
 
+// Nanoseconds a kernel of each epilogue kind holds back before it asks for its weights: KVB_SKINNY_HOLD_NS =
+// "plain,act,resid,rope" (default: none).  A kernel starts as soon as its predecessor has passed its own wait, and the
+// predecessor's first loads after that wait are the ones it cannot go on without.
+static inline unsigned hold_of(int epi) {
+    static int parsed = 0;
+    static unsigned ns[4] = {0, 0, 0, 0};
+    if (!parsed) {
+        const char* v = getenv("KVB_SKINNY_HOLD_NS");
+        if (v) sscanf(v, "%u,%u,%u,%u", &ns[0], &ns[1], &ns[2], &ns[3]);
+        parsed = 1;
+    }
+    return ns[epi & 3];
+}
+
 template <int RT, int NT, int EPI, bool PRE, typename TOut>
-int launch(const bf16* x, const bf16* w, const float* bias, TOut* y, int M, int N, int K, int x_stride, const Fused& fz,
+int launch(const bf16* x, const bf16* w, const float* bias, TOut* y, int M, int N, int K, int x_stride, const Fused& fz_in,
            cudaStream_t stream) {
+    Fused fz = fz_in;
+    fz.hold_ns = hold_of(EPI);
     const int blocks = (N + 16 * RT - 1) / (16 * RT);
     const Split s = choose_split(N, K / 32);
     const int ksplit = s.ksplit, warps = s.warps;
