@@ -35,8 +35,6 @@
 //    the pair by the row's position, and writes queries to their buffer and keys and values straight into their
 //    cache pages (k_add_bias, k_rope_pos and k_batched_write_kv of the reference, src/qwen_kernels.cu:45-53,
 //    :253-290, folded in).
-#include <stdio.h>
-
 #include "common.cuh"
 
 #ifdef KVB_TRACE
@@ -82,7 +80,6 @@ struct Fused {
     bf16* q_out;              // [M, Hq * D]
     int* err;
     int table_len, table_stride, Hq, Hkv, D, page_size, page_shift, writes;
-    unsigned hold_ns;         // the block sleeps this long before it asks for its weights (see `hold_of`)
 };
 
 __device__ __forceinline__ void unpack8(const uint4& v, float (&f)[8]) {
@@ -113,7 +110,6 @@ __global__ void __maxnreg__((RT == 1 && NT <= 2) ? 96 : 255) gemm_skinny_kernel(
                                                           const __grid_constant__ Fused fz) {
     SKINNY_TRACE(0)
     if (ksplit > 1) cluster_arrive_started();
-    if (fz.hold_ns) __nanosleep(fz.hold_ns);
     extern __shared__ __align__(16) float red[];          // [warps + ksplit][RT][NT][32 lanes][4]; PRE: then sums of squares and the norm's weight
     const int warps = blockDim.x >> 5, warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
     const int rank = blockIdx.x % ksplit;                  // the cluster spans x
@@ -478,25 +474,9 @@ bool resident(int N, int K) {
     return (long long)blocks * s.ksplit <= (long long)cached * sm_count;
 }
 
-// Nanoseconds a kernel of each epilogue kind holds back before it asks for its weights: KVB_SKINNY_HOLD_NS =
-// "plain,act,resid,rope" (default: none).  A kernel starts as soon as its predecessor has passed its own wait, and the
-// predecessor's first loads after that wait are the ones it cannot go on without.
-static inline unsigned hold_of(int epi) {
-    static int parsed = 0;
-    static unsigned ns[4] = {0, 0, 0, 0};
-    if (!parsed) {
-        const char* v = getenv("KVB_SKINNY_HOLD_NS");
-        if (v) sscanf(v, "%u,%u,%u,%u", &ns[0], &ns[1], &ns[2], &ns[3]);
-        parsed = 1;
-    }
-    return ns[epi & 3];
-}
-
 template <int RT, int NT, int EPI, bool PRE, typename TOut>
-int launch(const bf16* x, const bf16* w, const float* bias, TOut* y, int M, int N, int K, int x_stride, const Fused& fz_in,
+int launch(const bf16* x, const bf16* w, const float* bias, TOut* y, int M, int N, int K, int x_stride, const Fused& fz,
            cudaStream_t stream) {
-    Fused fz = fz_in;
-    fz.hold_ns = hold_of(EPI);
     const int blocks = (N + 16 * RT - 1) / (16 * RT);
     const Split s = choose_split(N, K / 32);
     const int ksplit = s.ksplit, warps = s.warps;
