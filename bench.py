@@ -277,8 +277,8 @@ def time_prefill(folder, tokens, clocks, repeats=3, warm=5):
     options = EngineOptions(dtype="bfloat16", page_size=16, max_cached_tokens=tokens + 16, max_running=1,
                             max_tokens_per_step=tokens, max_model_len=tokens + 16, use_graphs=True)
     core = EngineCore(folder, options)
-    ids = torch.randint(0, core.model.vocab_size, (tokens,), generator=torch.Generator().manual_seed(3)).tolist()
-    times = []
+    ids = torch.randint(0, core.model.vocab_size, (tokens,), generator=torch.Generator().manual_seed(3)).to(torch.int32).numpy()
+    times = []                                       # host token ids, as the scheduler hands a prompt's portion to the step
     with clocks.region("prefill"):
         for i in range(warm + repeats):              # the step is replayed from a graph once its shape has come a few times
             slot = core.cache.admit()

@@ -7,7 +7,7 @@ reference returns -1 / false and lets the caller go on, this raises.
 """
 from __future__ import annotations
 
-from typing import Dict, List, Optional
+from typing import Dict, List, Optional, Sequence
 
 import numpy as np
 
@@ -38,6 +38,30 @@ class PageAllocator:
         page = self._free.pop()
         self._held[page] = True
         return page
+
+    def alloc_many(self, count: int) -> List[int]:
+        """What `count` calls of `alloc` would hand out, in that order; nothing if the pool has fewer."""
+        if count > len(self._free):
+            raise OutOfPages(f"{count} pages needed, {len(self._free)} free")
+        if count <= 0:
+            return []
+        pages = self._free[-count:]
+        pages.reverse()
+        del self._free[-count:]
+        self._held[pages] = True
+        return pages
+
+    def free_many(self, pages: Sequence[int]) -> None:
+        """`free` for each page in turn; nothing is freed if one of them is out of range, not held, or listed twice."""
+        if len(pages) == 0:
+            return
+        ids = np.asarray(pages, dtype=np.int64)
+        if ids.min() < 0 or ids.max() >= self.num_pages:
+            raise ValueError(f"a page of {ids.tolist()} is outside the pool of {self.num_pages}")
+        if not self._held[ids].all() or len(np.unique(ids)) != len(ids):
+            raise ValueError(f"a page of {ids.tolist()} is freed twice (or was never handed out)")
+        self._held[ids] = False
+        self._free.extend(ids.tolist())
 
     def free(self, page: int) -> None:
         if not 0 <= page < self.num_pages:
@@ -100,15 +124,14 @@ class GroupPages:
         return max(0, len(take) - len(release) - self.allocator.num_free)
 
     def give_back(self, slot: int, logical_pages: range) -> None:
-        for i in logical_pages:
-            self.allocator.free(int(self.table[slot, i]))
-            self.table[slot, i] = -1
+        if len(logical_pages):
+            span = slice(logical_pages.start, logical_pages.stop)
+            self.allocator.free_many(self.table[slot, span])
+            self.table[slot, span] = -1
 
     def take(self, slot: int, logical_pages: range, new_lo: int, new_hi: int) -> None:
-        if len(logical_pages) > self.allocator.num_free:
-            raise OutOfPages(f"{len(logical_pages)} pages needed, {self.allocator.num_free} free")
-        for i in logical_pages:
-            self.table[slot, i] = self.allocator.alloc()
+        if len(logical_pages):
+            self.table[slot, logical_pages.start:logical_pages.stop] = self.allocator.alloc_many(len(logical_pages))
         self._lo[slot], self._hi[slot] = new_lo, new_hi
 
     def extend(self, slot: int, start: int, end: int) -> None:
@@ -122,8 +145,7 @@ class GroupPages:
 
     def release(self, slot: int) -> None:
         lo, hi = int(self._lo[slot]), int(self._hi[slot])
-        for i in range(lo, hi):
-            self.allocator.free(int(self.table[slot, i]))
+        self.allocator.free_many(self.table[slot, lo:hi])
         self.table[slot, lo:hi] = -1
         self._lo[slot] = self._hi[slot] = 0
 

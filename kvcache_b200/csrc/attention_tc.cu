@@ -11,9 +11,12 @@
 //               S lands in tensor memory, 128 lanes x 64 columns.
 //   softmax     each thread reads its row of S with tcgen05.ld, masks it (causal limit, window), keeps the running
 //               maximum and sum in base 2 (the reference's recurrence, src/qwen_kernels.cu:159-176), and writes
-//               P = 2^(s - m) as bfloat16 into swizzled shared memory.
-//   O_t = P V   tcgen05.mma, M 128 x N head size x K 64 keys; P is the A operand (K-major), the value tile as
-//               TMA left it - rows of keys, head size contiguous - is the B operand in MN-major form.
+//               P = 2^(s - m) as bfloat16 back into tensor memory (tcgen05.st), over the columns that held S.
+//   O_t = P V   tcgen05.mma, M 128 x N head size x K 64 keys; P is the A operand, read from tensor memory, the value
+//               tile as TMA left it - rows of keys, head size contiguous - is the B operand in MN-major form.
+//               (P went through shared memory at first: its stores and the product's reads of it were two fifths of
+//               the block's shared-memory traffic, and shared memory, which two blocks of an SM share, was what the
+//               MMA issue waited for.)
 //               The thread adds its row of O_t (tcgen05.ld) into float32 registers, o = o * 2^(m_old - m_new) + O_t.
 // S, P and O_t exist twice: while the threads run the softmax of tile i + 1, the tensor core multiplies P V of
 // tile i and Q K^T of tile i + 2, and a thread adds O_t of tile i only after it has handed over P of tile i + 1 -
@@ -36,9 +39,9 @@ constexpr int BQ = 128, BKEYS = 64;                  // query rows and keys of a
 constexpr int HALVES = D / 64;                       // 64-wide (128-byte) column blocks of a head
 constexpr int SUB_BYTES = BQ * 128;                  // a [128 rows x 64 columns] bfloat16 sub-tile (Q, P), swizzled
 constexpr int KV_SUB_BYTES = BKEYS * 128;            // a [64 keys x 64 columns] sub-tile (K, V)
-constexpr int Q_BYTES = HALVES * SUB_BYTES, KV_BYTES = HALVES * KV_SUB_BYTES, P_BYTES = SUB_BYTES;
+constexpr int Q_BYTES = HALVES * SUB_BYTES, KV_BYTES = HALVES * KV_SUB_BYTES;
 constexpr int STAGES = 3;                            // of keys, and of values: two rings, each filled on its own
-constexpr int SMEM_BYTES = Q_BYTES + 2 * P_BYTES + 2 * STAGES * KV_BYTES + 1024;
+constexpr int SMEM_BYTES = Q_BYTES + 2 * STAGES * KV_BYTES + 1024;
 constexpr int TMEM_COLS = D == 64 ? 256 : 512;       // S: 2 x 64 columns, O_t: 2 x D columns
 constexpr int THREADS = 192;                         // warps 0-3: softmax rows; warp 4: MMA issue; warp 5: TMA loads
 constexpr float NEG_INF = -INFINITY;
@@ -89,8 +92,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     extern __shared__ unsigned char smem_raw[];
     unsigned char* base = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     unsigned char* q_s = base;
-    unsigned char* p_s = q_s + Q_BYTES;
-    unsigned char* k_s = p_s + 2 * P_BYTES;                   // key stage s at k_s + s KV_BYTES
+    unsigned char* k_s = q_s + Q_BYTES;                       // key stage s at k_s + s KV_BYTES
     unsigned char* v_s = k_s + STAGES * KV_BYTES;             // value stage s at v_s + s KV_BYTES
     __shared__ Shared sh;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -139,15 +141,18 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
         bool ok = true;
         // Key (or value) tile kt_begin + i into stage i % STAGES of its ring, once the MMA that read the stage's
         // last tenant has finished.
-        // Lane pg looks up page pg of tile kt_begin + i (one coalesced read of the block table for the whole tile);
-        // -1 where the tile has no page that the rows can see.
 #ifdef KVB_TRACE
         long long l_wk = 0, l_wv = 0, l_start = clock64();
 #endif
-        auto lookup = [&](int i) -> int {
+        // Pages are looked up a batch of tiles at a time, one entry a lane (32 / pages_per_tile tiles), and the next batch
+        // while this one is used: a read of the block table takes about as long as a tile's softmax, and one read a tile,
+        // waited for tile by tile, held the copies back.  -1 where the rows can see none of a page's keys.
+        const int tiles_per_batch = 32 / pages_per_tile;
+        auto lookup_batch = [&](int b) -> int {
+            const int tile = b * tiles_per_batch + lane / pages_per_tile;
             int page = -1;
-            if (lane < pages_per_tile) {
-                const int first_key = (kt_begin + i) * BKEYS + lane * p.page_size;
+            if (tile < n) {
+                const int first_key = (kt_begin + tile) * BKEYS + (lane % pages_per_tile) * p.page_size;
                 if (first_key <= pos_last && first_key + p.page_size > key_lo) page = table[first_key >> p.page_shift];
             }
             return page;
@@ -198,13 +203,20 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
             mbar_expect_tx(&sh.q_full, Q_BYTES);
             for (int hb = 0; hb < HALVES; ++hb) tma_load_2d(q_s + hb * SUB_BYTES, &map_q, h * D + hb * 64, q_start + row0, &sh.q_full);
         }
-        // Keys are wanted two tiles before the values of the same tile: K_j goes before V_{j-1}.  The pages of a
-        // tile are looked up one tile ahead, so that the table's latency is not in the way of the copies.
-        int pages_next = lookup(0), pages_prev = -1;
+        // Keys are wanted two tiles before the values of the same tile: K_j goes before V_{j-1}.
+        int batch_cur = lookup_batch(0), batch_next = tiles_per_batch < n ? lookup_batch(1) : -1;
+        int pages_cur = -1, pages_prev = -1;
         for (int j = 0; j <= n && ok; ++j) {
-            const int pages_cur = pages_next;
-            if (j + 1 < n) pages_next = lookup(j + 1);
-            if (j < n) load_tile(j, pages_cur, &map_k, k_s, sh.k_full, sh.k_empty);
+            if (j < n) {
+                const int within = j % tiles_per_batch;
+                if (j > 0 && within == 0) {
+                    batch_cur = batch_next;
+                    batch_next = (j / tiles_per_batch + 1) * tiles_per_batch < n ? lookup_batch(j / tiles_per_batch + 1) : -1;
+                }
+                const int got = __shfl_sync(0xffffffffu, batch_cur, within * pages_per_tile + lane % pages_per_tile);
+                pages_cur = lane < pages_per_tile ? got : -1;
+                load_tile(j, pages_cur, &map_k, k_s, sh.k_full, sh.k_empty);
+            }
             if (ok && j >= 1) load_tile(j - 1, pages_prev, &map_v, v_s, sh.v_full, sh.v_empty);
             pages_prev = pages_cur;
         }
@@ -225,7 +237,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
         constexpr uint32_t idesc_o = instr_desc(BQ, D) | (1u << 16);            // B (values) is MN-major
         if (lane == 0) {
 #ifdef KVB_TRACE
-            long long m_wp = 0, m_wv = 0, m_wk = 0, m_t, m_start = clock64();
+            long long m_wp = 0, m_wv = 0, m_wk = 0, m_pv = 0, m_t, m_start = clock64();
 #define MCLK(acc) { const long long now_ = clock64(); acc += now_ - m_t; m_t = now_; }
 #define MCLK0() m_t = clock64();
 #else
@@ -254,20 +266,20 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
             for (int i = 0; i < n && ok; ++i) {
                 const int s = i % STAGES;
                 MCLK0()
-                ok = mbar_wait(&sh.p_ready[i & 1], (i >> 1) & 1);  // P_i is in shared memory; S_{i % 2} and O_{i % 2} are free
+                ok = mbar_wait(&sh.p_ready[i & 1], (i >> 1) & 1);  // P_i is in tensor memory, over S_{i % 2}; O_{i % 2} is free
                 MCLK(m_wp)
                 ok = ok && mbar_wait(&sh.v_full[s], (i / STAGES) & 1);
                 MCLK(m_wv)
                 if (!ok) break;
                 asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
                 const uint32_t v_addr = smem_u32(v_s + (size_t)s * KV_BYTES);
-                const uint32_t p_addr = smem_u32(p_s + (i & 1) * P_BYTES);
 #pragma unroll
-                for (int k = 0; k < BKEYS / 16; ++k)               // 16 keys a step: 32 bytes along P's rows, 2048 bytes down V
-                    umma(tmem_o + (i & 1) * D, smem_desc(p_addr) + 2 * k, smem_desc_mn(v_addr + k * 2048, KV_SUB_BYTES), idesc_o,
-                         k != 0 ? 1u : 0u);
+                for (int k = 0; k < BKEYS / 16; ++k)               // 16 keys a step: 8 columns of P in tensor memory, 2048 bytes down V
+                    umma_a_tmem(tmem_o + (i & 1) * D, tmem_s + (i & 1) * BKEYS + 8 * k, smem_desc_mn(v_addr + k * 2048, KV_SUB_BYTES),
+                                idesc_o, k != 0 ? 1u : 0u);
                 umma_commit(&sh.v_empty[s]);
                 umma_commit(&sh.o_full[i & 1]);
+                MCLK(m_pv)
                 if (i + 2 < n) ok = mma_scores(i + 2);
             }
             if (!ok) { atomicOr(p.err, KVB_DEV_TIMEOUT); sh.failed = 1; }
@@ -276,7 +288,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
                 const int cta = blockIdx.y * gridDim.x + blockIdx.x;
                 if (cta < 4096) {
                     long long* t = kvb_trace_buf + (4096 + cta) * 8;
-                    t[0] = m_wp; t[1] = m_wv; t[2] = m_wk; t[3] = clock64() - m_start;
+                    t[0] = m_wp; t[1] = m_wv; t[2] = m_wk; t[3] = clock64() - m_start; t[7] = m_pv;
                 }
             }
 #endif
@@ -363,24 +375,25 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
             const float corr = ex2(m - base_m);
             m = m_new;
             l *= corr;
-            // P = 2^(s * scale - m) as bfloat16 into shared memory, row `row`, 16-byte chunk c of the row at chunk
-            // position c ^ (row % 8).  A masked score is -inf and gives 0.
-            unsigned char* dst = p_s + (i & 1) * P_BYTES + row * 128;
+            // P = 2^(s * scale - m) as bfloat16 into tensor memory, over the first half of the columns that held this
+            // tile's S (every score of the row is in registers by now): keys 2c and 2c + 1 of the row in column c, where
+            // the product P V reads its A operand.  Shared memory carries neither P's stores nor the product's reads
+            // of it.  A masked score is -inf and gives 0.
 #pragma unroll
-            for (int c = 0; c < BKEYS / 8; ++c) {
-                uint32_t packed[4];
+            for (int half = 0; half < 2; ++half) {
+                uint32_t packed[16];
 #pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    const float p0 = ex2(fmaf(__uint_as_float(sv[8 * c + 2 * e]), p.scale_log2, -base_m));
-                    const float p1 = ex2(fmaf(__uint_as_float(sv[8 * c + 2 * e + 1]), p.scale_log2, -base_m));
+                for (int c = 0; c < 16; ++c) {
+                    const float p0 = ex2(fmaf(__uint_as_float(sv[32 * half + 2 * c]), p.scale_log2, -base_m));
+                    const float p1 = ex2(fmaf(__uint_as_float(sv[32 * half + 2 * c + 1]), p.scale_log2, -base_m));
                     l += p0 + p1;
                     __nv_bfloat162 v = __floats2bfloat162_rn(p0, p1);
-                    packed[e] = *reinterpret_cast<uint32_t*>(&v);
+                    packed[c] = *reinterpret_cast<uint32_t*>(&v);
                 }
-                *reinterpret_cast<uint4*>(dst + ((c ^ (row & 7)) << 4)) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+                tmem_st16(tmem_s + (i & 1) * BKEYS + lane_base + 16 * half, packed);
             }
+            tmem_st_wait();
             asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
-            asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");    // P was written by ordinary stores; the MMA reads it
             mbar_arrive(&sh.p_ready[i & 1]);
             TCLK(c_soft)
             // While the tensor core multiplies P_i V_i, add the O_t of the tile before.

@@ -173,6 +173,81 @@ __global__ void add_rmsnorm_vec_kernel(float* __restrict__ h, const T* __restric
     }
 }
 
+// One warp per row, for launches of many rows (prompt portions): a lane keeps its C chunks of four in registers, no
+// barrier of the block is needed, and all rows of 2,048 are resident at once.  The additions are those of the kernel
+// above in the same order - lane l's chunk c is thread l + 32 c's chunk there, each group of 32 is summed by the same
+// shuffles, and the groups are added one after the other - so a row's result is bit for bit the same whichever of
+// the two kernels a step's row count selects.  Needs H <= 128 C.
+template <typename T, int C>
+__global__ void add_rmsnorm_warp_kernel(float* __restrict__ h, const T* __restrict__ delta, const float* __restrict__ w,
+                                        T* __restrict__ out, const int* __restrict__ rows, int n_out, int H, float eps) {
+    const int lane = threadIdx.x & 31;
+    const int o = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    float4 ww[C];
+#pragma unroll
+    for (int c = 0; c < C; ++c) {
+        const int i = (lane + 32 * c) * 4;
+        ww[c] = i < H ? *reinterpret_cast<const float4*>(w + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    pdl_wait();
+    pdl_launch_dependents();
+    if (o >= n_out) return;
+    const int r = rows ? rows[o] : o;
+    float* hr = h + (size_t)r * H;
+    const T* dr = delta ? delta + (size_t)r * H : nullptr;
+    float4 kept[C];
+#pragma unroll
+    for (int c = 0; c < C; ++c) {
+        const int i = (lane + 32 * c) * 4;
+        kept[c] = i < H ? *reinterpret_cast<const float4*>(hr + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    if (dr) {
+#pragma unroll
+        for (int c = 0; c < C; ++c) {
+            const int i = (lane + 32 * c) * 4;
+            if (i < H) {
+                const float4 d = Vec4<T>::load(dr + i);
+                kept[c].x += d.x; kept[c].y += d.y; kept[c].z += d.z; kept[c].w += d.w;
+                if (!rows) *reinterpret_cast<float4*>(hr + i) = kept[c];
+            }
+        }
+    }
+    const int groups = (H / 4 + 31) >> 5;                   // the warps that the kernel above would run
+    float total = 0.f;
+#pragma unroll
+    for (int c = 0; c < C; ++c) {
+        float ss = 0.f;
+        ss += kept[c].x * kept[c].x; ss += kept[c].y * kept[c].y; ss += kept[c].z * kept[c].z; ss += kept[c].w * kept[c].w;
+        ss = warp_sum(ss);
+        if (c < groups) total += ss;
+    }
+    const float inv = 1.f / sqrtf(total / (float)H + eps);
+    T* orow = out + (size_t)o * H;
+#pragma unroll
+    for (int c = 0; c < C; ++c) {
+        const int i = (lane + 32 * c) * 4;
+        if (i < H) {
+            const float4 v = kept[c], g = ww[c];
+            Vec4<T>::store(orow + i, make_float4(v.x * inv * g.x, v.y * inv * g.y, v.z * inv * g.z, v.w * inv * g.w));
+        }
+    }
+}
+
+template <typename T>
+static bool launch_rmsnorm_warp(float* h, const T* delta, const float* w, T* out, const int* rows, int n_out, int H, float eps,
+                                cudaStream_t stream) {
+    constexpr int WARPS = 2;
+    const dim3 grid((n_out + WARPS - 1) / WARPS), block(32 * WARPS);
+    if (H <= 512) kvb_launch(add_rmsnorm_warp_kernel<T, 4>, grid, block, 0, stream, h, delta, w, out, rows, n_out, H, eps);
+    else if (H <= 1024) kvb_launch(add_rmsnorm_warp_kernel<T, 8>, grid, block, 0, stream, h, delta, w, out, rows, n_out, H, eps);
+    else if (H <= 1536) kvb_launch(add_rmsnorm_warp_kernel<T, 12>, grid, block, 0, stream, h, delta, w, out, rows, n_out, H, eps);
+    else if (H <= 2048) kvb_launch(add_rmsnorm_warp_kernel<T, 16>, grid, block, 0, stream, h, delta, w, out, rows, n_out, H, eps);
+    else return false;
+    return true;
+}
+
+constexpr int RMSNORM_WARP_MIN_ROWS = 256;                  // below this a block per row has more loads in flight
+
 KVB_API int kvb_add_rmsnorm(int dtype, float* h, const void* delta, const float* w, void* out, const int* rows,
                             int n_out, int H, float eps, cudaStream_t stream) {
     if (n_out <= 0) return KVB_OK;
@@ -180,6 +255,12 @@ KVB_API int kvb_add_rmsnorm(int dtype, float* h, const void* delta, const float*
     const bool vec = H % 4 == 0 && ((((uintptr_t)h | (uintptr_t)w | (uintptr_t)out | (uintptr_t)delta) & 15) == 0);
     // One chunk of four per thread where the row allows it.
     const int vec_threads = H / 4 >= 1024 ? 1024 : (H / 4 + 31) / 32 * 32;
+    if (vec && n_out >= RMSNORM_WARP_MIN_ROWS) {
+        if (dtype == KVB_F32 && launch_rmsnorm_warp<float>(h, (const float*)delta, w, (float*)out, rows, n_out, H, eps, stream))
+            return kvb_launch_status();
+        if (dtype == KVB_BF16 && launch_rmsnorm_warp<bf16>(h, (const bf16*)delta, w, (bf16*)out, rows, n_out, H, eps, stream))
+            return kvb_launch_status();
+    }
     if (vec && dtype == KVB_F32) {
         kvb_launch(add_rmsnorm_vec_kernel<float>, dim3(n_out), dim3(vec_threads), 0, stream, h, (const float*)delta, w, (float*)out, rows, H, eps);
         return kvb_launch_status();

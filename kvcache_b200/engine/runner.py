@@ -73,15 +73,33 @@ class StepLayout:
             self.table_offsets.append(offset)
             offset += _align4(S * table_width)
         self.total = offset
+        self._remembered_for = None
+        self._remembered = {}
+
+    def remember(self, buf) -> None:
+        """Views of `buf` (the runner's one device buffer) are made once and handed out again: a step asks for two dozen."""
+        self._remembered_for = buf
+        self._remembered = {}
 
     def view(self, buf, name: str):
+        if buf is self._remembered_for:
+            found = self._remembered.get(name)
+            if found is None:
+                begin, count = self.offsets[name]
+                found = self._remembered[name] = buf[begin:begin + count]
+            return found
         begin, count = self.offsets[name]
         return buf[begin:begin + count]
 
     def table(self, buf, group: int):
+        if buf is self._remembered_for and ("table", group) in self._remembered:
+            return self._remembered[("table", group)]
         begin = self.table_offsets[group]
         flat = buf[begin:begin + self.S * self.table_width]
-        return flat.view(self.S, self.table_width) if isinstance(flat, torch.Tensor) else flat.reshape(self.S, self.table_width)
+        shaped = flat.view(self.S, self.table_width) if isinstance(flat, torch.Tensor) else flat.reshape(self.S, self.table_width)
+        if buf is self._remembered_for:
+            self._remembered[("table", group)] = shaped
+        return shaped
 
 
 class _DecodeGraph:
@@ -112,6 +130,7 @@ class ModelRunner:
         self._staging_events = [None] * ring
         self._ring = 0
         self._graphs: Dict[int, _DecodeGraph] = {}
+        self._layouts: Dict[Tuple[int, int, int], StepLayout] = {}
         self._portion_shapes_seen: Dict[tuple, int] = {}
         self._sample_parts = None       # asked of the sampling module when a step first samples
         # Tokens the last sampling step chose, in the order of its wanted places.  The next step may take its
@@ -150,7 +169,13 @@ class ModelRunner:
         self.cache.extend([(e.slot, n) for e, n in zip(entries, counts)])   # raises OutOfPages before any change
 
         R = sum(len(e.want) for e in entries)
-        layout = StepLayout(T, S, R, self.cache.max_pages_per_request, len(self.cache.groups), self.planners)
+        layout = self._layouts.get((T, S, R))
+        if layout is None:
+            if len(self._layouts) > 4096:
+                self._layouts.clear()
+            layout = self._layouts[(T, S, R)] = StepLayout(T, S, R, self.cache.max_pages_per_request, len(self.cache.groups),
+                                                           self.planners)
+            layout.remember(self._meta_device)
         index, staging = self._next_staging()
         host = staging.numpy()
         counts_np = np.asarray(counts, dtype=np.int32)
@@ -162,6 +187,13 @@ class ModelRunner:
             layout.view(host, "token_src")[:] = [e.token_from_last for e in entries]
             row_segment = np.arange(S, dtype=np.int32)
             layout.view(host, "positions")[:] = starts_np
+        elif S == 1:                                 # one portion of one prompt
+            if entries[0].token_from_last >= 0:
+                raise ValueError("token_from_last applies to an entry of one token")
+            np.maximum(np.asarray(entries[0].tokens, dtype=np.int32), 0, out=layout.view(host, "token_ids"))
+            layout.view(host, "token_src")[:] = -1
+            row_segment = 0
+            layout.view(host, "positions")[:] = np.arange(starts[0], starts[0] + T, dtype=np.int32)
         else:
             layout.view(host, "token_ids")[:] = np.maximum(np.concatenate([np.asarray(e.tokens, dtype=np.int32) for e in entries]), 0)
             src = layout.view(host, "token_src")

@@ -34,6 +34,8 @@ from collections import deque
 from dataclasses import dataclass, field
 from typing import Deque, Dict, List, Optional, Sequence, Tuple
 
+import numpy as np
+
 from ..cache.manager import CacheManager
 from ..sampling.params import SamplingParams
 
@@ -68,10 +70,22 @@ class Request:
     finishing: bool = False        # its last token is on its way: it takes no part in further steps
     arrival: float = 0.0           # seconds on the scheduler's clock when it was submitted
     finished_at: Optional[float] = None
+    prompt_ids: Optional[np.ndarray] = None   # the prompt as int32, made once: a portion of it is a view, not a copy
 
     @property
     def tokens(self) -> List[int]:
         return self.prompt + self.output
+
+    def span(self, start: int, count: int):
+        """Tokens start..start+count-1 of prompt + output, without joining the two."""
+        n, end = len(self.prompt), start + count
+        if end <= n:
+            if self.prompt_ids is None:
+                self.prompt_ids = np.asarray(self.prompt, dtype=np.int32)
+            return self.prompt_ids[start:end]
+        if start >= n:
+            return self.output[start - n:end - n]
+        return self.prompt[start:] + self.output[:end - n]
 
     @property
     def num_tokens(self) -> int:
@@ -92,8 +106,8 @@ class Piece:
     token_from_last: int = -1      # >= 0: its (single) token is the previous step's sampled token at this index
 
     @property
-    def tokens(self) -> List[int]:
-        return self.request.tokens[self.start:self.start + self.count]
+    def tokens(self) -> Sequence[int]:
+        return self.request.span(self.start, self.count)
 
 
 @dataclass

@@ -14,6 +14,7 @@ The reference has one block per (query row, head) and no such lists (src/qwen_ke
 """
 from __future__ import annotations
 
+import functools
 from typing import Dict, Tuple
 
 import numpy as np
@@ -29,6 +30,13 @@ TC_MIN_KEY_TILES = 16           # a unit of that kernel has at least this many k
 
 
 def plan_prefill_units(segments, tile_rows: int = PREFILL_TILE_ROWS, min_key_tiles: int = 4):
+    """`_plan_prefill_units`, remembered: a prompt cut into portions of one size, and prompts of one length, bring the
+    same segments step after step.  The array that comes back is shared and not to be written."""
+    return _plan_prefill_units(tuple(segments), tile_rows, min_key_tiles)
+
+
+@functools.lru_cache(maxsize=1024)
+def _plan_prefill_units(segments, tile_rows: int, min_key_tiles: int):
     """The work list of prefill attention.  `segments`: (segment index, tokens cached before the step, tokens
     it brings) for every segment of more than one token.  A tile is `tile_rows` consecutive rows of a segment;
     a tile whose rows see many keys is cut into units of about equal numbers of key tiles, so that the blocks
@@ -50,7 +58,9 @@ def plan_prefill_units(segments, tile_rows: int = PREFILL_TILE_ROWS, min_key_til
         first = len(units)
         for split in range(nsplit):
             units.append((seg, row0, split, nsplit, tile_id, first, 0, 0))
-    return np.asarray(units, dtype=np.int32).reshape(-1, 8), len(tiles)
+    array = np.asarray(units, dtype=np.int32).reshape(-1, 8)
+    array.setflags(write=False)
+    return array, len(tiles)
 
 
 class PagedAttentionPlanner(StepPlanner):

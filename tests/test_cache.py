@@ -28,6 +28,38 @@ def test_allocator_order_and_reuse():
     assert pages_for(17, 16) == 2 and pages_for(16, 16) == 1 and pages_for(0, 16) == 0
 
 
+def test_many_pages_at_once_are_the_single_calls_in_turn():
+    rng = random.Random(5)
+    one, many = PageAllocator(40), PageAllocator(40)
+    held = []
+    for _ in range(200):
+        if held and rng.random() < 0.45:
+            k = rng.randint(1, min(6, len(held)))
+            group = [held.pop(rng.randrange(len(held))) for _ in range(k)]
+            for page in group:
+                one.free(page)
+            many.free_many(group)
+        else:
+            k = rng.randint(0, 7)
+            if k > one.num_free:
+                with pytest.raises(OutOfPages):
+                    many.alloc_many(k)
+                assert many.num_free == one.num_free
+                continue
+            singles = [one.alloc() for _ in range(k)]
+            assert many.alloc_many(k) == singles
+            held += singles
+        assert one._free == many._free and (one._held == many._held).all()
+    a = PageAllocator(6)
+    pages = a.alloc_many(4)
+    for bad in ([1, 1], [2, 5], [0, 6], [-1]):
+        with pytest.raises(ValueError):
+            a.free_many(bad)
+        assert a.num_free == 2 and all(a.is_held(p) for p in pages)     # a refused call frees nothing
+    a.free_many(np.asarray([3, 1], dtype=np.int32))
+    assert a.alloc_many(2) == [1, 3]
+
+
 def _manager(num_pages=8, page=4, slots=4, window=None, max_tokens=64, two_groups=False):
     entries = [CacheEntry(PagedKVSpec(2, 8, None), None), CacheEntry(PagedKVSpec(2, 8, None), None)]
     if window:

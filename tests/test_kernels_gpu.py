@@ -45,7 +45,8 @@ def test_embed_flags_bad_token(kernels):
 
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("T,H,eps", [(1, 64, 1e-6), (5, 896, 1e-6), (19, 120, 1e-5), (3, 3584, 1e-6), (4, 50, 1e-3),
-                                     (300, 896, 1e-6), (257, 5000, 1e-5), (261, 120, 1e-6)])   # many rows, rows longer than the registers keep
+                                     (300, 896, 1e-6), (257, 5000, 1e-5), (261, 120, 1e-6),    # many rows, rows longer than the registers keep
+                                     (259, 1536, 1e-6), (256, 2048, 1e-5), (300, 1028, 1e-6), (258, 516, 1e-6)])
 def test_add_rmsnorm(kernels, dtype, T, H, eps):
     g = torch.Generator().manual_seed(1)
     h = torch.randn(T, H, generator=g) * 3
@@ -73,6 +74,32 @@ def test_add_rmsnorm(kernels, dtype, T, H, eps):
         kernels.add_rmsnorm(h_dev, delta.to(DEV), w.to(DEV), eps, out, rows.to(DEV))
         assert torch.equal(h_dev.cpu(), h)
         assert_close(out, out_ref, REL[dtype], "many gathered rows")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("H", [896, 120, 1536, 2048, 516])
+def test_add_rmsnorm_does_not_depend_on_the_row_count(kernels, dtype, H):
+    """Launches of many rows take a kernel with a warp per row, launches of few rows one with a block per row; a row's
+    numbers are the same bit for bit, so a prompt gives the same logits whole and in portions."""
+    T = 300
+    g = torch.Generator().manual_seed(4)
+    h = (torch.randn(T, H, generator=g) * 3).to(DEV)
+    delta = torch.randn(T, H, generator=g).to(dtype).to(DEV)
+    w = (1 + 0.1 * torch.randn(H, generator=g)).to(DEV)
+    h_all, out_all = h.clone(), torch.empty(T, H, dtype=dtype, device=DEV)
+    kernels.add_rmsnorm(h_all, delta, w, 1e-6, out_all)
+    h_few, out_few = h.clone(), torch.empty(T, H, dtype=dtype, device=DEV)
+    for a in range(0, T, 100):
+        kernels.add_rmsnorm(h_few[a:a + 100], delta[a:a + 100], w, 1e-6, out_few[a:a + 100])
+    assert torch.equal(h_all, h_few)
+    assert torch.equal(out_all, out_few)
+    rows = torch.arange(T - 1, -1, -1, dtype=torch.int32, device=DEV)
+    gathered, few = torch.empty(T, H, dtype=dtype, device=DEV), torch.empty(T, H, dtype=dtype, device=DEV)
+    kernels.add_rmsnorm(h.clone(), delta, w, 1e-6, gathered, rows)
+    for a in range(0, T, 100):
+        kernels.add_rmsnorm(h.clone(), delta, w, 1e-6, few[a:a + 100], rows[a:a + 100])
+    assert torch.equal(gathered, few)
+    assert torch.equal(gathered.flip(0), out_all)
 
 
 @pytest.mark.parametrize("dtype", DTYPES)

@@ -1,5 +1,6 @@
 """The scheduler's decisions, on the host alone: a fake step that only moves the cache's
 bookkeeping and hands out tokens by rule."""
+import numpy as np
 import pytest
 
 from kvcache_b200.cache import CacheManager
@@ -285,3 +286,14 @@ def test_statistics_of_the_references_engine():
     assert a.finished_at == 2.0 and b.finished_at == 4.0
     assert st.avg_latency_us == pytest.approx(3.0e6) and st.p99_latency_us == pytest.approx(4.0e6) and st.wall_us == pytest.approx(4.0e6)
     assert st.slot_steps == 1 + 2 + 1 + 1 and st.useful_steps == 1 + 2 + 1 + 1 and st.slot_utilisation == 1.0
+
+
+def test_a_piece_hands_out_its_tokens_without_joining_prompt_and_output():
+    from kvcache_b200.engine.scheduler import Piece, Request
+    request = Request(0, [5, 6, 7, 8], SamplingParams(max_new_tokens=4), output=[9, 10, 11])
+    whole = request.tokens
+    for start in range(len(whole)):
+        for count in range(1, len(whole) - start + 1):
+            assert list(Piece(request, start, count, False).tokens) == whole[start:start + count]
+    inside = Piece(request, 1, 2, False).tokens
+    assert isinstance(inside, np.ndarray) and inside.dtype == np.int32 and inside.base is request.prompt_ids
