@@ -559,7 +559,8 @@ class CudaKernels(KernelSet):
                     tc = self._attn_tc[D] = _Library("attention_tc", f"d{D}", [f"-DKVB_HEAD_DIM={D}"])
                 units = counts["tc_units"]
                 scratch = workspace.buffer("attn.tc_scratch", (units * num_heads * 128 * (D + 2),), torch.float32)
-                tickets = workspace.zeros("attn.tc_tickets", (max(counts["tc_tiles"], 1) * num_heads,), torch.int32)
+                # Two counters of the kernel's work queue, then a ticket per (tile, head); the kernel leaves all of them zero.
+                tickets = workspace.zeros("attn.tc_tickets", (2 + max(counts["tc_tiles"], 1) * num_heads,), torch.int32)
                 self._count("attention_tc")
                 _check(tc.kvb_attention_tc(
                     _ptr(q), _ptr(out), _ptr(kv.k_pages), _ptr(kv.v_pages), kv.k_pages.shape[0], _ptr(kv.block_table),

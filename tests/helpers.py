@@ -52,7 +52,7 @@ def paged_scenario(segments, *, num_kv_heads: int, head_dim: int, page_size: int
     pos = np.concatenate([np.arange(s, s + n) for s, n in segments]).astype(np.int32)
     row_seg = np.concatenate([np.full(n, i) for i, (s, n) in enumerate(segments)]).astype(np.int32)
     q_start = np.cumsum([0] + [n for _, n in segments[:-1]]).astype(np.int32)
-    dev = lambda a: torch.as_tensor(a, dtype=torch.int32).to(device)
+    dev = lambda a: torch.tensor(np.array(a), dtype=torch.int32).to(device)
     from kvcache_b200.kernels.attention_plan import PagedAttentionPlanner, plan_prefill_units
     from kvcache_b200.parts.base import StepPlan
     arrays, counts = PagedAttentionPlanner().plan(np.asarray([s for s, _ in segments]), np.asarray([n for _, n in segments]))
