@@ -594,40 +594,32 @@ __global__ void __launch_bounds__(160) flash_decode_tma_kernel(const __grid_cons
             asm volatile("prefetch.tensormap [%0];\n" ::"l"(&map_k) : "memory");
             asm volatile("prefetch.tensormap [%0];\n" ::"l"(&map_v) : "memory");
         }
-        // Stage i holds keys [(my_begin + i KW) * 64, + NKEYS).  Lane pg takes page pg of it.
-        auto load_stage = [&](int i) {
+        // Stage i holds keys [(my_begin + i KW) * 64, + NKEYS).  Lane pg takes page pg of it: its number is looked up ahead
+        // of the copy (the ring's first round all at once, then one stage ahead), so that the table's latency is paid
+        // once and not stage by stage.  -1: beyond the last key, or given back behind a window.
+        auto lookup = [&](int i) -> int {
+            int page = -1;
+            if (lane < pages_per_stage && i < n) {
+                const int first_key = (my_begin + i * KW) * KT + lane * p.page_size;
+                if (first_key < kv_len && first_key + p.page_size > key_lo) page = table[first_key >> p.page_shift];
+            }
+            return page;
+        };
+        // Every lane asks the barrier (one lane asking and telling the others costs twice as much).  A page that is not
+        // there is copied from before the pool's first row: the TMA unit fills what lies outside the tensor with zeros
+        // (the slot must hold finite numbers, because 0 * NaN would poison the sums) and still counts the bytes.
+        auto load_stage = [&](int i, int my_page) {
             const int s = i % STAGES;
             unsigned char* dst = stages + (size_t)s * STAGE_BYTES;
-            const int key0 = (my_begin + i * KW) * KT;
-            int my_page = -1;
-            if (lane < pages_per_stage) {
-                const int first_key = key0 + lane * p.page_size;
-                if (first_key < kv_len && first_key + p.page_size > key_lo) my_page = table[first_key >> p.page_shift];
-            }
             if (i >= STAGES) {
-                if (lane == 0) ok = mbar_wait(&sh.empty[s], ((i - STAGES) / STAGES) & 1);
-                ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+                ok = mbar_wait(&sh.empty[s], ((i - STAGES) / STAGES) & 1);
+                ok = __all_sync(0xffffffffu, ok);
                 if (!ok) return;
             }
-            const unsigned held = __ballot_sync(0xffffffffu, my_page >= 0);
-            const int present = __popc(held);
-            if (present < pages_per_stage) {
-                // No page there (beyond the last key, or given back behind a window): the slot must still hold
-                // finite numbers, because 0 * NaN would poison the sums.
-                const int bytes = p.page_size * 128;
-                for (int pg = 0; pg < pages_per_stage; ++pg) {
-                    if ((held >> pg) & 1u) continue;
-                    for (int x = 0; x < 2 * HALVES; ++x)
-                        for (int off = lane * 16; off < bytes; off += 32 * 16)
-                            *reinterpret_cast<uint4*>(dst + x * HALF_BYTES + pg * bytes + off) = make_uint4(0, 0, 0, 0);
-                }
-                asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
-                __syncwarp();
-            }
-            if (lane == 0) mbar_expect_tx(&sh.full[s], (uint32_t)present * 2 * HALVES * p.page_size * 128);
+            if (lane == 0) mbar_expect_tx(&sh.full[s], (uint32_t)pages_per_stage * 2 * HALVES * p.page_size * 128);
             __syncwarp();
-            if (my_page >= 0) {
-                const int row = (my_page * p.Hkv + hk) * p.page_size;   // row of the pool seen as [pages * heads * page, D]
+            if (lane < pages_per_stage) {
+                const int row = my_page >= 0 ? (my_page * p.Hkv + hk) * p.page_size : -p.page_size;   // of the pool as [pages * heads * page, D]
 #pragma unroll
                 for (int hb = 0; hb < HALVES; ++hb) {
                     tma_load_2d(dst + hb * HALF_BYTES + lane * p.page_size * 128, &map_k, hb * 64, row, &sh.full[s]);
@@ -639,14 +631,24 @@ __global__ void __launch_bounds__(160) flash_decode_tma_kernel(const __grid_cons
         // round are fetched before the wait.  Fused, all of them are old: nobody but this kernel writes the pool
         // meanwhile, and the new position's slot is made afresh in shared memory.
         const int first = min(n, STAGES);
+        int first_pages[STAGES];
+#pragma unroll
+        for (int i = 0; i < STAGES; ++i) first_pages[i] = lookup(i);
+        int page_next = lookup(STAGES);
         unsigned early = 0;
-        for (int i = 0; i < first && ok; ++i)
-            if (FUSED || (my_begin + (i + 1) * KW) * KT <= first_pos) { load_stage(i); early |= 1u << i; }
+#pragma unroll
+        for (int i = 0; i < STAGES; ++i)
+            if (i < first && (FUSED || (my_begin + (i + 1) * KW) * KT <= first_pos)) { load_stage(i, first_pages[i]); early |= 1u << i; }
         pdl_wait();
         pdl_launch_dependents();
-        for (int i = 0; i < first && ok; ++i)
-            if (!((early >> i) & 1u)) load_stage(i);
-        for (int i = first; i < n && ok; ++i) load_stage(i);
+#pragma unroll
+        for (int i = 0; i < STAGES; ++i)
+            if (i < first && !((early >> i) & 1u)) load_stage(i, first_pages[i]);
+        for (int i = first; i < n && ok; ++i) {
+            const int page = page_next;
+            page_next = lookup(i + 1);
+            load_stage(i, page);
+        }
         if (!ok && lane == 0) { atomicOr(err, KVB_DEV_TIMEOUT); sh.failed = 1; }
     } else {
         // ---- scanning warps ----
