@@ -139,6 +139,10 @@ _SIGNATURES = {
                              _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float,
                              _c_void_p, _c_void_p],
     },
+    "primitive_costs": {
+        "kvb_primitive_costs_count": [],
+        "kvb_primitive_costs": [_c_void_p, _c_void_p, _c_void_p, _c_void_p],
+    },
     "wait_probe": {
         "kvb_wait_probe": [_c_void_p, _c_void_p, _c_void_p],
     },
@@ -292,6 +296,24 @@ class CudaKernels(KernelSet):
         if gave_up != 2:
             raise KernelError("the wait of the probe kernel ended although nothing arrived on its barrier")
         return polls
+
+    PRIMITIVE_NAMES = ("wait on a completed mbarrier, all lanes", "the same, one lane asks and the warp meets again", "shuffle",
+                       "vote and population count", "expect_tx by one lane and the warp meets again",
+                       "tcgen05.mma 128 x 64 x 16, operands in shared memory", "tcgen05.mma 128 x 128 x 16, operands in shared memory",
+                       "tcgen05.mma 128 x 64 x 16, A in tensor memory", "tcgen05.commit", "TMA copy of one page (16 rows of 128 bytes)",
+                       "tcgen05.ld of 32 columns and its wait")
+
+    def primitive_costs(self) -> Dict[str, float]:
+        """Clocks per primitive of the warp-specialised kernels on an otherwise idle SM (csrc/primitive_costs.cu)."""
+        lib = _Library("primitive_costs")
+        count = lib.kvb_primitive_costs_count()
+        zeros = torch.zeros(4 << 20, dtype=torch.uint8, device=self.device)
+        out = torch.zeros(count + 1, dtype=torch.float32, device=self.device)
+        for _ in range(2):          # the second run finds the code and the tensor map cached
+            self._count("primitive_costs")
+            _check(lib.kvb_primitive_costs(_ptr(zeros), _ptr(out), _ptr(self.error_word), self._stream()), "primitive_costs")
+        self.check_errors()
+        return dict(zip(self.PRIMITIVE_NAMES, out[:count].tolist()))
 
     def paged_attention_planner(self) -> PagedAttentionPlanner:
         """The work lists `paged_attention` and `rope_append_attention` read from `StepBatch.plans` (one planner for all layers)."""

@@ -37,6 +37,8 @@ MODULES: Dict[str, dict] = {
     "attention_flash": {"src": "attention_flash.cu", "deps": ["common.cuh", "flash_core.cuh", "no_alloc.h", "tc_common.cuh"]},
     "attention_tc": {"src": "attention_tc.cu", "deps": ["common.cuh", "tc_common.cuh"]},
     "gemm_wstream": {"src": "gemm_wstream.cu", "deps": ["common.cuh", "tc_common.cuh"]},
+    # What barrier waits, votes, MMA issue and page copies cost on this GPU (python -m kvcache_b200.kernels.primitive_costs).
+    "primitive_costs": {"src": "primitive_costs.cu", "deps": ["common.cuh", "tc_common.cuh"]},
     # One wait that cannot end, with a short poll limit: shows that a stalled wait reaches the host as an error bit.
     "wait_probe": {"src": "wait_probe.cu", "deps": ["common.cuh", "tc_common.cuh"], "flags": ["-DKVB_SPIN_LIMIT=4096"]},
 }

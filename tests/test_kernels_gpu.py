@@ -742,3 +742,13 @@ def test_norm_bias_rotation_and_append_folded_into_the_qkv_product(kernels, scen
                                  batch_to(batch, DEV), kv_dev, q_out, Hq)
     assert torch.equal(kv_dev.k_pages, before)
     kernels.check_errors()
+
+
+def test_primitive_costs_probe(kernels):
+    """The probe that the helper warps' layout rests on (csrc/primitive_costs.cu) runs to its end, flags nothing, and
+    reports a cost for each primitive."""
+    costs = kernels.primitive_costs()
+    assert len(costs) == len(kernels.PRIMITIVE_NAMES)
+    for name, clocks in costs.items():
+        assert 1.0 < clocks < 20000.0, (name, clocks)
+    kernels.check_errors()
