@@ -11,7 +11,7 @@
 namespace {
 using namespace tc;
 
-enum { WAIT_ALL, WAIT_ONE, SHUFFLE, VOTE, EXPECT_TX, MMA_SS_N64, MMA_SS_N128, MMA_TS_N64, COMMIT, TMA_PAGE, TMEM_LOAD, COUNT };
+enum { WAIT_ALL, WAIT_ONE, SHUFFLE, VOTE, EXPECT_TX, MMA_SS_N64, MMA_SS_N128, MMA_TS_N64, COMMIT, TMA_PAGE, TMEM_LOAD, MMA_SYNC, MMA_SYNC_CHAIN, COUNT };
 
 __global__ void __launch_bounds__(64) primitive_costs_kernel(const __grid_constant__ CUtensorMap map, float* __restrict__ out,
                                                              int* __restrict__ err) {
@@ -80,13 +80,31 @@ __global__ void __launch_bounds__(64) primitive_costs_kernel(const __grid_consta
         uint32_t r[32];
         float acc = 0.f;
         for (int i = 0; i < N; ++i) { tmem_ld32(tmem + ((i & 3) * 32), r); acc += __uint_as_float(r[i & 31]); }
+        // The warp-level mma.sync of the decode attention (m16n8k16, bfloat16): eight accumulators in turn, then one chain.
+        t[MMA_SYNC] = clock64();
+        float c[8][4];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) c[j][0] = c[j][1] = c[j][2] = c[j][3] = 0.f;
+        const uint32_t a0 = (uint32_t)v, b0 = b;
+        for (int i = 0; i < N / 8; ++i) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+                asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+                             : "+f"(c[j][0]), "+f"(c[j][1]), "+f"(c[j][2]), "+f"(c[j][3]) : "r"(a0), "r"(a0), "r"(a0), "r"(a0), "r"(b0), "r"(b0));
+        }
+        t[MMA_SYNC_CHAIN] = clock64();
+        for (int i = 0; i < N; ++i)
+            asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+                         : "+f"(c[0][0]), "+f"(c[0][1]), "+f"(c[0][2]), "+f"(c[0][3]) : "r"(a0), "r"(a0), "r"(a0), "r"(a0), "r"(b0), "r"(b0));
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc += c[j][0] + c[j][3];
         t[COUNT] = clock64();
         // Everything asynchronous has ended before the block leaves: the MMAs (one more commit, waited for) and the copies.
         if (lane == 0) umma_commit(&finished);
         ok &= mbar_wait(&finished, 0);
         for (int i = 0; i < 4; ++i) ok &= mbar_wait(&landed[i], 0);
         if (lane == 0) {
-            const float per[COUNT] = {N, N, N, N, N, N, N, N, N, 16, N};
+            const float per[COUNT] = {N, N, N, N, N, N, N, N, N, 16, N, N, N};
             for (int k = 0; k < COUNT; ++k) out[k] = (float)(t[k + 1] - t[k]) / per[k];
             out[COUNT] = acc + (float)(v + (int)b) * 0.f;
             if (!ok) atomicOr(err, KVB_DEV_TIMEOUT);

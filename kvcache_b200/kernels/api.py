@@ -301,7 +301,8 @@ class CudaKernels(KernelSet):
                        "vote and population count", "expect_tx by one lane and the warp meets again",
                        "tcgen05.mma 128 x 64 x 16, operands in shared memory", "tcgen05.mma 128 x 128 x 16, operands in shared memory",
                        "tcgen05.mma 128 x 64 x 16, A in tensor memory", "tcgen05.commit", "TMA copy of one page (16 rows of 128 bytes)",
-                       "tcgen05.ld of 32 columns and its wait")
+                       "tcgen05.ld of 32 columns and its wait", "mma.sync m16n8k16 (bfloat16), eight accumulators in turn",
+                       "mma.sync m16n8k16, each needing the one before")
 
     def primitive_costs(self) -> Dict[str, float]:
         """Clocks per primitive of the warp-specialised kernels on an otherwise idle SM (csrc/primitive_costs.cu)."""
