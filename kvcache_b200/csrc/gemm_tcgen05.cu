@@ -27,6 +27,11 @@ namespace tc {
 constexpr int BM = 128, BK = 64;
 constexpr int A_BYTES = BM * BK * 2;
 constexpr int THREADS = 192;
+#ifndef KVB_PAIR_KSUB
+#define KVB_PAIR_KSUB 2
+#endif
+constexpr int PAIR_KSUB = KVB_PAIR_KSUB;                // sub-tiles of 64 along K in a stage of the two-SM kernel
+constexpr int PAIR_STAGES = 6 / PAIR_KSUB;
 // One thread's 32 consecutive accumulator columns (row m, columns n .. n + 31) on their way to memory: bias and
 // conversion, or the gated activation on interleaved gate/up columns.
 template <typename TOut, bool SWIGLU>
@@ -254,8 +259,12 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1)
 gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
                          const float* __restrict__ bias, TOut* __restrict__ y, int M, int N, int K, int* __restrict__ err) {
     constexpr int BN = 256, HALF_N = 128;
-    constexpr int B_BYTES = HALF_N * BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;     // per block
-    constexpr int STAGES = 6;
+    // A stage holds KSUB sub-tiles of 64 along K of each operand (the 128-byte swizzle takes no wider box): the thread that
+    // issues the MMAs pays for a barrier wait and a commit - about 250 clocks - once a stage, and with 64 of K a stage that
+    // was half as long again as the four MMAs themselves take (the tensor pipe was busy two thirds of the time).
+    constexpr int KSUB = PAIR_KSUB;
+    constexpr int B_BYTES = HALF_N * BK * 2, SUB_BYTES_ = A_BYTES + B_BYTES, STAGE_BYTES = KSUB * SUB_BYTES_;     // per block
+    constexpr int STAGES = PAIR_STAGES;
     extern __shared__ unsigned char smem_raw[];
     unsigned char* tiles = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     __shared__ Shared<STAGES> sh;
@@ -265,7 +274,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
     const int pair = blockIdx.x >> 1, num_pairs = gridDim.x >> 1;
     const int m_blocks = (M + 2 * BM - 1) / (2 * BM), n_blocks = (N + BN - 1) / BN;
     const int num_tiles = m_blocks * n_blocks;
-    const int kblocks = (K + BK - 1) / BK;
+    const int kblocks = (K + KSUB * BK - 1) / (KSUB * BK);      // stages along K; what lies beyond K is read as zeros
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) { mbar_init(&sh.full[s], 1); mbar_init(&sh.empty[s], 1); }
@@ -297,8 +306,11 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
                     const uint32_t round = it / STAGES;
                     if (round > 0 && !mbar_wait(&sh.empty[s], (round - 1) & 1)) { atomicOr(err, KVB_DEV_TIMEOUT); sh.failed = 1; ok = false; break; }
                     if (leader) mbar_expect_tx(&sh.full[s], 2 * STAGE_BYTES);      // the bytes of both blocks
-                    tma_load_2d_pair(tiles + s * STAGE_BYTES, &map_x, kb * BK, m0, &sh.full[s]);
-                    tma_load_2d_pair(tiles + s * STAGE_BYTES + A_BYTES, &map_w, kb * BK, n0, &sh.full[s]);
+#pragma unroll
+                    for (int sub = 0; sub < KSUB; ++sub) {
+                        tma_load_2d_pair(tiles + s * STAGE_BYTES + sub * SUB_BYTES_, &map_x, (kb * KSUB + sub) * BK, m0, &sh.full[s]);
+                        tma_load_2d_pair(tiles + s * STAGE_BYTES + sub * SUB_BYTES_ + A_BYTES, &map_w, (kb * KSUB + sub) * BK, n0, &sh.full[s]);
+                    }
                 }
             }
         }
@@ -317,11 +329,14 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
                     const int s = it % STAGES;
                     if (!mbar_wait(&sh.full[s], (it / STAGES) & 1)) { atomicOr(err, KVB_DEV_TIMEOUT); sh.failed = 1; ok = false; break; }
                     asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-                    const uint32_t a_addr = smem_u32(tiles + s * STAGE_BYTES), b_addr = a_addr + A_BYTES;
-                    const uint64_t adesc = smem_desc(a_addr), bdesc = smem_desc(b_addr);
 #pragma unroll
-                    for (int k = 0; k < BK / 16; ++k)
-                        umma_pair(acc, adesc + 2 * k, bdesc + 2 * k, idesc, (kb | k) != 0 ? 1u : 0u);
+                    for (int sub = 0; sub < KSUB; ++sub) {
+                        const uint32_t a_addr = smem_u32(tiles + s * STAGE_BYTES + sub * SUB_BYTES_), b_addr = a_addr + A_BYTES;
+                        const uint64_t adesc = smem_desc(a_addr), bdesc = smem_desc(b_addr);
+#pragma unroll
+                        for (int k = 0; k < BK / 16; ++k)
+                            umma_pair(acc, adesc + 2 * k, bdesc + 2 * k, idesc, (kb | sub | k) != 0 ? 1u : 0u);
+                    }
                     umma_commit_pair(&sh.empty[s]);
                 }
                 umma_commit_pair(&sh.accum_full[b]);
@@ -429,7 +444,7 @@ static int launch_pair(const void* x, const void* w, const float* bias, TOut* y,
     if (rc != KVB_OK) return rc;
     rc = make_map(&mw, w, N, K, 128);
     if (rc != KVB_OK) return rc;
-    const size_t smem = (size_t)6 * (A_BYTES + 128 * BK * 2) + 1024;
+    const size_t smem = (size_t)PAIR_STAGES * PAIR_KSUB * (A_BYTES + 128 * BK * 2) + 1024;
     auto kernel = gemm_tcgen05_pair_kernel<TOut, SWIGLU>;
     static bool configured = false;
     if (!configured) {
