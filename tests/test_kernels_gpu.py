@@ -523,6 +523,11 @@ TC_SCENARIOS = [
     ([(700, 1), (100, 450), (30, 1), (2000, 1)], 14, 2, 64, 16, None, 16),
     ([(515, 1), (200, 400), (64, 1)], 12, 2, 128, 16, None, 16),
     ([(400, 1), (350, 390)], 7, 1, 64, 32, 300, 16),
+    # many more pieces of work than the GPU holds blocks: every block takes several from the queue, its pipeline's
+    # bookkeeping running on from piece to piece (two blocks a SM at head size 64, one at 128)
+    ([(0, 1500)], 14, 2, 64, 16, None, 1),
+    ([(200, 900), (0, 130)], 8, 2, 128, 16, None, 1),
+    ([(700, 1200)], 10, 2, 64, 16, 500, 2),
 ]
 
 
