@@ -129,7 +129,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     // and a block that had a short piece takes another (a grid of one block per piece left the last pieces waiting for
     // places long after the first blocks had gone).  Buffers, stages and barrier phases go by g, the count of key tiles
     // the block has been through, so the pipeline's bookkeeping runs on from one piece to the next.
-    int g0 = 0, units_done = 0;
+    int g0 = 0, units_done = 0, units_seen = 0;
     for (;;) {
     if (tid == 0) sh.work = atomicAdd(p.queue, 1);
     __syncthreads();
@@ -151,6 +151,9 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     const int kt_begin = tile_begin + split * per_split, kt_end = min(tile_end, kt_begin + per_split);
     const int n = kt_end - kt_begin;
 
+    // Everything up to here - barriers, tensor memory, the first piece and its record, which the host wrote at the start of
+    // the step - has needed nothing of the kernel before (the rotation and append, which lets this one start early).
+    if (units_seen++ == 0) { pdl_wait(); pdl_launch_dependents(); }
     if (split < n_valid) {       // else a window has left this unit without keys
 
     if (warp >= 4) {
@@ -503,6 +506,6 @@ KVB_API int kvb_attention_tc(const void* q, void* out, const void* k_pages, cons
     }
     const int places = kvb_sm_count() * (D == 64 ? 2 : 1);       // blocks the GPU holds at once (shared memory, registers, tensor memory)
     dim3 grid(p.n_work < places ? p.n_work : places);
-    attention_tc_kernel<<<grid, THREADS, SMEM_BYTES, stream>>>(mq, mk, mv, p);
+    kvb_launch(attention_tc_kernel, grid, dim3(THREADS), (size_t)SMEM_BYTES, stream, mq, mk, mv, p);
     return kvb_launch_status();
 }
