@@ -299,17 +299,30 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
             asm volatile("prefetch.tensormap [%0];\n" ::"l"(&map_w) : "memory");
             uint32_t it = 0;
             bool ok = true;
+            // The weights of the first tile's first round of stages are asked for before the wait for the kernel that makes
+            // x: nobody writes them, and the ring is full of them by the time x exists.
+            const int early = pair < num_tiles ? (kblocks < STAGES ? kblocks : STAGES) : 0;
+            for (int kb = 0; kb < early; ++kb) {
+                const int n0 = (pair / m_blocks) * BN + rank * HALF_N;
+                if (leader) mbar_expect_tx(&sh.full[kb], 2 * STAGE_BYTES);         // the bytes of both blocks
+#pragma unroll
+                for (int sub = 0; sub < KSUB; ++sub)
+                    tma_load_2d_pair(tiles + kb * STAGE_BYTES + sub * SUB_BYTES_ + A_BYTES, &map_w, (kb * KSUB + sub) * BK, n0, &sh.full[kb]);
+            }
+            pdl_wait();
             for (int tile = pair; tile < num_tiles && ok; tile += num_pairs) {
                 const int m0 = (tile % m_blocks) * 2 * BM + rank * BM, n0 = (tile / m_blocks) * BN + rank * HALF_N;
                 for (int kb = 0; kb < kblocks; ++kb, ++it) {
                     const int s = it % STAGES;
                     const uint32_t round = it / STAGES;
+                    const bool weights_asked = (int)it < early;
                     if (round > 0 && !mbar_wait(&sh.empty[s], (round - 1) & 1)) { atomicOr(err, KVB_DEV_TIMEOUT); sh.failed = 1; ok = false; break; }
-                    if (leader) mbar_expect_tx(&sh.full[s], 2 * STAGE_BYTES);      // the bytes of both blocks
+                    if (leader && !weights_asked) mbar_expect_tx(&sh.full[s], 2 * STAGE_BYTES);
 #pragma unroll
                     for (int sub = 0; sub < KSUB; ++sub) {
                         tma_load_2d_pair(tiles + s * STAGE_BYTES + sub * SUB_BYTES_, &map_x, (kb * KSUB + sub) * BK, m0, &sh.full[s]);
-                        tma_load_2d_pair(tiles + s * STAGE_BYTES + sub * SUB_BYTES_ + A_BYTES, &map_w, (kb * KSUB + sub) * BK, n0, &sh.full[s]);
+                        if (!weights_asked)
+                            tma_load_2d_pair(tiles + s * STAGE_BYTES + sub * SUB_BYTES_ + A_BYTES, &map_w, (kb * KSUB + sub) * BK, n0, &sh.full[s]);
                     }
                 }
             }
@@ -455,7 +468,7 @@ static int launch_pair(const void* x, const void* w, const float* bias, TOut* y,
     const int tiles = ((M + 2 * BM - 1) / (2 * BM)) * ((N + 255) / 256);
     int pairs = sm_count() / 2;
     if (tiles < pairs) pairs = tiles;
-    kernel<<<2 * pairs, THREADS, smem, stream>>>(mx, mw, bias, y, M, N, K, err);
+    kvb_launch(kernel, dim3(2 * pairs), dim3(THREADS), smem, stream, mx, mw, bias, y, M, N, K, err);   // the cluster of two is the kernel's own attribute
     return kvb_launch_status();
 }
 
