@@ -46,7 +46,7 @@ class CacheManager:
         self.dtype = TORCH_DTYPES[dtype]
         self.device = torch.device(device) if device is not None else None
         self.slots = SlotAllocator(max_slots)
-        self.lengths = np.zeros(max_slots, dtype=np.int64)
+        self.lengths = [0] * max_slots             # a plain list: read several times a step and request, as Python ints
         self.groups: List[CacheGroup] = []
         self.entry_group: Dict[int, Tuple[int, int]] = {}   # cache id -> (group index, index in group)
         self.states: Dict[int, object] = {}      # cache id -> [slots, *shape] tensor, or {name: such a tensor}
@@ -88,7 +88,7 @@ class CacheManager:
 
     def length(self, slot: int) -> int:
         """Tokens of the request that steps have run so far (its next position)."""
-        return int(self.lengths[slot])
+        return self.lengths[slot]
 
     def pages_short(self, additions: Sequence[Tuple[int, int]]) -> int:
         """Largest shortfall of pages over the groups if each `(slot, new tokens)` of
@@ -97,7 +97,7 @@ class CacheManager:
         for g in self.groups:
             need = 0
             for slot, count in additions:
-                start = int(self.lengths[slot])
+                start = self.lengths[slot]
                 g.pages._check_length(start + count)
                 release, take, _, _ = g.pages.plan(slot, start, start + count)
                 need += len(take) - len(release)
@@ -106,7 +106,7 @@ class CacheManager:
 
     def page_delta(self, slot: int, count: int) -> List[int]:
         """Pages each group would take, net of those it gives back, if `count` tokens were appended to `slot`."""
-        start = int(self.lengths[slot])
+        start = self.lengths[slot]
         out = []
         for g in self.groups:
             g.pages._check_length(start + count)
@@ -131,7 +131,7 @@ class CacheManager:
         if short > 0:
             raise OutOfPages(f"the step needs {short} more pages than the pool has free")
         for g in self.groups:
-            plans = [(slot, g.pages.plan(slot, int(self.lengths[slot]), int(self.lengths[slot]) + count))
+            plans = [(slot, g.pages.plan(slot, self.lengths[slot], self.lengths[slot] + count))
                      for slot, count in additions]
             for slot, (release, _, _, _) in plans:
                 g.pages.give_back(slot, release)

@@ -93,8 +93,8 @@ class GroupPages:
         # table[slot, i]: physical page of the request's i-th logical page, -1 if none is held.
         self.table = np.full((max_slots, max_pages_per_request), -1, dtype=np.int32)
         # The request holds its logical pages lo..hi-1: table[slot, i] >= 0 exactly there.
-        self._lo = np.zeros(max_slots, dtype=np.int64)
-        self._hi = np.zeros(max_slots, dtype=np.int64)
+        self._lo = [0] * max_slots                 # plain lists: read several times a step and request, as Python ints
+        self._hi = [0] * max_slots
 
     # ---- what a range of new positions needs --------------------------------
     def first_needed_page(self, start: int) -> int:
@@ -106,7 +106,7 @@ class GroupPages:
     def plan(self, slot: int, start: int, end: int):
         """(logical pages to give back, logical pages to take, new lo, new hi) for running
         positions start..end-1 of `slot`."""
-        lo, hi = int(self._lo[slot]), int(self._hi[slot])
+        lo, hi = self._lo[slot], self._hi[slot]
         need_lo, need_hi = self.first_needed_page(start), pages_for(end, self.page_size)
         release = range(lo, min(max(need_lo, lo), hi))
         take = range(max(hi, need_lo), need_hi)
@@ -144,7 +144,7 @@ class GroupPages:
         self.take(slot, take, new_lo, new_hi)
 
     def release(self, slot: int) -> None:
-        lo, hi = int(self._lo[slot]), int(self._hi[slot])
+        lo, hi = self._lo[slot], self._hi[slot]
         self.allocator.free_many(self.table[slot, lo:hi])
         self.table[slot, lo:hi] = -1
         self._lo[slot] = self._hi[slot] = 0

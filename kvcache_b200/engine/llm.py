@@ -31,6 +31,7 @@ class LLM:
         self.scheduler = self._new_scheduler()
         self._pending = None            # the step whose tokens have not been read yet
         self._step_events = []          # (begin, end) CUDA events of steps whose device time has not been read yet
+        self._timing_events = []        # pairs that have been read: recorded again by later steps
         self.pipelined = True           # plan and launch a step before reading the one before it
         self.last_stats = None
         self.last_seconds = 0.0
@@ -62,11 +63,13 @@ class LLM:
                    for p in pieces]
         timed = self.core.device.type == "cuda"
         if timed:
-            begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            begin.record()
+            stream = self.core.runner.current_stream()
+            begin, end = self._timing_events.pop() if self._timing_events else \
+                (torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
+            begin.record(stream)
         _, tokens = self.core.runner.step(entries, sample=True)
         if timed:
-            end.record()
+            end.record(stream)
             self._step_events.append((begin, end))
         self.scheduler.launched(pieces)
         count = sum(1 for p in pieces if p.samples)
@@ -112,7 +115,7 @@ class LLM:
                     return
                 end.synchronize()
             self.scheduler.add_gpu_time(begin.elapsed_time(end) * 1e3)
-            self._step_events.pop(0)
+            self._timing_events.append(self._step_events.pop(0))
 
     def generate(self, prompts: Sequence[Sequence[int]],
                  params: Union[SamplingParams, Sequence[SamplingParams], None] = None) -> List[List[int]]:

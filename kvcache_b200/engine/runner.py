@@ -75,11 +75,39 @@ class StepLayout:
         self.total = offset
         self._remembered_for = None
         self._remembered = {}
+        self._host_views = {}
 
     def remember(self, buf) -> None:
         """Views of `buf` (the runner's one device buffer) are made once and handed out again: a step asks for two dozen."""
         self._remembered_for = buf
         self._remembered = {}
+        self._host_views = {}
+
+    def host_views(self, index: int, host) -> dict:
+        """The sections of staging buffer `index` (a numpy array) by name, and its block-table rows under ("table", g)."""
+        found = self._host_views.get(index)
+        if found is None:
+            found = {name: host[begin:begin + count] for name, (begin, count) in self.offsets.items()}
+            for g in range(self.num_groups):
+                found[("table", g)] = self.table(host, g)
+            self._host_views[index] = found
+        return found
+
+    def cut(self, buf, name: str, length: int):
+        """The first `length` elements of a section of the remembered buffer."""
+        key = (name, length)
+        found = self._remembered.get(key)
+        if found is None:
+            found = self._remembered[key] = self.view(buf, name)[:length]
+        return found
+
+    def upload_pair(self, index: int, dev, staging):
+        """(device slice, pinned slice) of the layout's length for staging buffer `index`."""
+        key = ("upload", index)
+        found = self._remembered.get(key)
+        if found is None:
+            found = self._remembered[key] = (dev[:self.total], staging[:self.total])
+        return found
 
     def view(self, buf, name: str):
         if buf is self._remembered_for:
@@ -127,7 +155,12 @@ class ModelRunner:
         self.split_mixed_steps = True     # see _split
         ring = 4 if self._on_cuda else 1
         self._staging = [torch.zeros(capacity, dtype=torch.int32, pin_memory=self._on_cuda) for _ in range(ring)]
-        self._staging_events = [None] * ring
+        self._staging_np = [t.numpy() for t in self._staging]
+        # Events are made once and recorded again and again, on a stream that is looked up once a step: an event made per
+        # use and recorded on "the current stream" costs two stream look-ups of 10-20 us each on the host.
+        self._staging_events = [torch.cuda.Event() if self._on_cuda else None for _ in range(ring)]
+        self._staging_used = [False] * ring
+        self._device_index = (self.device.index or 0) if self._on_cuda else None
         self._ring = 0
         self._graphs: Dict[int, _DecodeGraph] = {}
         self._layouts: Dict[Tuple[int, int, int], StepLayout] = {}
@@ -137,6 +170,7 @@ class ModelRunner:
         # input ids from here (StepEntry.token_from_last) without the host ever seeing them.
         self.last_tokens = torch.zeros(max(self.max_segments, 1), dtype=torch.int32, device=self.device)
         self._token_host = [torch.zeros(max(self.max_segments, 1), dtype=torch.int32, pin_memory=self._on_cuda) for _ in range(3)]
+        self._token_events = [torch.cuda.Event() if self._on_cuda else None for _ in range(3)]
         self._token_ring = 0
         self.steps_run = 0
         self.last_h2d_bytes = 0
@@ -146,10 +180,13 @@ class ModelRunner:
     def _next_staging(self):
         i = self._ring
         self._ring = (self._ring + 1) % len(self._staging)
-        event = self._staging_events[i]
-        if event is not None:
-            event.synchronize()
+        if self._staging_used[i]:
+            self._staging_events[i].synchronize()
         return i, self._staging[i]
+
+    def current_stream(self):
+        """The stream the step's work goes to (the caller's current one), as an object that events can be recorded on."""
+        return torch.cuda.current_stream(self._device_index) if self._on_cuda else None
 
     def prepare(self, entries: Sequence[StepEntry]):
         """Extends the cache for the entries, packs and uploads the step's metadata."""
@@ -177,26 +214,26 @@ class ModelRunner:
                                                            self.planners)
             layout.remember(self._meta_device)
         index, staging = self._next_staging()
-        host = staging.numpy()
+        hv = layout.host_views(index, self._staging_np[index])
         counts_np = np.asarray(counts, dtype=np.int32)
         starts_np = np.asarray(starts, dtype=np.int32)
         q_start = np.zeros(S, dtype=np.int32)
         np.cumsum(counts_np[:-1], out=q_start[1:])
         if T == S:                                   # one token per request: no concatenation needed
-            layout.view(host, "token_ids")[:] = [max(e.tokens[0], 0) for e in entries]
-            layout.view(host, "token_src")[:] = [e.token_from_last for e in entries]
+            hv["token_ids"][:] = [max(e.tokens[0], 0) for e in entries]
+            hv["token_src"][:] = [e.token_from_last for e in entries]
             row_segment = np.arange(S, dtype=np.int32)
-            layout.view(host, "positions")[:] = starts_np
+            hv["positions"][:] = starts_np
         elif S == 1:                                 # one portion of one prompt
             if entries[0].token_from_last >= 0:
                 raise ValueError("token_from_last applies to an entry of one token")
-            np.maximum(np.asarray(entries[0].tokens, dtype=np.int32), 0, out=layout.view(host, "token_ids"))
-            layout.view(host, "token_src")[:] = -1
+            np.maximum(np.asarray(entries[0].tokens, dtype=np.int32), 0, out=hv["token_ids"])
+            hv["token_src"][:] = -1
             row_segment = 0
-            layout.view(host, "positions")[:] = np.arange(starts[0], starts[0] + T, dtype=np.int32)
+            hv["positions"][:] = np.arange(starts[0], starts[0] + T, dtype=np.int32)
         else:
-            layout.view(host, "token_ids")[:] = np.maximum(np.concatenate([np.asarray(e.tokens, dtype=np.int32) for e in entries]), 0)
-            src = layout.view(host, "token_src")
+            hv["token_ids"][:] = np.maximum(np.concatenate([np.asarray(e.tokens, dtype=np.int32) for e in entries]), 0)
+            src = hv["token_src"]
             src[:] = -1
             for i, e in enumerate(entries):
                 if e.token_from_last >= 0:
@@ -204,13 +241,13 @@ class ModelRunner:
                         raise ValueError("token_from_last applies to an entry of one token")
                     src[q_start[i]] = e.token_from_last
             row_segment = np.repeat(np.arange(S, dtype=np.int32), counts_np)
-            layout.view(host, "positions")[:] = np.arange(T, dtype=np.int32) - q_start[row_segment] + starts_np[row_segment]
-        layout.view(host, "row_segment")[:] = row_segment
-        layout.view(host, "seg_q_start")[:] = q_start
-        layout.view(host, "seg_q_len")[:] = counts_np
-        layout.view(host, "seg_kv_len")[:] = starts_np + counts_np
+            hv["positions"][:] = np.arange(T, dtype=np.int32) - q_start[row_segment] + starts_np[row_segment]
+        hv["row_segment"][:] = row_segment
+        hv["seg_q_start"][:] = q_start
+        hv["seg_q_len"][:] = counts_np
+        hv["seg_kv_len"][:] = starts_np + counts_np
         slots = [e.slot for e in entries]
-        layout.view(host, "seg_slot")[:] = slots
+        hv["seg_slot"][:] = slots
         if R:
             wanted, temps, counters, seeds = [], [], [], []
             for i, e in enumerate(entries):
@@ -220,27 +257,27 @@ class ModelRunner:
                     temps.append(t)
                     counters.append(counter)
                     seeds.append(seed & 0x7FFFFFFFFFFFFFFF)
-            layout.view(host, "wanted_rows")[:] = wanted
-            layout.view(host, "sample_temperature").view(np.float32)[:] = temps
-            layout.view(host, "sample_counter")[:] = counters
-            layout.view(host, "sample_seed").view(np.int64)[:] = seeds
+            hv["wanted_rows"][:] = wanted
+            hv["sample_temperature"].view(np.float32)[:] = temps
+            hv["sample_counter"][:] = counters
+            hv["sample_seed"].view(np.int64)[:] = seeds
         for g in range(len(self.cache.groups)):
-            layout.table(host, g)[:] = self.cache.table_rows(g, slots)
+            hv[("table", g)][:] = self.cache.table_rows(g, slots)
         planned = []
         for planner in self.planners:
             arrays, plan_counts = planner.plan(starts_np, counts_np)
             for name, array in arrays.items():
                 if len(array):
-                    layout.view(host, f"{planner.name}.{name}")[:len(array)] = array
+                    hv[f"{planner.name}.{name}"][:len(array)] = array
             planned.append((planner.name, {name: len(array) for name, array in arrays.items()}, plan_counts))
 
         dev = self._meta_device
-        dev[:layout.total].copy_(staging[:layout.total], non_blocking=True)
+        there, here = layout.upload_pair(index, dev, staging)
+        there.copy_(here, non_blocking=True)
         self.last_h2d_bytes = layout.total * 4
         if self._on_cuda:
-            event = torch.cuda.Event()
-            event.record()
-            self._staging_events[index] = event
+            self._staging_events[index].record(self.current_stream())
+            self._staging_used[index] = True
         batch = StepBatch(
             num_tokens=T, num_segments=S, num_wanted=R,
             token_ids=layout.view(dev, "token_ids"), positions=layout.view(dev, "positions"),
@@ -248,9 +285,9 @@ class ModelRunner:
             seg_q_len=layout.view(dev, "seg_q_len"), seg_kv_len=layout.view(dev, "seg_kv_len"),
             seg_slot=layout.view(dev, "seg_slot"), wanted_rows=layout.view(dev, "wanted_rows"),
             token_src=layout.view(dev, "token_src"), last_tokens=self.last_tokens,
-            plans={name: StepPlan({key: layout.view(dev, f"{name}.{key}")[:length] for key, length in lengths.items()}, plan_counts)
+            plans={name: StepPlan({key: layout.cut(dev, f"{name}.{key}", length) for key, length in lengths.items()}, plan_counts)
                    for name, lengths, plan_counts in planned},
-            max_q_len=int(counts_np.max()), max_kv_len=int((starts_np + counts_np).max()),
+            max_q_len=max(counts), max_kv_len=max(s + c for s, c in zip(starts, counts)),
             host={"counts": counts_np, "starts": starts_np, "q_start": q_start, "slots": slots})
         view = self.cache.step_view([layout.table(dev, g) for g in range(len(self.cache.groups))])
         return batch, view, layout
@@ -362,8 +399,8 @@ class ModelRunner:
         host[:count].copy_(self.last_tokens[:count], non_blocking=True)
         if not self._on_cuda:
             return lambda: host[:count].numpy().copy()
-        event = torch.cuda.Event()
-        event.record()
+        event = self._token_events[index]       # its last use was three reads ago: that copy has long been waited for
+        event.record(self.current_stream())
 
         def wait():
             event.synchronize()
