@@ -44,14 +44,14 @@ constexpr int D = KVB_HEAD_DIM;
 static_assert(D == 64 || D == 128, "head size 64 or 128");
 constexpr int BQ = 128, BKEYS = 64;                  // query rows and keys of a tile
 constexpr int HALVES = D / 64;                       // 64-wide (128-byte) column blocks of a head
-constexpr int SUB_BYTES = BQ * 128;                  // a [128 rows x 64 columns] bfloat16 sub-tile (Q, P), swizzled
+constexpr int SUB_BYTES = BQ * 128;                  // a [128 rows x 64 columns] bfloat16 sub-tile of Q, swizzled
 constexpr int KV_SUB_BYTES = BKEYS * 128;            // a [64 keys x 64 columns] sub-tile (K, V)
 constexpr int Q_BYTES = HALVES * SUB_BYTES, KV_BYTES = HALVES * KV_SUB_BYTES;
 constexpr int STAGES = 4;                            // of keys, and of values: two rings, each filled on its own
 static_assert(STAGES == 4, "the helper warps reuse a stage two tiles after its MMA without asking a barrier");
 constexpr int SMEM_BYTES = Q_BYTES + 2 * STAGES * KV_BYTES + 1024;
 constexpr int TMEM_COLS = D == 64 ? 256 : 512;       // S: 2 x 64 columns, O_t: 2 x D columns
-constexpr int THREADS = 192;                         // warps 0-3: softmax rows; warp 4: MMA issue; warp 5: TMA loads
+constexpr int THREADS = 192;                         // warps 0-3: softmax rows; warp 4: keys and Q K^T; warp 5: values and P V
 constexpr float NEG_INF = -INFINITY;
 
 // Shared-memory descriptor of an MN-major operand with 128-byte swizzle: rows of 64 elements (128 bytes) along
@@ -159,7 +159,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     if (warp >= 4) {
         // ---- warp 4: keys and S = Q K^T; warp 5: values and O_t = P V.  Its first lanes copy a page each of a tile, its
         // first lane issues the MMAs; every lane waits on the barriers (a wait by one lane and a broadcast costs twice
-        // as much), and a vote keeps the outcome the same in all of them. ----
+        // as much). ----
         const bool keys = warp == 4;
         const int* table = p.block_table + (size_t)seg * p.table_stride;
         const int pages_per_tile = BKEYS >> p.page_shift;
