@@ -254,11 +254,13 @@ __device__ __forceinline__ void mbar_arrive_leader(uint64_t* bar) {
     asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];\n" ::"r"(smem_u32(bar) & PEER_BIT_MASK) : "memory");
 }
 
-template <typename TOut, bool SWIGLU>
+template <int BN, typename TOut, bool SWIGLU>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1)
 gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
                          const float* __restrict__ bias, TOut* __restrict__ y, int M, int N, int K, int* __restrict__ err) {
-    constexpr int BN = 256, HALF_N = 128;
+    // BN columns of y a tile, 256 or a little fewer: the launcher takes the width whose last round of tiles wastes least.
+    static_assert(BN % 32 == 0 && BN >= 128 && BN <= 256, "tile width");
+    constexpr int HALF_N = BN / 2, ACC_STRIDE = 256;             // the two accumulators lie 256 columns apart whatever BN
     // A stage holds KSUB sub-tiles of 64 along K of each operand (the 128-byte swizzle takes no wider box): the thread that
     // issues the MMAs pays for a barrier wait and a commit - about 250 clocks - once a stage, and with 64 of K a stage that
     // was half as long again as the four MMAs themselves take (the tensor pipe was busy two thirds of the time).
@@ -284,7 +286,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
         asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
     }
     if (warp == 1) {   // both blocks of the pair take part in the allocation: two accumulators of 256 columns in each
-        asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_u32(&sh.tmem_base)), "r"(2 * BN) : "memory");
+        asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_u32(&sh.tmem_base)), "r"(2 * ACC_STRIDE) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;\n" ::: "memory");
     }
     asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
@@ -337,7 +339,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
                 const uint32_t use = local >> 1;
                 if (use > 0 && !mbar_wait(&sh.accum_empty[b], (use - 1) & 1)) { atomicOr(err, KVB_DEV_TIMEOUT); sh.failed = 1; ok = false; break; }
                 asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-                const uint32_t acc = tmem + b * BN;
+                const uint32_t acc = tmem + b * ACC_STRIDE;
                 for (int kb = 0; kb < kblocks; ++kb, ++it) {
                     const int s = it % STAGES;
                     if (!mbar_wait(&sh.full[s], (it / STAGES) & 1)) { atomicOr(err, KVB_DEV_TIMEOUT); sh.failed = 1; ok = false; break; }
@@ -369,7 +371,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
 #pragma unroll 1
             for (int c = 0; c < BN / 32; ++c) {
                 uint32_t r[32];
-                tmem_ld32(tmem + ((uint32_t)(quarter * 32) << 16) + b * BN + c * 32, r);
+                tmem_ld32(tmem + ((uint32_t)(quarter * 32) << 16) + b * ACC_STRIDE + c * 32, r);
                 const int n = n0 + c * 32;
                 if (m >= M || n >= N) continue;
                 store_chunk<TOut, SWIGLU>(r, bias, y, m, n, N);
@@ -390,7 +392,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
     cluster_sync_all();
     if (warp == 1) {
         asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-        asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;\n" ::"r"(tmem), "r"(2 * BN) : "memory");
+        asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;\n" ::"r"(tmem), "r"(2 * ACC_STRIDE) : "memory");
     }
 }
 
@@ -450,22 +452,22 @@ static int launch(const void* x, const void* w, const float* bias, TOut* y, int 
     return kvb_launch_status();
 }
 
-template <typename TOut, bool SWIGLU>
+template <int BN, typename TOut, bool SWIGLU>
 static int launch_pair(const void* x, const void* w, const float* bias, TOut* y, int M, int N, int K, int* err, cudaStream_t stream) {
     CUtensorMap mx, mw;
     int rc = make_map(&mx, x, M, K, BM);
     if (rc != KVB_OK) return rc;
-    rc = make_map(&mw, w, N, K, 128);
+    rc = make_map(&mw, w, N, K, BN / 2);
     if (rc != KVB_OK) return rc;
-    const size_t smem = (size_t)PAIR_STAGES * PAIR_KSUB * (A_BYTES + 128 * BK * 2) + 1024;
-    auto kernel = gemm_tcgen05_pair_kernel<TOut, SWIGLU>;
+    const size_t smem = (size_t)PAIR_STAGES * PAIR_KSUB * (A_BYTES + (BN / 2) * BK * 2) + 1024;
+    auto kernel = gemm_tcgen05_pair_kernel<BN, TOut, SWIGLU>;
     static bool configured = false;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
-    const int tiles = ((M + 2 * BM - 1) / (2 * BM)) * ((N + 255) / 256);
+    const int tiles = ((M + 2 * BM - 1) / (2 * BM)) * ((N + BN - 1) / BN);
     int pairs = sm_count() / 2;
     if (tiles < pairs) pairs = tiles;
     kvb_launch(kernel, dim3(2 * pairs), dim3(THREADS), smem, stream, mx, mw, bias, y, M, N, K, err);   // the cluster of two is the kernel's own attribute
@@ -478,7 +480,19 @@ template <typename TOut, bool SWIGLU>
 static int dispatch(const void* x, const void* w, const float* bias, TOut* y, int M, int N, int K, int* err, cudaStream_t stream) {
     const int wide_tiles = ((M + BM - 1) / BM) * ((N + 255) / 256);
     const int pair_tiles = ((M + 2 * BM - 1) / (2 * BM)) * ((N + 255) / 256);
-    if (pair_mode() && pair_tiles >= sm_count()) return launch_pair<TOut, SWIGLU>(x, w, bias, y, M, N, K, err, stream);
+    if (pair_mode() && pair_tiles >= sm_count()) {
+        // The pairs work through the tiles in rounds, and the last round may be nearly empty (2,048 x 9,728: 304 tiles of
+        // 256 columns on 74 pairs are 4.1 rounds and cost 5).  Of 256, 224 and 192 columns the width is taken whose
+        // rounds times width is least: there 352 tiles of 224 are 4.8 rounds, an eighth less time.
+        const int m_pairs = (M + 2 * BM - 1) / (2 * BM), pairs = sm_count() / 2;
+        auto cost = [&](int bn) { const int t = m_pairs * ((N + bn - 1) / bn); return (long long)((t + pairs - 1) / pairs) * bn; };
+        // A narrower tile reads more operand bytes per product, so it must save a twentieth at least (4,096 x 17,920 x
+        // 1,536: 18 rounds of 224 against 16 of 256 are 1.6 % less by this count and measured 2.5 % more time).
+        const long long wide = cost(256) * 20, c224 = cost(224) * 21, c192 = cost(192) * 21;
+        if (c224 < wide && c224 <= c192) return launch_pair<224, TOut, SWIGLU>(x, w, bias, y, M, N, K, err, stream);
+        if (c192 < wide) return launch_pair<192, TOut, SWIGLU>(x, w, bias, y, M, N, K, err, stream);
+        return launch_pair<256, TOut, SWIGLU>(x, w, bias, y, M, N, K, err, stream);
+    }
     if (wide_tiles >= sm_count()) return launch<256, TOut, SWIGLU>(x, w, bias, y, M, N, K, err, stream);
     return launch<128, TOut, SWIGLU>(x, w, bias, y, M, N, K, err, stream);
 }

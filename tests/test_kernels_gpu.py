@@ -198,7 +198,8 @@ def test_gemm_skinny_rows_do_not_depend_on_the_batch(kernels, request):
 
 TC_SHAPES = [(128, 128, 64), (128, 128, 128), (2048, 1152, 896), (300, 896, 4864), (17, 331, 120), (129, 130, 72),
              (1, 64, 8), (250, 9728, 896), (64, 151936, 896), (1000, 200, 200),
-             (2048, 9728, 896), (2100, 9800, 904), (4096, 5000, 136)]        # enough 256 x 256 tiles for two SMs per tile
+             (2048, 9728, 896), (2100, 9800, 904), (4096, 5000, 136),        # enough 256 x 256 tiles for two SMs per tile
+             (2048, 4736, 200), (2048, 6144, 136), (4000, 2440, 264)]        # ... of 192 columns, of 256, of 192 with ragged edges
 
 
 @pytest.mark.parametrize("M,N,K", [(17, 1152, 896), (64, 896, 4864), (100, 896, 896), (128, 1000, 320), (33, 331, 120),
@@ -276,7 +277,7 @@ def test_gemm_tcgen05(M, N, K):
 
 
 @pytest.mark.parametrize("M,I,K", [(128, 64, 64), (300, 4864, 896), (77, 200, 120), (2048, 320, 96), (2048, 4864, 896),
-                                   (2500, 4872, 200)])
+                                   (2500, 4872, 200), (2048, 2368, 136), (2048, 3072, 72)])    # tiles of 224, 224, 192 and 256 columns
 def test_gemm_tcgen05_gated(M, I, K):
     from kvcache_b200.engine.workspace import Workspace
     from kvcache_b200.kernels.api import CudaKernels
