@@ -563,6 +563,37 @@ def test_paged_attention_tc(kernels, request, scenario):
         assert int(ws._buffers["attn.tc_tickets"].sum()) == 0
 
 
+@pytest.mark.parametrize("seed", [0, 1, 2])
+def test_paged_attention_random_shapes(kernels, request, seed):
+    """Random mixes of segments (one token, a few, hundreds), group sizes, page sizes, windows and unit sizes through the
+    tensor-memory prefill kernel and the TMA decode kernel, against float64 on the same bfloat16 inputs."""
+    import random
+    from kvcache_b200.engine.workspace import Workspace
+    rng = random.Random(seed)
+    saved = kernels.tc_attention_min_rows
+    kernels.tc_attention_min_rows = 2
+    request.addfinalizer(lambda: setattr(kernels, "tc_attention_min_rows", saved))
+    ws = Workspace(DEV)
+    for it in range(8):
+        D, Hkv, G = rng.choice([64, 128]), rng.choice([1, 2, 4]), rng.choice([1, 2, 3, 7])
+        page, window = rng.choice([8, 16, 32, 64]), rng.choice([None, None, rng.randint(40, 900)])
+        segments = [(rng.randint(0, 1500), rng.choice([1, 2, rng.randint(2, 200), rng.randint(100, 900)]))
+                    for _ in range(rng.randint(1, 4))]
+        batch, kv = paged_scenario(segments, num_kv_heads=Hkv, head_dim=D, page_size=page, dtype=torch.bfloat16, device="cpu",
+                                   window=window, seed=100 * seed + it, tc_min_key_tiles=rng.choice([1, 2, 4, 16]))
+        T, Hq = batch.num_tokens, Hkv * G
+        q = torch.randn(T, Hq * D, generator=torch.Generator().manual_seed(it)).to(torch.bfloat16)
+        ref = torch.empty(T, Hq * D, dtype=torch.bfloat16)
+        REF.paged_attention(q, batch, kv, ref, Hq, D ** -0.5)
+        if window:
+            for i, (cached, new) in enumerate(segments):
+                kv.block_table[i, :max(0, cached - window + 1) // page] = -1
+        out = torch.full((T, Hq * D), float("nan"), dtype=torch.bfloat16, device=DEV)
+        kernels.paged_attention(q.to(DEV), batch_to(batch, DEV), clone_kv(kv, DEV), out, Hq, D ** -0.5, ws)
+        kernels.check_errors()
+        assert_close(out, ref, REL[torch.bfloat16], f"{segments}, Hq {Hq}, Hkv {Hkv}, D {D}, page {page}, window {window}")
+
+
 def test_flash_attention_sees_one_far_key_and_the_window_edge(kernels):
     """bfloat16 tensor-core path: a single key that takes all the weight is found among
     thousands (another page, another split); with a window it is seen at distance
